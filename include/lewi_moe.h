@@ -1,0 +1,187 @@
+/*
+ * lewi_moe.h -- C ABI of liblewi_moe.so: the MoE-layer hot path of Lewi Surge as sm_100a CUDA kernels.
+ *
+ * Conventions (all entry points):
+ *   - every pointer is a DEVICE pointer unless the parameter name ends in `_host`;
+ *   - `stream` is a cudaStream_t passed as void*; calls only enqueue work, never synchronise,
+ *     never allocate: the caller owns inputs, outputs and workspaces;
+ *   - return value: 0 = enqueued; negative = rejected argument (nothing was launched);
+ *     device-side problems (a bounded wait that ran out, an index out of range) are recorded in a
+ *     per-device status word read with lewi_last_status();
+ *   - row-major tensors; `bf16` = __nv_bfloat16 bits; dtype codes LEWI_BF16 / LEWI_F32.
+ *
+ * Slot numbering: routed slot i = t*k + j (token t, j-th choice), as in the reference's
+ * `selected_experts.reshape(-1)` (modal/moe_permute.py:401).
+ *
+ * Padded-block layout: the rows of expert e occupy padded rows [pad_offsets[e], pad_offsets[e+1]),
+ * every group start is a multiple of `block` (128); unused rows of the last block of a group are
+ * zero rows.  Static bound on padded rows: lewi_padded_rows_bound().
+ */
+#ifndef LEWI_MOE_H_
+#define LEWI_MOE_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define LEWI_BF16 0
+#define LEWI_F32 1
+
+/* error codes (negative return values) */
+#define LEWI_OK 0
+#define LEWI_ERR_ARG (-1)       /* null pointer / non-positive size / unsupported dtype          */
+#define LEWI_ERR_SHAPE (-2)     /* shape not supported by the kernels (alignment, limits)        */
+#define LEWI_ERR_WORKSPACE (-3) /* workspace too small                                           */
+#define LEWI_ERR_CUDA (-4)      /* a CUDA runtime / driver call failed at launch                 */
+#define LEWI_ERR_LIMIT (-5)     /* size beyond a compiled-in maximum                             */
+
+/* device status bits (lewi_last_status) */
+#define LEWI_STATUS_WAIT_TIMEOUT 1 /* a bounded device-side wait ran out */
+#define LEWI_STATUS_BAD_INDEX 2    /* an index read from a table was out of range and skipped */
+
+int lewi_version(void);
+const char* lewi_error_string(int code);
+
+/* Reads (and clears) the status word of the current device.  Synchronises `stream`. */
+int lewi_last_status(void* stream);
+
+/* Static bound on padded rows: floor((m + num_experts*(block-1)) / block) * block. */
+int64_t lewi_padded_rows_bound(int64_t m, int num_experts, int block);
+
+/* Bytes of scratch that lewi_router_topk / lewi_sort_indices need for T tokens (M = T*k slots). */
+int64_t lewi_route_workspace_bytes(int64_t num_slots, int num_experts);
+
+/* ------------------------------------------------------------------------------------------------
+ * Router.  Replaces the router of maxtext.layers.moe.RoutedMoE as configured by
+ * configs/stage1.yml:33-41 (softmax -> top-k -> renormalise), plus the slot sort of
+ * modal/moe_permute.py:240-264 and the padded-block table, in one call.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* logits[T,E] (f32) = x[T,d] (bf16) . w_router[d,E] (f32) (+ bias[E] if not null), f32 accumulate. */
+int lewi_router_logits(void* stream, const void* x, const float* w_router, const float* bias,
+                       float* logits, int64_t T, int d, int E);
+
+/* Fused softmax + top-k + renormalise + stable counting sort + block table.
+ *   logits   f32 [T,E]
+ *   topk_idx i32 [T,k]  experts by probability descending, lower index first on ties
+ *   topk_w   f32 [T,k]  renormalised probabilities
+ *   counts i32 [E], offsets i32 [E+1], pad_offsets i32 [E+1]
+ *   block_expert i32 [Mpad/block] (-1 past n_blocks), n_blocks i32 [1]
+ *   order i32 [M], pos i32 [M]      exactly sort_indices() of the reference (pos = inverse of order)
+ *   pad_pos i32 [M]                 padded row of slot i
+ *   row_slot i32 [Mpad]             slot held by padded row r, -1 for a padding row
+ *   probs_mean f32 [E] or null      column sums of the soft-max probabilities (for the load-balance loss)
+ */
+int lewi_router_topk(void* stream, const float* logits, int64_t T, int E, int k, int block,
+                     int32_t* topk_idx, float* topk_w, int32_t* counts, int32_t* offsets,
+                     int32_t* pad_offsets, int32_t* block_expert, int32_t* n_blocks, int32_t* order,
+                     int32_t* pos, int32_t* pad_pos, int32_t* row_slot, float* probs_sum,
+                     void* workspace, int64_t workspace_bytes);
+
+/* sort_indices(flat_experts, num_experts, method) of modal/moe_permute.py:240-264 (both methods give
+ * the same result; this is the counting sort).  Padded-layout outputs may be null (block <= 0 too). */
+int lewi_sort_indices(void* stream, const int32_t* flat_experts, int64_t M, int E, int block,
+                      int32_t* order, int32_t* pos, int32_t* counts, int32_t* offsets,
+                      int32_t* pad_offsets, int32_t* block_expert, int32_t* n_blocks,
+                      int32_t* pad_pos, int32_t* row_slot, void* workspace, int64_t workspace_bytes);
+
+/* Gradient of the renormalised top-k weights with respect to the logits: dlogits f32 [T,E] and/or
+ * a bf16 copy dlogits_bf16 [T,E] (either may be null) that feeds the tensor-core GEMMs for the
+ * router-weight and input gradients. */
+int lewi_router_topk_bwd(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
+                         float* dlogits, void* dlogits_bf16, int64_t T, int E, int k);
+
+/* dst (bf16) = round-to-nearest-even(src (f32)), n elements.  Used for the bf16 copy of the f32 router
+ * weight (the reference casts rhs to the lhs dtype before its GEMMs: modal/padded_gmm.py:67). */
+int lewi_cast_f32_to_bf16(void* stream, const float* src, void* dst, int64_t n);
+
+/* Row/group tables for a drop-in ragged_dot: from group_sizes[E] (rows already sorted by expert)
+ * builds pad_offsets, block_expert, n_blocks, row_of_padded[Mpad] (-1 = padding) and
+ * padded_of_row[M] (-1 for rows past sum(group_sizes)).  Replaces the index arithmetic of
+ * modal/padded_gmm.py:51-64 with a dropless layout. */
+int lewi_group_tables(void* stream, const int32_t* group_sizes, int64_t M, int E, int block,
+                      int32_t* pad_offsets, int32_t* block_expert, int32_t* n_blocks,
+                      int32_t* row_of_padded, int32_t* padded_of_row);
+
+/* ------------------------------------------------------------------------------------------------
+ * Gather kernels.  Replace gather_rows / gather_reduce / gather_dot of
+ * modal/moe_permute.py:116-158, 214-225, 228-234.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* out[i] = x[idx[i]] * scale[i] (scale may be null; multiply in f32, cast back).
+ * idx[i] < 0 writes a zero row.  If idx_div > 1 the source row is idx[i] / idx_div (dispatch uses
+ * order // k).  If scale_by_idx != 0, scale is indexed by idx[i] instead of i.
+ * If n_rows_dev is not null only the first (*n_rows_dev * rows_per_unit) rows are produced. */
+int lewi_gather_rows(void* stream, const void* x, const int32_t* idx, const float* scale, void* out,
+                     int64_t n_src, int64_t m, int d, int dtype, int idx_div, int scale_by_idx,
+                     const int32_t* n_rows_dev, int rows_per_unit);
+
+/* out[t] = sum_j w[t,j] * y[pos[t,j]] (+ add0[t] + add1[t]) accumulated in f32.
+ * w, add0, add1 may be null.  in_dtype: dtype of y/add0/add1; out_dtype: dtype of out.
+ * y has n_y_rows rows; a negative pos contributes nothing, a pos >= n_y_rows is skipped and
+ * raises LEWI_STATUS_BAD_INDEX. */
+int lewi_gather_reduce(void* stream, const void* y, const int32_t* pos, const float* w,
+                       const void* add0, const void* add1, void* out, int64_t n, int k, int d,
+                       int in_dtype, int out_dtype, int64_t n_y_rows);
+
+/* out[t,j] = <g[t], y[pos[t,j]]> in f32. */
+int lewi_gather_dot(void* stream, const void* y, const int32_t* pos, const void* g, float* out,
+                    int64_t n, int k, int d, int dtype, int64_t n_y_rows);
+
+/* ------------------------------------------------------------------------------------------------
+ * Grouped GEMMs on the padded-block layout (tcgen05 tensor cores, TMEM accumulators, TMA loads).
+ * Replace jax.lax.ragged_dot as patched by modal/padded_gmm.py:45-69 and modal/te_gmm.py:12-19 and
+ * the expert SwiGLU of maxtext.layers.moe.RoutedMoE (weights wi_0/wi_1 [E,d,f], wo [E,f,d],
+ * modal/stage2.py:338-341).  `a` has `rows` rows; row block b (128 rows) belongs to expert
+ * block_expert[b]; only the first *n_blocks blocks are processed.  block_expert == null means a
+ * single group (expert 0) of `rows` rows (the shared expert); then n_blocks may be null too.
+ * K and N extents must be multiples of 64; all operands bf16.
+ * ---------------------------------------------------------------------------------------------- */
+
+/* out[r, :] = a[r, :] . b[e]      a [rows,K], b [E,K,N], out [rows,N] (out_dtype), optional f32 row_scale[rows]. */
+int lewi_grouped_gemm_nn(void* stream, const void* a, const void* b, void* out, const float* row_scale,
+                         const int32_t* block_expert, const int32_t* n_blocks, int64_t rows, int K,
+                         int N, int E, int out_dtype);
+
+/* out[r, :] = a[r, :] . b[e]^T    a [rows,K], b [E,N,K], out [rows,N]. */
+int lewi_grouped_gemm_nt(void* stream, const void* a, const void* b, void* out, const float* row_scale,
+                         const int32_t* block_expert, const int32_t* n_blocks, int64_t rows, int K,
+                         int N, int E, int out_dtype);
+
+/* out[e] = a[rows of e]^T . b[rows of e]   a [rows,Ma], b [rows,Nb], out [E,Ma,Nb] (out_dtype).
+ * pad_offsets i32 [E+1] gives each expert's padded row range (null: one group of all rows).
+ * Experts without rows get zeros.  If out2 is not null, columns >= Nb/2 of the product go to
+ * out2 [E,Ma,Nb/2] and out is [E,Ma,Nb/2] (used for dW_gate | dW_up from one pass). */
+int lewi_grouped_gemm_tn(void* stream, const void* a, const void* b, void* out, void* out2,
+                         const int32_t* pad_offsets, int64_t rows, int Ma, int Nb, int E,
+                         int out_dtype);
+
+/* Fused gate/up projection + SwiGLU:  g = xs.Wg[e], u = xs.Wu[e], h = silu(g)*u.
+ * xs [rows,d], w_gate/w_up [E,d,f], gu [rows,2f] (g | u, bf16, may be null), h [rows,f] bf16. */
+int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_gate,
+                                    const void* w_up, void* gu, void* h,
+                                    const int32_t* block_expert, const int32_t* n_blocks,
+                                    int64_t rows, int d, int f, int E);
+
+/* Backward of the down projection fused with the SwiGLU derivative:
+ * dh = dys.Wd[e]^T; dg = dh*u*silu'(g); du = dh*silu(g).  dys [rows,d], w_down [E,f,d],
+ * gu [rows,2f], dgu [rows,2f] (dg | du). */
+int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_down, const void* gu,
+                                 void* dgu, const int32_t* block_expert, const int32_t* n_blocks,
+                                 int64_t rows, int d, int f, int E);
+
+/* dxs = dg.Wg[e]^T + du.Wu[e]^T.  dgu [rows,2f], w_gate/w_up [E,d,f], dxs [rows,d] bf16. */
+int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, const void* w_up,
+                         void* dxs, const int32_t* block_expert, const int32_t* n_blocks,
+                         int64_t rows, int d, int f, int E);
+
+/* Bring-up hook (not part of the drop-in surface): overrides the shared-memory matrix-descriptor
+ * geometry in bytes for K-major and MN-major operands; 0 keeps a value. */
+int lewi_debug_set_desc(int k_lbo, int k_sbo, int k_step, int mn_lbo, int mn_sbo, int mn_step);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LEWI_MOE_H_ */
