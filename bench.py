@@ -1,0 +1,388 @@
+#!/usr/bin/env python
+"""MoE layer forward+backward throughput on B200 (tokens/s), with roofline and CPU baseline.
+
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference] [--config config2]
+
+One step = one forward + backward of the MoE layer over one batch of seeded synthetic activations
+(router, dispatch, SwiGLU expert grouped GEMMs, shared expert, combine, and every gradient).  Prints
+ONE JSON line on rank 0.  For N > 1 launch under torch.distributed.run, one rank per GPU.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+  sys.path.insert(0, ROOT)
+
+# Workloads named by BASELINE.json's configs (per-GPU shapes).
+CONFIGS = {
+    "config1": dict(T=4096, d=1024, E=64, f=512, k=6, fs=512, bias=False),
+    "config2": dict(T=32768, d=1024, E=128, f=512, k=6, fs=512, bias=False),
+    "config3": dict(T=65536, d=1024, E=128, f=512, k=6, fs=512, bias=True),
+    "config4": dict(T=16384, d=2048, E=256, f=768, k=8, fs=2048, bias=False),
+    "config5": dict(T=16384, d=1024, E=128, f=512, k=6, fs=512, bias=False),
+}
+METRIC = "moe_layer_fwd_bwd_tokens_per_s"
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+def layer_flops(c):
+  m = c["T"] * c["k"]
+  return 18 * m * c["d"] * c["f"] + 18 * c["T"] * c["d"] * c["fs"] + 6 * c["T"] * c["d"] * c["E"]
+
+
+def kernel_work(c):
+  """Algorithmic work per launch of each kernel of the step: (bound, amount) in flops or bytes."""
+  T, d, E, f, k, fs = c["T"], c["d"], c["E"], c["f"], c["k"], c["fs"]
+  m = T * k
+  row = 2 * d
+  return {
+      "router_logits": ("hbm", T * row + T * E * 4 + d * E * 4),
+      "router_topk": ("hbm", T * E * 4 + m * 4 * 6),
+      "dispatch_gather": ("hbm", (T + m) * row),
+      "gemm_gateup_swiglu": ("tensor", 4 * m * d * f),
+      "gemm_down": ("tensor", 2 * m * d * f),
+      "shared_gateup_swiglu": ("tensor", 4 * T * d * fs),
+      "shared_down": ("tensor", 2 * T * d * fs),
+      "combine_gather_reduce": ("hbm", (m + 2 * T) * row),
+      "combine_bwd_gather_dot": ("hbm", (m + T) * row + 4 * m),
+      "combine_bwd_scaled_gather": ("hbm", (T + m) * row),
+      "gemm_dh_dswiglu": ("tensor", 2 * m * d * f),
+      "gemm_dw_down": ("tensor", 2 * m * d * f),
+      "gemm_dx": ("tensor", 4 * m * d * f),
+      "gemm_dw_gateup": ("tensor", 4 * m * d * f),
+      "shared_dh_dswiglu": ("tensor", 2 * T * d * fs),
+      "shared_dw_down": ("tensor", 2 * T * d * fs),
+      "shared_dx": ("tensor", 4 * T * d * fs),
+      "shared_dw_gateup": ("tensor", 4 * T * d * fs),
+      "router_topk_bwd": ("hbm", T * E * 4 + T * E * 2 + m * 8),
+      "router_dx": ("tensor", 2 * T * d * E),
+      "router_dw": ("tensor", 2 * T * d * E),
+      "dispatch_bwd_gather_reduce": ("hbm", (m + 4 * T) * row),
+  }
+
+
+def load_peaks():
+  p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+  try:
+    with open(p) as fh:
+      j = json.load(fh)
+    return dict(hbm_gbs=float(j["hbm_gbs"]), bf16_tflops=float(j["bf16_tflops"]),
+                bf16_tflops_sustained=float(j.get("bf16_tflops_sustained", j["bf16_tflops"]))), "measured"
+  except Exception:  # noqa: BLE001
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+class ClockSampler:
+  """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
+  Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+       "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+       "clocks_event_reasons.sw_power_cap")
+
+  def __init__(self, gpu_index):
+    self.gpu_index = gpu_index
+    self.proc = None
+    self.path = None
+
+  def start(self):
+    try:
+      fd, self.path = tempfile.mkstemp(suffix=".csv")
+      os.close(fd)
+      self.fh = open(self.path, "w")
+      self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.Q}",
+                                    "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.fh,
+                                   stderr=subprocess.DEVNULL)
+    except Exception:  # noqa: BLE001
+      self.proc = None
+
+  def stop(self):
+    out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
+    if self.proc is None:
+      return out
+    self.proc.terminate()
+    try:
+      self.proc.wait(timeout=5)
+    except Exception:  # noqa: BLE001
+      self.proc.kill()
+    self.fh.close()
+    sm, mx, reasons = [], [], set()
+    try:
+      for line in open(self.path):
+        p = [x.strip() for x in line.split(",")]
+        if len(p) < 9:
+          continue
+        try:
+          sm.append(float(p[1]))
+          mx.append(float(p[2]))
+        except ValueError:
+          continue
+        for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
+          if val.lower().startswith("active"):
+            reasons.add(name)
+      os.unlink(self.path)
+    except Exception:  # noqa: BLE001
+      pass
+    if sm:
+      out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+    return out
+
+
+def make_device_inputs(c, device, seed, torch):
+  """Seeded synthetic activations and random-init weights with the benchmark's shapes/distributions."""
+  g = torch.Generator(device=device).manual_seed(seed)
+  rn = lambda *s, std=1.0, dt=torch.bfloat16: (torch.randn(s, generator=g, device=device, dtype=torch.float32) * std).to(dt)
+  T, d, E, f, fs = c["T"], c["d"], c["E"], c["f"], c["fs"]
+  w = dict(w_router=rn(d, E, std=0.02, dt=torch.float32), w_gate=rn(E, d, f, std=0.02), w_up=rn(E, d, f, std=0.02),
+           w_down=rn(E, f, d, std=0.02), ws_gate=rn(d, fs, std=0.02), ws_up=rn(d, fs, std=0.02),
+           ws_down=rn(fs, d, std=0.02))
+  bias = None
+  if c["bias"]:
+    import numpy as np
+    rank = np.random.default_rng(seed + 1000).permutation(E) + 1
+    bias = torch.tensor(2.0 * np.log(1.0 / rank.astype(np.float64) ** 1.2), dtype=torch.float32, device=device)
+  return rn(T, d), rn(T, d), w, bias
+
+
+def cpu_oracle_step(c, sample_tokens, seed=0):
+  """Time one forward+backward of the CPU oracle on `sample_tokens` tokens of workload c."""
+  import numpy as np
+  import oracle as O
+  inp = O.make_inputs(sample_tokens, c["d"], c["E"], c["f"], c["fs"], seed)
+  args = [inp[n] for n in ("x", "w_router", "w_gate", "w_up", "w_down", "ws_gate", "ws_up", "ws_down")]
+  bias = O.zipf_bias(c["E"], seed) if c["bias"] else None
+
+  def step():
+    t0 = time.perf_counter()
+    out, cache = O.moe_layer_fwd(*args, c["k"], router_bias=bias)
+    O.moe_layer_bwd(inp["dout"], *args, c["k"], cache)
+    return time.perf_counter() - t0
+
+  return step
+
+
+def run_reference(args, c, rank, world):
+  """Reference arm: the CPU restatement of the reference's layer math on the host cores."""
+  if rank != 0:
+    return
+  import numpy as np  # noqa: F401
+  cores = os.cpu_count() or 1
+  sample = min(c["T"], 4096)
+  step = cpu_oracle_step(c, sample)
+  for _ in range(min(args.warmup, 1)):
+    step()
+  times = [step() for _ in range(args.steps)]
+  dt = sum(times) / len(times)
+  val = sample / dt
+  line = {
+      "impl": "reference", "metric": METRIC, "value": val, "unit": "tokens/s", "n_gpus": args.gpus, "steps": args.steps,
+      "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+      "config": workload_config(args, c, world),
+      "cpu_baseline": {"value": val, "unit": "tokens/s", "cores": cores, "kind": "port",
+                       "sample": f"{sample} tokens of the workload per step (NumPy float32 oracle of the reference math; "
+                                 "the reference's JAX layer cannot be installed here)"},
+      "e2e": {"value": val, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+  }
+  print(json.dumps(line), flush=True)
+
+
+def workload_config(args, c, world):
+  return {"workload": f"{args.config}: MoE layer fwd+bwd, T={c['T']} tokens per GPU, d={c['d']}, E={c['E']} experts x "
+                      f"SwiGLU ffn {c['f']}, top-{c['k']} + 1 shared expert (ffn {c['fs']}), padded block 128"
+                      + (", Zipf(1.2) router logit bias" if c["bias"] else ""),
+          "tokens_per_gpu": c["T"], "global_tokens": c["T"] * world,
+          "parallelism": "single GPU" if world == 1 else f"expert-parallel x{world} (all-to-all dispatch/combine)",
+          "l2": "inputs larger than L2 (weights 0.4 GB + activations > 2 GB per step)"}
+
+
+def main():
+  ap = argparse.ArgumentParser()
+  ap.add_argument("--gpus", type=int, default=1)
+  ap.add_argument("--steps", type=int, default=20)
+  ap.add_argument("--warmup", type=int, default=5)
+  ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+  ap.add_argument("--config", default=None, choices=sorted(CONFIGS))
+  ap.add_argument("--no-cpu-baseline", action="store_true")
+  args = ap.parse_args()
+  rank = int(os.environ.get("RANK", "0"))
+  world = int(os.environ.get("WORLD_SIZE", "1"))
+  local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+  if args.config is None:
+    args.config = "config2"
+  c = dict(CONFIGS[args.config])
+
+  if args.impl == "reference":
+    run_reference(args, c, rank, world)
+    return
+
+  import torch
+  import torch.distributed as dist
+  from lewi_surge_b200 import _lib, layer
+
+  if not torch.cuda.is_available():
+    raise SystemExit("bench.py needs a CUDA device: the kernels have no CPU path")
+  args.warmup = max(args.warmup, 3)
+  torch.cuda.set_device(local_rank)
+  device = torch.device("cuda", local_rank)
+  if world > 1:
+    dist.init_process_group("nccl", device_id=device)
+  lib = _lib.load()
+
+  x, dout, wd, bias = make_device_inputs(c, device, seed=rank, torch=torch)
+  w = layer.MoEWeights(router_bias=bias, **wd)
+  if world > 1:
+    from lewi_surge_b200 import ep
+    runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
+    step_fn = lambda: runner.step(x, dout)
+  else:
+    def step_fn():
+      out, cache = layer.moe_layer_fwd(x, w, c["k"])
+      return layer.moe_layer_bwd(dout, w, cache)
+
+  def barrier():
+    if world > 1:
+      dist.barrier()
+    torch.cuda.synchronize()
+
+  for _ in range(args.warmup):
+    step_fn()
+  barrier()
+
+  # ---- timed region: K steps, CUDA events on the launching stream, per-kernel events inside it
+  marks = []
+  def hook(name):
+    ev = torch.cuda.Event(enable_timing=True)
+    ev.record()
+    marks.append((name, ev))
+  sampler = ClockSampler(local_rank)
+  if rank == 0:
+    sampler.start()
+  layer.set_profile_hook(hook)
+  launches0 = lib.lewi_launch_count()
+  ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+  barrier()
+  ev0.record()
+  for _ in range(args.steps):
+    hook("step_begin")
+    step_fn()
+  ev1.record()
+  barrier()
+  launches = lib.lewi_launch_count() - launches0
+  layer.set_profile_hook(None)
+  clocks = sampler.stop() if rank == 0 else None
+  ms_total = ev0.elapsed_time(ev1)
+  tms = torch.tensor([ms_total], dtype=torch.float64, device=device)
+  if world > 1:
+    dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+  ms_step = float(tms.item()) / args.steps
+  status = _lib.last_status()
+  if status != 0:
+    raise SystemExit(f"device status {status} after the timed region (a bounded wait ran out or an index was bad)")
+
+  # per-kernel durations (averaged over steps)
+  per = {}
+  for (n0, e0), (n1, e1) in zip(marks[:-1], marks[1:]):
+    if n1 == "step_begin":
+      continue
+    per.setdefault(n1, []).append(e0.elapsed_time(e1))
+  kernels = {n: sum(v) / len(v) for n, v in per.items()}
+
+  # ---- end-to-end through the public API with host buffers (pinned), copies inside the timed region
+  e2e = None
+  if world == 1:
+    xh, gh = x.cpu().pin_memory(), dout.cpu().pin_memory()
+    oh, dxh = torch.empty_like(xh).pin_memory(), torch.empty_like(xh).pin_memory()
+    bufs = {}
+    for _ in range(3):
+      layer.moe_layer_step_host(xh, gh, w, c["k"], oh, dxh, bufs)
+    torch.cuda.synchronize()
+    n_e2e = max(3, min(args.steps, 10))
+    t0 = time.perf_counter()
+    for _ in range(n_e2e):
+      layer.moe_layer_step_host(xh, gh, w, c["k"], oh, dxh, bufs)
+      torch.cuda.synchronize()
+    dt = (time.perf_counter() - t0) / n_e2e
+    e2e = {"value": c["T"] / dt, "unit": "tokens/s", "h2d_bytes_per_step": xh.numel() * 2 + gh.numel() * 2,
+           "d2h_bytes_per_step": oh.numel() * 2 + dxh.numel() * 2, "ms_per_step": dt * 1e3,
+           "note": "x and upstream gradient copied in from pinned host memory, output and dx copied back, every step"}
+
+  if rank != 0:
+    if world > 1:
+      dist.destroy_process_group()
+    return
+
+  peaks, peak_kind = load_peaks()
+  work = kernel_work(c)
+  table = {}
+  for n, ms in kernels.items():
+    if n not in work:
+      continue
+    bound, amount = work[n]
+    if bound == "tensor":
+      ach = amount / (ms * 1e-3) / 1e12
+      table[n] = dict(ms=round(ms, 4), bound=bound, achieved=round(ach, 1), unit="TFLOP/s",
+                      frac=round(ach / peaks["bf16_tflops_sustained"], 4))
+    else:
+      ach = amount / (ms * 1e-3) / 1e9
+      table[n] = dict(ms=round(ms, 4), bound=bound, achieved=round(ach, 1), unit="GB/s",
+                      frac=round(ach / peaks["hbm_gbs"], 4))
+  dominant = max(kernels, key=lambda n: kernels[n] if n in work else -1)
+  dk = table[dominant]
+  roofline = {"kernel": dominant, "bound": dk["bound"], "achieved": dk["achieved"],
+              "peak": peaks["bf16_tflops_sustained"] if dk["bound"] == "tensor" else peaks["hbm_gbs"],
+              "unit": dk["unit"], "frac": dk["frac"], "traffic": KNOWN_TRAFFIC.get((args.config, dominant)),
+              "peak_source": f"{peak_kind} ({'sustained bf16 GEMM' if dk['bound'] == 'tensor' else 'copy bandwidth'}; "
+                             "kernel timed inside the step)",
+              "ms_per_launch": dk["ms"]}
+  gemm_ms = sum(ms for n, ms in kernels.items() if work.get(n, ("", 0))[0] == "tensor")
+  gemm_flops = sum(work[n][1] for n in kernels if work.get(n, ("", 0))[0] == "tensor")
+  mem_ms = sum(ms for n, ms in kernels.items() if n in ("dispatch_gather", "combine_gather_reduce",
+                                                         "combine_bwd_gather_dot", "combine_bwd_scaled_gather",
+                                                         "dispatch_bwd_gather_reduce"))
+  mem_bytes = sum(work[n][1] for n in ("dispatch_gather", "combine_gather_reduce", "combine_bwd_gather_dot",
+                                       "combine_bwd_scaled_gather", "dispatch_bwd_gather_reduce") if n in kernels)
+  summary = {
+      "layer_tflops": round(layer_flops(c) / (ms_step * 1e-3) / 1e12, 1),
+      "layer_frac_of_bf16_peak": round(layer_flops(c) / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], 4),
+      "grouped_gemm_tflops": round(gemm_flops / (gemm_ms * 1e-3) / 1e12, 1) if gemm_ms else None,
+      "grouped_gemm_frac_of_bf16_peak": round(gemm_flops / (gemm_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], 4) if gemm_ms else None,
+      "permute_combine_gbs": round(mem_bytes / (mem_ms * 1e-3) / 1e9, 1) if mem_ms else None,
+      "permute_combine_frac_of_hbm": round(mem_bytes / (mem_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4) if mem_ms else None,
+  }
+
+  cpu_baseline = None
+  if world == 1 and not args.no_cpu_baseline:
+    sample = min(c["T"], 4096)
+    step = cpu_oracle_step(c, sample)
+    step()
+    best = min(step() for _ in range(3))
+    cpu_baseline = {"value": sample / best, "unit": "tokens/s", "cores": os.cpu_count() or 1, "kind": "port",
+                    "sample": f"{sample} tokens of the workload, forward+backward, best of 3 (NumPy float32 oracle)"}
+
+  line = {
+      "metric": METRIC, "value": c["T"] * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
+      "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+      "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, c, world),
+      "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu_baseline,
+      "summary": summary, "kernels": table,
+  }
+  print(json.dumps(line), flush=True)
+  if world > 1:
+    dist.destroy_process_group()
+
+
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) taken from ncu captures
+# summarised under profiles/; keyed by (config, kernel).
+KNOWN_TRAFFIC = {}
+
+
+if __name__ == "__main__":
+  main()

@@ -44,6 +44,9 @@ extern "C" {
 int lewi_version(void);
 const char* lewi_error_string(int code);
 
+/* Number of kernels this library has launched in this process (host-side counter; not thread-safe). */
+int64_t lewi_launch_count(void);
+
 /* Reads (and clears) the status word of the current device.  Synchronises `stream`. */
 int lewi_last_status(void* stream);
 

@@ -20,6 +20,7 @@ P = c_void_p  # every device pointer crosses the boundary as an integer address
 SIGNATURES = {
     "lewi_version": (c_int, []),
     "lewi_error_string": (c_char_p, [c_int]),
+    "lewi_launch_count": (c_int64, []),
     "lewi_last_status": (c_int, [P]),
     "lewi_padded_rows_bound": (c_int64, [c_int64, c_int, c_int]),
     "lewi_route_workspace_bytes": (c_int64, [c_int64, c_int]),

@@ -77,12 +77,19 @@ inline int num_sms() {
   return cached[dev];
 }
 
+// Host-side count of kernel launches made through this library (read by lewi_launch_count()).
+inline long long& launch_counter() {
+  static long long n = 0;
+  return n;
+}
+
 #define LEWI_CHECK_LAUNCH()                                 \
   do {                                                      \
     if (cudaPeekAtLastError() != cudaSuccess) {             \
       (void)cudaGetLastError();                             \
       return LEWI_ERR_CUDA;                                 \
     }                                                       \
+    ++::lewi::launch_counter();                             \
   } while (0)
 
 }  // namespace lewi

@@ -28,6 +28,19 @@ from . import ops
 
 BLOCK = ops.BLOCK
 
+_HOOK = None
+
+
+def set_profile_hook(fn):
+  """fn(name) is called after every kernel launch of the layer (used to drop CUDA events); None disables."""
+  global _HOOK
+  _HOOK = fn
+
+
+def _mark(name):
+  if _HOOK is not None:
+    _HOOK(name)
+
 
 @dataclass
 class MoEWeights:
@@ -166,17 +179,25 @@ def moe_layer_fwd(x, w: MoEWeights, k, logits=None):
   t, d = x.shape
   if logits is None:
     logits = router_logits(x, w.w_router, w.router_bias)
+    _mark("router_logits")
   tb = router_topk(logits, k)
+  _mark("router_topk")
   # dispatch: padded row r holds token row_slot[r] // k (zero row where row_slot[r] < 0)
   xs = torch.empty((tb.mpad, d), dtype=x.dtype, device=x.device)
   ops.gather_rows(x, tb.row_slot, idx_div=k, out=xs, n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
+  _mark("dispatch_gather")
   gu, h = gateup_swiglu(xs, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks)
+  _mark("gemm_gateup_swiglu")
   ys = ops.grouped_gemm_nn(h, w.w_down, tb.block_expert, tb.n_blocks)
+  _mark("gemm_down")
   gus = hs = ysh = None
   if w.ws_gate is not None:
     gus, hs = gateup_swiglu(x, w.ws_gate[None], w.ws_up[None], None, None)
+    _mark("shared_gateup_swiglu")
     ysh = ops.grouped_gemm_nn(hs, w.ws_down[None], None, None)
+    _mark("shared_down")
   out = ops.gather_reduce(ys, tb.pad_pos.view(t, k), tb.topk_w, x.dtype, add0=ysh)
+  _mark("combine_gather_reduce")
   return out, LayerCache(x=x, logits=logits, tables=tb, xs=xs, gu=gu, h=h, ys=ys, gus=gus, hs=hs, k=k)
 
 
@@ -189,31 +210,67 @@ def moe_layer_bwd(dout, w: MoEWeights, c: LayerCache):
   pad_pos = tb.pad_pos.view(t, k)
   # combine backward: dw = <g, y>, dy = w * g (scaled gather into padded order)
   dw = ops.gather_dot(c.ys, pad_pos, dout)
+  _mark("combine_bwd_gather_dot")
   dys = torch.empty_like(c.ys)
   ops.gather_rows(dout, tb.row_slot, tb.topk_w.view(-1), idx_div=k, scale_by_idx=True, out=dys,
                   n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
+  _mark("combine_bwd_scaled_gather")
   # experts backward
   dgu = dh_dswiglu(dys, w.w_down, c.gu, tb.block_expert, tb.n_blocks)
+  _mark("gemm_dh_dswiglu")
   dw_down = ops.grouped_gemm_tn(c.h, dys, tb.pad_offsets, e, out_dtype=w.w_down.dtype)
+  _mark("gemm_dw_down")
   dxs = dx_from_dgu(dgu, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks)
+  _mark("gemm_dx")
   dw_gate, dw_up = ops.grouped_gemm_tn(c.xs, dgu, tb.pad_offsets, e, out_dtype=w.w_gate.dtype, split=True)
+  _mark("gemm_dw_gateup")
   grads = dict(dw_gate=dw_gate, dw_up=dw_up, dw_down=dw_down, dw=dw)
   # shared expert backward
   dxsh = None
   if w.ws_gate is not None:
     dgus = dh_dswiglu(dout, w.ws_down[None], c.gus, None, None)
+    _mark("shared_dh_dswiglu")
     dws_down = ops.grouped_gemm_tn(c.hs, dout, None, 1, out_dtype=w.ws_down.dtype)[0]
+    _mark("shared_dw_down")
     dxsh = dx_from_dgu(dgus, w.ws_gate[None], w.ws_up[None], None, None)
+    _mark("shared_dx")
     dws_gate, dws_up = ops.grouped_gemm_tn(x, dgus, None, 1, out_dtype=w.ws_gate.dtype, split=True)
+    _mark("shared_dw_gateup")
     grads.update(dws_gate=dws_gate[0], dws_up=dws_up[0], dws_down=dws_down)
   # router backward
   _, dlb = router_topk_bwd(c.logits, tb.topk_idx, dw, want_f32=False, want_bf16=True)
+  _mark("router_topk_bwd")
   w_r_bf16 = cast_bf16(w.w_router)                                  # [d,E] = K-major operand over E
   dx_r = ops.grouped_gemm_nt(dlb, w_r_bf16[None], None, None)        # [T,d] = dlogits . W_r^T
+  _mark("router_dx")
   dw_router = ops.grouped_gemm_tn(x, dlb, None, 1, out_dtype=torch.float32)[0]   # [d,E] = x^T . dlogits
+  _mark("router_dw")
   grads.update(dw_router=dw_router, dlogits_bf16=dlb)
   # dispatch backward: dx[t] = sum_j dxs[row(t,j)] (+ shared-expert and router terms)
   grads["dx"] = ops.gather_reduce(dxs, pad_pos, None, x.dtype, add0=dxsh, add1=dx_r)
+  _mark("dispatch_bwd_gather_reduce")
+  return grads
+
+
+def moe_layer_step_host(x_host, dout_host, w: MoEWeights, k, out_host, dx_host, bufs=None):
+  """One forward+backward with HOST activations: copies x and the upstream gradient in from (pinned)
+  host memory, runs the layer, copies the output and dx back.  Weight gradients stay on the device
+  (they feed the optimizer there).  Returns the gradient dict; the copies are asynchronous on the
+  current stream, so synchronise before reading the host buffers."""
+  dev = w.w_gate.device
+  if bufs is None:
+    bufs = {}
+  xd = bufs.get("x")
+  if xd is None or xd.shape != x_host.shape:
+    xd = bufs["x"] = torch.empty(x_host.shape, dtype=x_host.dtype, device=dev)
+    bufs["dout"] = torch.empty(dout_host.shape, dtype=dout_host.dtype, device=dev)
+  gd = bufs["dout"]
+  xd.copy_(x_host, non_blocking=True)
+  gd.copy_(dout_host, non_blocking=True)
+  out, cache = moe_layer_fwd(xd, w, k)
+  grads = moe_layer_bwd(gd, w, cache)
+  out_host.copy_(out, non_blocking=True)
+  dx_host.copy_(grads["dx"], non_blocking=True)
   return grads
 
 

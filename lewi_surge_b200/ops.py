@@ -64,6 +64,8 @@ def gather_rows(x, idx, scale=None, *, idx_div=1, scale_by_idx=False, out=None, 
     out = torch.empty((m, d), dtype=x.dtype, device=x.device)
   if scale is not None:
     scale = scale.to(torch.float32).contiguous()
+  if m == 0:
+    return out
   check(lib.lewi_gather_rows(stream(), ptr(x), ptr(idx), ptr(scale), ptr(out), x.shape[0], m, d, _dt(x),
                              int(idx_div), int(bool(scale_by_idx)), ptr(n_rows_dev), int(rows_per_unit)),
         "lewi_gather_rows")
@@ -88,6 +90,8 @@ def gather_reduce(y, pos, w=None, out_dtype=None, *, add0=None, add1=None, out=N
   for a in (add0, add1):
     if a is not None and a.dtype != y.dtype:
       raise LewiError("addends must have the dtype of y")
+  if n == 0:
+    return out
   check(lib.lewi_gather_reduce(stream(), ptr(y), ptr(pos), ptr(w), ptr(add0), ptr(add1), ptr(out), n, k, d, _dt(y),
                                _dt(out), y.shape[0]), "lewi_gather_reduce")
   return out
@@ -104,6 +108,8 @@ def gather_dot(y, pos, g):
   g = g.to(y.dtype).contiguous()
   n, k = pos.shape
   out = torch.empty((n, k), dtype=torch.float32, device=y.device)
+  if n == 0:
+    return out
   check(lib.lewi_gather_dot(stream(), ptr(y), ptr(pos), ptr(g), ptr(out), n, k, y.shape[1], _dt(y), y.shape[0]),
         "lewi_gather_dot")
   return out
@@ -124,6 +130,8 @@ def sort_indices(flat_experts, num_experts=None, method=None):
   m = flat.shape[0]
   order = torch.empty(m, dtype=torch.int32, device=flat.device)
   pos = torch.empty(m, dtype=torch.int32, device=flat.device)
+  if m == 0:
+    return order, pos
   ws = route_workspace(m, num_experts, flat.device)
   check(lib.lewi_sort_indices(stream(), ptr(flat), m, int(num_experts), 0, ptr(order), ptr(pos), None, None, None,
                               None, None, None, None, ptr(ws), ws.numel()), "lewi_sort_indices")
