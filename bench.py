@@ -13,9 +13,7 @@ import argparse
 import json
 import os
 import statistics
-import subprocess
 import sys
-import tempfile
 import time
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -82,66 +80,68 @@ def load_peaks():
 
 
 class ClockSampler:
-  """nvidia-smi clock / throttle-reason samples taken while the timed region runs."""
-  Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
-       "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
-       "clocks_event_reasons.sw_power_cap")
+  """SM clock and throttle-reason samples taken through NVML (read-only) while the timed region runs."""
 
-  def __init__(self, gpu_index):
-    self.gpu_index = gpu_index
-    self.proc = None
-    self.path = None
+  def __init__(self, gpu_index, period_s=0.005):
+    self.gpu_index, self.period = gpu_index, period_s
+    self.samples, self.reasons, self.max_mhz = [], set(), None
+    self._stop = False
+    self._thread = None
+
+  def _run(self):
+    try:
+      import pynvml as nv
+      nv.nvmlInit()
+      vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+      idx = self.gpu_index
+      if vis:
+        try:
+          idx = int(vis.split(",")[self.gpu_index])
+        except (ValueError, IndexError):
+          idx = self.gpu_index
+      h = nv.nvmlDeviceGetHandleByIndex(idx)
+      self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+      names = {
+          getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+          getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+          getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+          getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+      }
+      get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+      while not self._stop:
+        self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+        r = int(get_reasons(h))
+        for bit, name in names.items():
+          if r & bit:
+            self.reasons.add(name)
+        time.sleep(self.period)
+    except Exception:  # noqa: BLE001  (no NVML: the line reports no samples)
+      pass
 
   def start(self):
-    try:
-      fd, self.path = tempfile.mkstemp(suffix=".csv")
-      os.close(fd)
-      self.fh = open(self.path, "w")
-      self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.gpu_index}", f"--query-gpu={self.Q}",
-                                    "--format=csv,noheader,nounits", "-lms", "100"], stdout=self.fh,
-                                   stderr=subprocess.DEVNULL)
-    except Exception:  # noqa: BLE001
-      self.proc = None
+    import threading
+    self._thread = threading.Thread(target=self._run, daemon=True)
+    self._thread.start()
 
   def stop(self):
-    out = dict(sm_mhz=None, sm_max_mhz=None, reasons=[], samples=0)
-    if self.proc is None:
-      return out
-    self.proc.terminate()
-    try:
-      self.proc.wait(timeout=5)
-    except Exception:  # noqa: BLE001
-      self.proc.kill()
-    self.fh.close()
-    sm, mx, reasons = [], [], set()
-    try:
-      for line in open(self.path):
-        p = [x.strip() for x in line.split(",")]
-        if len(p) < 9:
-          continue
-        try:
-          sm.append(float(p[1]))
-          mx.append(float(p[2]))
-        except ValueError:
-          continue
-        for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), p[5:9]):
-          if val.lower().startswith("active"):
-            reasons.add(name)
-      os.unlink(self.path)
-    except Exception:  # noqa: BLE001
-      pass
-    if sm:
-      out.update(sm_mhz=statistics.median(sm), sm_max_mhz=max(mx), reasons=sorted(reasons), samples=len(sm))
+    self._stop = True
+    if self._thread is not None:
+      self._thread.join(timeout=2)
+    out = dict(sm_mhz=None, sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons), samples=len(self.samples))
+    if self.samples:
+      out["sm_mhz"] = statistics.median(self.samples)
     return out
 
 
-def make_device_inputs(c, device, seed, torch):
-  """Seeded synthetic activations and random-init weights with the benchmark's shapes/distributions."""
+def make_device_inputs(c, device, seed, torch, world=1):
+  """Seeded synthetic activations and random-init weights with the benchmark's shapes/distributions.
+  With world > 1 only this rank's E/world experts are created (expert parallelism)."""
   g = torch.Generator(device=device).manual_seed(seed)
   rn = lambda *s, std=1.0, dt=torch.bfloat16: (torch.randn(s, generator=g, device=device, dtype=torch.float32) * std).to(dt)
   T, d, E, f, fs = c["T"], c["d"], c["E"], c["f"], c["fs"]
-  w = dict(w_router=rn(d, E, std=0.02, dt=torch.float32), w_gate=rn(E, d, f, std=0.02), w_up=rn(E, d, f, std=0.02),
-           w_down=rn(E, f, d, std=0.02), ws_gate=rn(d, fs, std=0.02), ws_up=rn(d, fs, std=0.02),
+  el = E // world
+  w = dict(w_router=rn(d, E, std=0.02, dt=torch.float32), w_gate=rn(el, d, f, std=0.02), w_up=rn(el, d, f, std=0.02),
+           w_down=rn(el, f, d, std=0.02), ws_gate=rn(d, fs, std=0.02), ws_up=rn(d, fs, std=0.02),
            ws_down=rn(fs, d, std=0.02))
   bias = None
   if c["bias"]:
@@ -206,11 +206,13 @@ def workload_config(args, c, world):
 def main():
   ap = argparse.ArgumentParser()
   ap.add_argument("--gpus", type=int, default=1)
-  ap.add_argument("--steps", type=int, default=20)
+  ap.add_argument("--steps", type=int, default=100)
   ap.add_argument("--warmup", type=int, default=5)
   ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
   ap.add_argument("--config", default=None, choices=sorted(CONFIGS))
   ap.add_argument("--no-cpu-baseline", action="store_true")
+  ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+  ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling a smaller case)")
   args = ap.parse_args()
   rank = int(os.environ.get("RANK", "0"))
   world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -218,6 +220,8 @@ def main():
   if args.config is None:
     args.config = "config2"
   c = dict(CONFIGS[args.config])
+  if args.tokens:
+    c["T"] = args.tokens
 
   if args.impl == "reference":
     run_reference(args, c, rank, world)
@@ -236,7 +240,7 @@ def main():
     dist.init_process_group("nccl", device_id=device)
   lib = _lib.load()
 
-  x, dout, wd, bias = make_device_inputs(c, device, seed=rank, torch=torch)
+  x, dout, wd, bias = make_device_inputs(c, device, seed=rank, torch=torch, world=world)
   w = layer.MoEWeights(router_bias=bias, **wd)
   if world > 1:
     from lewi_surge_b200 import ep
@@ -297,7 +301,7 @@ def main():
 
   # ---- end-to-end through the public API with host buffers (pinned), copies inside the timed region
   e2e = None
-  if world == 1:
+  if world == 1 and not args.no_e2e:
     xh, gh = x.cpu().pin_memory(), dout.cpu().pin_memory()
     oh, dxh = torch.empty_like(xh).pin_memory(), torch.empty_like(xh).pin_memory()
     bufs = {}
@@ -334,14 +338,16 @@ def main():
       ach = amount / (ms * 1e-3) / 1e9
       table[n] = dict(ms=round(ms, 4), bound=bound, achieved=round(ach, 1), unit="GB/s",
                       frac=round(ach / peaks["hbm_gbs"], 4))
-  dominant = max(kernels, key=lambda n: kernels[n] if n in work else -1)
-  dk = table[dominant]
-  roofline = {"kernel": dominant, "bound": dk["bound"], "achieved": dk["achieved"],
-              "peak": peaks["bf16_tflops_sustained"] if dk["bound"] == "tensor" else peaks["hbm_gbs"],
-              "unit": dk["unit"], "frac": dk["frac"], "traffic": KNOWN_TRAFFIC.get((args.config, dominant)),
-              "peak_source": f"{peak_kind} ({'sustained bf16 GEMM' if dk['bound'] == 'tensor' else 'copy bandwidth'}; "
-                             "kernel timed inside the step)",
-              "ms_per_launch": dk["ms"]}
+  roofline = None
+  dominant = max(table, key=lambda n: kernels[n]) if table else None
+  dk = table.get(dominant)
+  if dk is not None:
+    roofline = {"kernel": dominant, "bound": dk["bound"], "achieved": dk["achieved"],
+                "peak": peaks["bf16_tflops_sustained"] if dk["bound"] == "tensor" else peaks["hbm_gbs"],
+                "unit": dk["unit"], "frac": dk["frac"], "traffic": KNOWN_TRAFFIC.get((args.config, dominant)),
+                "peak_source": f"{peak_kind} ({'sustained bf16 GEMM' if dk['bound'] == 'tensor' else 'copy bandwidth'}; "
+                               "kernel timed inside the step)",
+                "ms_per_launch": dk["ms"]}
   gemm_ms = sum(ms for n, ms in kernels.items() if work.get(n, ("", 0))[0] == "tensor")
   gemm_flops = sum(work[n][1] for n in kernels if work.get(n, ("", 0))[0] == "tensor")
   mem_ms = sum(ms for n, ms in kernels.items() if n in ("dispatch_gather", "combine_gather_reduce",

@@ -62,9 +62,15 @@ int64_t lewi_route_workspace_bytes(int64_t num_slots, int num_experts);
  * modal/moe_permute.py:240-264 and the padded-block table, in one call.
  * ---------------------------------------------------------------------------------------------- */
 
-/* logits[T,E] (f32) = x[T,d] (bf16) . w_router[d,E] (f32) (+ bias[E] if not null), f32 accumulate. */
+/* logits[T,E] (f32) = x[T,d] (bf16) . w_router[d,E] (f32) (+ bias[E] if not null), f32 accumulate.
+ * With a workspace of lewi_router_logits_workspace_bytes(d,E) bytes (and d, E multiples of 64) the
+ * product runs on the tensor cores without losing float32 precision: the weight is split into
+ * three bf16 pieces whose sum is the f32 value, and every bf16 x bf16 product is exact in f32.
+ * Without a workspace a CUDA-core float32 kernel is used. */
+int64_t lewi_router_logits_workspace_bytes(int d, int E);
 int lewi_router_logits(void* stream, const void* x, const float* w_router, const float* bias,
-                       float* logits, int64_t T, int d, int E);
+                       float* logits, int64_t T, int d, int E, void* workspace,
+                       int64_t workspace_bytes);
 
 /* Fused softmax + top-k + renormalise + stable counting sort + block table.
  *   logits   f32 [T,E]
@@ -156,10 +162,17 @@ int lewi_grouped_gemm_nt(void* stream, const void* a, const void* b, void* out, 
 /* out[e] = a[rows of e]^T . b[rows of e]   a [rows,Ma], b [rows,Nb], out [E,Ma,Nb] (out_dtype).
  * pad_offsets i32 [E+1] gives each expert's padded row range (null: one group of all rows).
  * Experts without rows get zeros.  If out2 is not null, columns >= Nb/2 of the product go to
- * out2 [E,Ma,Nb/2] and out is [E,Ma,Nb/2] (used for dW_gate | dW_up from one pass). */
+ * out2 [E,Ma,Nb/2] and out is [E,Ma,Nb/2] (used for dW_gate | dW_up from one pass).
+ * workspace: optional scratch, see lewi_grouped_gemm_tn_workspace_bytes(). */
 int lewi_grouped_gemm_tn(void* stream, const void* a, const void* b, void* out, void* out2,
                          const int32_t* pad_offsets, int64_t rows, int Ma, int Nb, int E,
-                         int out_dtype);
+                         int out_dtype, void* workspace, int64_t workspace_bytes);
+
+/* Scratch that lets lewi_grouped_gemm_tn cut the contraction into parts when there are too few
+ * output tiles to fill the GPU (one group, long contraction: the shared expert's and the router's
+ * weight gradients).  Partial products are summed in a fixed order, so results are reproducible.
+ * 0 means no split is wanted; the workspace argument may always be null. */
+int64_t lewi_grouped_gemm_tn_workspace_bytes(int64_t rows, int Ma, int Nb, int E, int split_out);
 
 /* Fused gate/up projection + SwiGLU:  g = xs.Wg[e], u = xs.Wu[e], h = silu(g)*u.
  * xs [rows,d], w_gate/w_up [E,d,f], gu [rows,2f] (g | u, bf16, may be null), h [rows,f] bf16. */

@@ -24,7 +24,8 @@ SIGNATURES = {
     "lewi_last_status": (c_int, [P]),
     "lewi_padded_rows_bound": (c_int64, [c_int64, c_int, c_int]),
     "lewi_route_workspace_bytes": (c_int64, [c_int64, c_int]),
-    "lewi_router_logits": (c_int, [P, P, P, P, P, c_int64, c_int, c_int]),
+    "lewi_router_logits_workspace_bytes": (c_int64, [c_int, c_int]),
+    "lewi_router_logits": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, P, c_int64]),
     "lewi_router_topk": (c_int, [P, P, c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P, P, P, c_int64]),
     "lewi_sort_indices": (c_int, [P, P, c_int64, c_int, c_int, P, P, P, P, P, P, P, P, P, P, c_int64]),
     "lewi_router_topk_bwd": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int]),
@@ -35,7 +36,8 @@ SIGNATURES = {
     "lewi_gather_dot": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int64]),
     "lewi_grouped_gemm_nn": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int]),
     "lewi_grouped_gemm_nt": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int]),
-    "lewi_grouped_gemm_tn": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int]),
+    "lewi_grouped_gemm_tn": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, P, c_int64]),
+    "lewi_grouped_gemm_tn_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int]),
     "lewi_grouped_gemm_gateup_swiglu": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dh_dswiglu": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dx": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),

@@ -501,6 +501,21 @@ __global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* __restr
     dst[i] = __float2bfloat16_rn(src[i]);
 }
 
+// f32 -> three bf16 pieces with hi + mid + lo == w to 24 mantissa bits; dst is [3][n].
+__global__ void __launch_bounds__(256) split3_bf16_kernel(const float* __restrict__ src,
+                                                          __nv_bfloat16* __restrict__ dst, long long n) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    const float w = src[i];
+    const __nv_bfloat16 hi = __float2bfloat16_rn(w);
+    const float r1 = w - __bfloat162float(hi);
+    const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
+    const float r2 = r1 - __bfloat162float(mid);
+    dst[i] = hi;
+    dst[n + i] = mid;
+    dst[2 * n + i] = __float2bfloat16_rn(r2);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host
 
 inline int route_n_chunks(long long num_slots, int chunk_slots) {

@@ -76,12 +76,14 @@ class RouteTables:
   mpad: int
 
 
-def router_logits(x, w_router, bias=None):
+def router_logits(x, w_router, bias=None, tensor_cores=True):
   lib = _lib.load()
   t, d = x.shape
   e = w_router.shape[1]
   logits = torch.empty((t, e), dtype=torch.float32, device=x.device)
-  check(lib.lewi_router_logits(stream(), ptr(x), ptr(w_router), ptr(bias), ptr(logits), t, d, e),
+  ws_bytes = int(lib.lewi_router_logits_workspace_bytes(d, e)) if tensor_cores else 0
+  ws = torch.empty(ws_bytes, dtype=torch.uint8, device=x.device) if ws_bytes > 0 else None
+  check(lib.lewi_router_logits(stream(), ptr(x), ptr(w_router), ptr(bias), ptr(logits), t, d, e, ptr(ws), ws_bytes),
         "lewi_router_logits")
   return logits
 

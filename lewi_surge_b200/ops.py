@@ -277,8 +277,10 @@ def grouped_gemm_tn(a, b, pad_offsets, num_experts, out_dtype=torch.bfloat16, ou
       out2 = torch.empty((num_experts, ma, nb // 2), dtype=out_dtype, device=a.device)
   elif out is None:
     out = torch.empty((num_experts, ma, nb), dtype=out_dtype, device=a.device)
+  ws_bytes = int(lib.lewi_grouped_gemm_tn_workspace_bytes(rows, ma, nb, int(num_experts), int(bool(split))))
+  ws = torch.empty(ws_bytes, dtype=torch.uint8, device=a.device) if ws_bytes > 0 else None
   check(lib.lewi_grouped_gemm_tn(stream(), ptr(a), ptr(b), ptr(out), ptr(out2), ptr(pad_offsets), rows, ma, nb,
-                                 int(num_experts), _dt(out)), "lewi_grouped_gemm_tn")
+                                 int(num_experts), _dt(out), ptr(ws), ws_bytes), "lewi_grouped_gemm_tn")
   return (out, out2) if split else out
 
 

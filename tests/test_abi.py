@@ -55,6 +55,7 @@ def test_argument_rejection_without_gpu(lib):
   assert lib.lewi_router_topk(None, None, 4, 8, 2, 128, None, None, None, None, None, None, None, None, None, None,
                               None, None, None, 0) == -1
   assert lib.lewi_grouped_gemm_nn(None, None, None, None, None, None, None, 128, 64, 64, 1, 0) == -1
+  assert lib.lewi_grouped_gemm_tn(None, None, None, None, None, None, 128, 64, 64, 1, 0, None, 0) == -1
   assert lib.lewi_grouped_gemm_nn(None, 16, 16, 16, None, None, None, 128, 60, 64, 1, 0) == -2  # K % 64
 
 

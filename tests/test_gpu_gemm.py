@@ -36,6 +36,7 @@ def expected_nn(a, b, pad):
 
 CASES = [
     ([128], 64, 64),
+    ([70, 3], 96, 40),                         # extents that are multiples of 8 but not of the tile sizes
     ([128, 128], 128, 256),
     ([5, 0, 9, 3, 7, 1, 6, 4], 64, 64),        # group sizes of modal/te_run.py:72 (an empty group)
     ([300, 0, 17, 128, 129], 256, 320),
@@ -164,6 +165,29 @@ def test_single_group_with_ragged_row_count(cuda):
   assert O.rel_err(to_np(dw)[0], x.T @ gy) <= 1e-4
 
 
+@pytest.mark.parametrize("t,ma,nb,split", [(4096, 128, 128, False), (5000, 256, 512, True), (32768, 512, 1024, False)])
+def test_single_group_long_contraction_is_split(cuda, t, ma, nb, split):
+  """One group with many rows: the contraction is cut into parts and summed in a fixed order."""
+  from lewi_surge_b200 import ops, _lib
+  assert _lib.load().lewi_grouped_gemm_tn_workspace_bytes(t, ma, nb, 1, int(split)) > 0
+  rng = np.random.default_rng(t)
+  a = O.bf16_round(rng.standard_normal((t, ma)))
+  b = O.bf16_round(rng.standard_normal((t, nb)))
+  A, B = to_dev(a, torch.bfloat16, cuda), to_dev(b, torch.bfloat16, cuda)
+  want = a.T @ b
+  if split:
+    o1, o2 = ops.grouped_gemm_tn(A, B, None, 1, out_dtype=torch.float32, split=True)
+    got = np.concatenate([to_np(o1)[0], to_np(o2)[0]], axis=1)
+    again = ops.grouped_gemm_tn(A, B, None, 1, out_dtype=torch.float32, split=True)
+    assert torch.equal(again[0], o1) and torch.equal(again[1], o2)
+  else:
+    got = to_np(ops.grouped_gemm_tn(A, B, None, 1, out_dtype=torch.float32))[0]
+  assert O.rel_err(got, want) <= 1e-4
+  got16 = ops.grouped_gemm_tn(A, B, None, 1, out_dtype=torch.bfloat16, split=split)
+  got16 = np.concatenate([to_np(g)[0] for g in got16], axis=1) if split else to_np(got16)[0]
+  assert O.rel_err(got16, want) <= TOL
+
+
 def test_ragged_dot_drop_in_known_answer(cuda):
   """The reference's own check of ragged_dot semantics (modal/te_run.py:68-80): forward, dlhs, drhs on
   out[:S] with group sizes [5,0,9,3,7,1,6,4] and three tail rows outside every group."""
@@ -190,8 +214,8 @@ def test_ragged_dot_drop_in_known_answer(cuda):
 
 def test_gemm_argument_checks(cuda):
   from lewi_surge_b200 import ops, _lib
-  a = torch.zeros(128, 96, dtype=torch.bfloat16, device=cuda)     # K = 96 is not a multiple of 64
-  b = torch.zeros(1, 96, 64, dtype=torch.bfloat16, device=cuda)
+  a = torch.zeros(128, 100, dtype=torch.bfloat16, device=cuda)    # K = 100 is not a multiple of 8
+  b = torch.zeros(1, 100, 64, dtype=torch.bfloat16, device=cuda)
   with pytest.raises(_lib.LewiError):
     ops.grouped_gemm_nn(a, b, None, None)
 
