@@ -36,6 +36,7 @@ extern "C" {
 #define LEWI_ERR_WORKSPACE (-3) /* workspace too small                                           */
 #define LEWI_ERR_CUDA (-4)      /* a CUDA runtime / driver call failed at launch                 */
 #define LEWI_ERR_LIMIT (-5)     /* size beyond a compiled-in maximum                             */
+#define LEWI_ERR_STATIC_SCRATCH (-6) /* problem does not fit the built-in scratch (static variant) */
 
 /* device status bits (lewi_last_status) */
 #define LEWI_STATUS_WAIT_TIMEOUT 1 /* a bounded device-side wait ran out */
@@ -88,6 +89,30 @@ int lewi_router_topk(void* stream, const float* logits, int64_t T, int E, int k,
                      int32_t* pad_offsets, int32_t* block_expert, int32_t* n_blocks, int32_t* order,
                      int32_t* pos, int32_t* pad_pos, int32_t* row_slot, float* probs_sum,
                      void* workspace, int64_t workspace_bytes);
+
+/* lewi_router_topk without a workspace argument.  It has no counterpart in the reference: it exists
+ * for callers that are not allowed to allocate device memory and have no scratch buffer to hand in --
+ * for example a custom-call handler running under a compiled XLA program, where every buffer was
+ * planned when the program was compiled, or a host runtime with a fixed memory budget that forbids
+ * cudaMalloc on its serving path.  The scratch is a fixed array inside the library image
+ * (lewi_router_topk_static_max_bytes() bytes, currently 4 MiB, resident on every GPU that loads the
+ * library until the process exits).  Inputs, outputs and semantics are exactly those of
+ * lewi_router_topk.
+ *   - The problem must satisfy lewi_route_workspace_bytes(T*k, E) <= lewi_router_topk_static_max_bytes();
+ *     otherwise LEWI_ERR_STATIC_SCRATCH is returned and nothing is launched.
+ *   - The first call on each device looks up the array's device address (a host-side CUDA runtime
+ *     query, made with that device current).  Make that first call outside any stream capture.
+ *   - The call itself allocates nothing: no cudaMalloc/cudaFree, no allocating library routine.
+ *   - All calls on one device share the one array and it keeps the previous call's contents; every
+ *     word that is read is written first within the same call, so nothing needs clearing.  Two calls
+ *     whose kernels overlap on the GPU (different streams, or different host threads) race on it:
+ *     issue them on one stream or serialise them yourself. */
+int64_t lewi_router_topk_static_max_bytes(void);
+int lewi_router_topk_static(void* stream, const float* logits, int64_t T, int E, int k, int block,
+                            int32_t* topk_idx, float* topk_w, int32_t* counts, int32_t* offsets,
+                            int32_t* pad_offsets, int32_t* block_expert, int32_t* n_blocks,
+                            int32_t* order, int32_t* pos, int32_t* pad_pos, int32_t* row_slot,
+                            float* probs_sum);
 
 /* sort_indices(flat_experts, num_experts, method) of modal/moe_permute.py:240-264 (both methods give
  * the same result; this is the counting sort).  Padded-layout outputs may be null (block <= 0 too). */

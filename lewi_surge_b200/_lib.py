@@ -27,6 +27,8 @@ SIGNATURES = {
     "lewi_router_logits_workspace_bytes": (c_int64, [c_int, c_int]),
     "lewi_router_logits": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, P, c_int64]),
     "lewi_router_topk": (c_int, [P, P, c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P, P, P, c_int64]),
+    "lewi_router_topk_static_max_bytes": (c_int64, []),
+    "lewi_router_topk_static": (c_int, [P, P, c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P, P]),
     "lewi_sort_indices": (c_int, [P, P, c_int64, c_int, c_int, P, P, P, P, P, P, P, P, P, P, c_int64]),
     "lewi_router_topk_bwd": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int]),
     "lewi_cast_f32_to_bf16": (c_int, [P, P, P, c_int64]),
