@@ -213,6 +213,7 @@ def main():
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
   ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling a smaller case)")
+  ap.add_argument("--single-cta", action="store_true", help="A/B switch: force the cta_group::1 GEMM kernels")
   args = ap.parse_args()
   rank = int(os.environ.get("RANK", "0"))
   world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -239,6 +240,8 @@ def main():
   if world > 1:
     dist.init_process_group("nccl", device_id=device)
   lib = _lib.load()
+  if args.single_cta:
+    lib.lewi_debug_set_cta_pair(0)
 
   x, dout, wd, bias = make_device_inputs(c, device, seed=rank, torch=torch, world=world)
   w = layer.MoEWeights(router_bias=bias, **wd)

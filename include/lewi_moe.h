@@ -171,18 +171,21 @@ int lewi_gather_dot(void* stream, const void* y, const int32_t* pos, const void*
  * modal/stage2.py:338-341).  `a` has `rows` rows; row block b (128 rows) belongs to expert
  * block_expert[b]; only the first *n_blocks blocks are processed.  block_expert == null means a
  * single group (expert 0) of `rows` rows (the shared expert); then n_blocks may be null too.
- * K and N extents must be multiples of 64; all operands bf16.
+ * pad_offsets i32 [E+1] (the padded row range of every expert, as the router call produces it) lets
+ * the library run CTA pairs (tcgen05 cta_group::2: two SMs share one 256-row tile and each loads half
+ * of the weight tile); when it is null but block_expert is given, single-CTA kernels are used.
+ * K and N extents must be multiples of 8; all operands bf16.
  * ---------------------------------------------------------------------------------------------- */
 
 /* out[r, :] = a[r, :] . b[e]      a [rows,K], b [E,K,N], out [rows,N] (out_dtype), optional f32 row_scale[rows]. */
 int lewi_grouped_gemm_nn(void* stream, const void* a, const void* b, void* out, const float* row_scale,
-                         const int32_t* block_expert, const int32_t* n_blocks, int64_t rows, int K,
-                         int N, int E, int out_dtype);
+                         const int32_t* block_expert, const int32_t* n_blocks,
+                         const int32_t* pad_offsets, int64_t rows, int K, int N, int E, int out_dtype);
 
 /* out[r, :] = a[r, :] . b[e]^T    a [rows,K], b [E,N,K], out [rows,N]. */
 int lewi_grouped_gemm_nt(void* stream, const void* a, const void* b, void* out, const float* row_scale,
-                         const int32_t* block_expert, const int32_t* n_blocks, int64_t rows, int K,
-                         int N, int E, int out_dtype);
+                         const int32_t* block_expert, const int32_t* n_blocks,
+                         const int32_t* pad_offsets, int64_t rows, int K, int N, int E, int out_dtype);
 
 /* out[e] = a[rows of e]^T . b[rows of e]   a [rows,Ma], b [rows,Nb], out [E,Ma,Nb] (out_dtype).
  * pad_offsets i32 [E+1] gives each expert's padded row range (null: one group of all rows).
@@ -204,23 +207,26 @@ int64_t lewi_grouped_gemm_tn_workspace_bytes(int64_t rows, int Ma, int Nb, int E
 int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_gate,
                                     const void* w_up, void* gu, void* h,
                                     const int32_t* block_expert, const int32_t* n_blocks,
-                                    int64_t rows, int d, int f, int E);
+                                    const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
 
 /* Backward of the down projection fused with the SwiGLU derivative:
  * dh = dys.Wd[e]^T; dg = dh*u*silu'(g); du = dh*silu(g).  dys [rows,d], w_down [E,f,d],
  * gu [rows,2f], dgu [rows,2f] (dg | du). */
 int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_down, const void* gu,
                                  void* dgu, const int32_t* block_expert, const int32_t* n_blocks,
-                                 int64_t rows, int d, int f, int E);
+                                 const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
 
 /* dxs = dg.Wg[e]^T + du.Wu[e]^T.  dgu [rows,2f], w_gate/w_up [E,d,f], dxs [rows,d] bf16. */
 int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, const void* w_up,
                          void* dxs, const int32_t* block_expert, const int32_t* n_blocks,
-                         int64_t rows, int d, int f, int E);
+                         const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
 
 /* Bring-up hook (not part of the drop-in surface): overrides the shared-memory matrix-descriptor
  * geometry in bytes for K-major and MN-major operands; 0 keeps a value. */
 int lewi_debug_set_desc(int k_lbo, int k_sbo, int k_step, int mn_lbo, int mn_sbo, int mn_step);
+
+/* Bring-up hook: 0 forces the single-CTA GEMM kernels everywhere, 1 (default) allows CTA pairs. */
+int lewi_debug_set_cta_pair(int on);
 
 #ifdef __cplusplus
 }

@@ -36,13 +36,14 @@ SIGNATURES = {
     "lewi_gather_rows": (c_int, [P, P, P, P, P, c_int64, c_int64, c_int, c_int, c_int, c_int, P, c_int]),
     "lewi_gather_reduce": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64]),
     "lewi_gather_dot": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int64]),
-    "lewi_grouped_gemm_nn": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int]),
-    "lewi_grouped_gemm_nt": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int]),
+    "lewi_grouped_gemm_nn": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int]),
+    "lewi_grouped_gemm_nt": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int]),
     "lewi_grouped_gemm_tn": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, P, c_int64]),
     "lewi_grouped_gemm_tn_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int]),
-    "lewi_grouped_gemm_gateup_swiglu": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
-    "lewi_grouped_gemm_dh_dswiglu": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
-    "lewi_grouped_gemm_dx": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_grouped_gemm_gateup_swiglu": (c_int, [P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_grouped_gemm_dh_dswiglu": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_grouped_gemm_dx": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_debug_set_cta_pair": (c_int, [c_int]),
     "lewi_debug_set_desc": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
 }
 

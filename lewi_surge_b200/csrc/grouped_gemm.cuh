@@ -22,19 +22,27 @@
 namespace lewi {
 namespace gg {
 
-constexpr int BM = 128;       // rows per tile (= routing block)
+constexpr int BM = 128;       // rows per CTA tile (= routing block)
 constexpr int BN = 256;       // accumulator columns per tile (MMA N)
 constexpr int BK = 64;        // contraction elements per stage (128 bytes of bf16)
-constexpr int STAGES = 4;
+constexpr int RING_BYTES = 192 * 1024;         // shared-memory operand ring of one CTA
 constexpr int A_BYTES = BM * BK * 2;           // 16 KB
-constexpr int B_BYTES = BN * BK * 2;           // 32 KB
-constexpr int STAGE_BYTES = A_BYTES + B_BYTES; // 48 KB
 constexpr int CHUNK_BYTES = 64 * BK * 2;       // 8 KB: one [64 k][64 mn] box of an MN-major operand
+// One CTA per tile (cta_group::1): B is 256 x 64 = 32 KB, 4 stages of 48 KB.
+// A CTA pair per 256-row tile (cta_group::2): each CTA holds its own 128 rows of A and HALF of B
+// (128 x 64 = 16 KB), 6 stages of 32 KB; the tensor cores of both SMs read both halves.
+template <bool PAIR> struct Cfg {
+  static constexpr int B_BYTES = PAIR ? BN * BK : BN * BK * 2;
+  static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
+  static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
+};
+constexpr int MAX_STAGES = 6;
+constexpr int PAIR_PREFIX_BYTES = 1040;        // uint16 prefix of row-block pairs per expert (E <= 512)
 constexpr int EPI_WARPS = 8;      // two warps per TMEM lane quarter, each takes half of the columns
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int STAGING_PER_WARP = 4096;  // epilogue transposition buffer of one warp
-constexpr size_t SMEM_BYTES = (size_t)STAGES * STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ +
+constexpr size_t SMEM_BYTES = (size_t)RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + PAIR_PREFIX_BYTES +
                               (size_t)EPI_WARPS * STAGING_PER_WARP;
 
 enum Major { NN = 0, NT = 1, TN = 2 };
@@ -144,6 +152,7 @@ __device__ __forceinline__ void warp_own_row32_bf16(uint8_t* stage, int lane, co
 
 struct Tile {
   int e;        // expert
+  int second;   // pair mode, NN/NT: 1 if the second 128-row block of the pair belongs to the same expert
   int row0;     // first row of the row-indexed operand (NN/NT: A rows; TN: first contraction row)
   int m0;       // TN: first output row
   int n0;       // first accumulator column in output coordinates (SWIGLU: first h column)
@@ -153,17 +162,21 @@ struct Tile {
   int split;    // TN: index of the contraction part
 };
 
-template <int MAJOR, int EPI>
-__device__ __forceinline__ Tile decode_tile(const Args& a, int tile, int n_tiles_n) {
+// Row-block pairs (pair mode, NN/NT): expert e owns ceil(blocks_e / 2) pairs; pp[e] is the exclusive
+// prefix of those counts (uint16 in shared memory).  Pair p belongs to the largest e with pp[e] <= p.
+template <int MAJOR, int EPI, bool PAIR>
+__device__ __forceinline__ Tile decode_tile(const Args& a, int tile, int n_tiles_n, const uint16_t* pp) {
   Tile t;
+  t.second = 1;
   if constexpr (MAJOR == TN) {
-    const int m_tiles = (a.Ma + BM - 1) / BM;
+    constexpr int TM = PAIR ? 2 * BM : BM;
+    const int m_tiles = (a.Ma + TM - 1) / TM;
     const int per_e = m_tiles * n_tiles_n;
     t.split = tile % a.k_splits;
     tile /= a.k_splits;
     t.e = tile / per_e;
     const int rem = tile - t.e * per_e;
-    t.m0 = (rem / n_tiles_n) * BM;
+    t.m0 = (rem / n_tiles_n) * TM;
     const int nt = rem % n_tiles_n;
     if (a.out2 != nullptr) {  // two column halves, tiled separately so that no tile straddles them
       const int half = a.N / 2, per_half = n_tiles_n / 2;
@@ -186,42 +199,66 @@ __device__ __forceinline__ Tile decode_tile(const Args& a, int tile, int n_tiles
     t.kb0 = t.split * per;
     t.kb = max(0, min(per, kb_total - t.kb0));
   } else {
-    const int blk = tile / n_tiles_n;
-    const int nt = tile - blk * n_tiles_n;
-    t.e = a.block_expert ? a.block_expert[blk] : 0;
-    t.row0 = blk * BM;
+    const int unit = tile / n_tiles_n;   // row block (one CTA) or pair of row blocks (CTA pair)
+    const int nt = tile - unit * n_tiles_n;
     t.m0 = 0;
     t.n0 = nt * (EPI == SWIGLU ? BN / 2 : BN);
     t.nlim = a.N;
     t.kb0 = 0;
     t.split = 0;
     t.kb = a.kb_total;
-    if (t.e < 0 || t.e >= a.E) {  // corrupted table: skip the tile's work but keep the roles in step
-      t.e = 0;
-      t.kb = 0;
+    if constexpr (PAIR) {
+      if (a.pad_offsets != nullptr) {
+        int lo = 0, hi = a.E;  // largest e with pp[e] <= unit
+        while (hi - lo > 1) {
+          const int mid = (lo + hi) >> 1;
+          if ((int)pp[mid] <= unit) lo = mid; else hi = mid;
+        }
+        t.e = lo;
+        const int first = a.pad_offsets[lo] / BM + 2 * (unit - (int)pp[lo]);
+        t.row0 = first * BM;
+        t.second = (first + 1) * BM < a.pad_offsets[lo + 1];
+      } else {
+        t.e = 0;
+        t.row0 = unit * 2 * BM;
+        t.second = (long long)t.row0 + BM < a.rows;
+      }
+    } else {
+      t.e = a.block_expert ? a.block_expert[unit] : 0;
+      t.row0 = unit * BM;
+      if (t.e < 0 || t.e >= a.E) {  // corrupted table: skip the tile's work but keep the roles in step
+        t.e = 0;
+        t.kb = 0;
+      }
     }
   }
   return t;
 }
 
-template <int MAJOR, int EPI>
+template <int MAJOR, int EPI, bool PAIR>
 __global__ void __launch_bounds__(THREADS, 1)
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_b2, const Args a) {
+  constexpr int STAGES = Cfg<PAIR>::STAGES;
+  constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
+  constexpr int B_CHUNKS = PAIR ? 2 : 4;   // 64-column boxes of an MN-major B operand held by one CTA
   extern __shared__ uint8_t smem_raw[];
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t bar_base = smem_base + STAGES * STAGE_BYTES;
-  // barrier layout (8 bytes each): full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], drain
+  const uint32_t bar_base = smem_base + RING_BYTES;
+  // barrier layout (8 bytes each): full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], drain
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
-  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + b); };
-  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * STAGES + 2 + b); };
-  const uint32_t drain_bar = bar_base + 8u * (2 * STAGES + 4);
+  auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
+  auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + b); };
+  auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 2 + b); };
+  const uint32_t drain_bar = bar_base + 8u * (2 * MAX_STAGES + 4);
   uint8_t* generic_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(generic_base + STAGES * STAGE_BYTES + 128);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + STAGES * STAGE_BYTES + 136);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(generic_base + RING_BYTES + 160);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + RING_BYTES + 168);
+  uint16_t* pair_prefix = reinterpret_cast<uint16_t*>(generic_base + RING_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;   // 0 = leader of the pair
+  const bool leader = cta_rank == 0;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -230,7 +267,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(tfull_bar(b), 1);
-      ptx::mbar_init(tempty_bar(b), EPI_WARPS);
+      ptx::mbar_init(tempty_bar(b), PAIR ? 2 * EPI_WARPS : EPI_WARPS);
     }
     ptx::mbar_init(drain_bar, 1);
     *abort_flag = 0;
@@ -240,47 +277,89 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     ptx::prefetch_tensormap(&tm_b);
     if constexpr (EPI == SWIGLU || MAJOR == NT) ptx::prefetch_tensormap(&tm_b2);
   }
+  int n_units = 0;  // NN/NT: row blocks (or pairs of row blocks) to process
+  if constexpr (MAJOR != TN) {
+    if constexpr (PAIR) {
+      if (a.pad_offsets != nullptr) {
+        if (threadIdx.x == 32) {  // exclusive prefix of ceil(blocks_e / 2); a few hundred adds at most
+          int run = 0;
+          for (int e = 0; e < a.E; ++e) {
+            pair_prefix[e] = (uint16_t)run;
+            const int nb = (a.pad_offsets[e + 1] - a.pad_offsets[e]) / BM;
+            run += (nb + 1) >> 1;
+          }
+          pair_prefix[a.E] = (uint16_t)min(run, 65535);
+        }
+      }
+    }
+  }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
-    ptx::tmem_relinquish();
+    if constexpr (PAIR) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(tmem_slot)), TMEM_COLS);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) ptx::cluster_sync();   // both CTAs' barriers exist before anything remote touches them
   ptx::tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   // tile range
   int n_tiles_n, total_tiles;
   if constexpr (MAJOR == TN) {
+    constexpr int TM = PAIR ? 2 * BM : BM;
     n_tiles_n = a.out2 != nullptr ? 2 * ((a.N / 2 + BN - 1) / BN) : (a.N + BN - 1) / BN;
-    total_tiles = a.E * ((a.Ma + BM - 1) / BM) * n_tiles_n * a.k_splits;
+    total_tiles = a.E * ((a.Ma + TM - 1) / TM) * n_tiles_n * a.k_splits;
   } else {
     const int bn_out = (EPI == SWIGLU) ? BN / 2 : BN;
     n_tiles_n = (a.N + bn_out - 1) / bn_out;
-    int nb = a.n_blocks_host;
-    if (a.n_blocks != nullptr) nb = min(nb, max(a.n_blocks[0], 0));
-    total_tiles = nb * n_tiles_n;
+    if constexpr (PAIR) {
+      if (a.pad_offsets != nullptr) n_units = pair_prefix[a.E];
+      else n_units = (int)((a.rows + 2 * BM - 1) / (2 * BM));
+      n_units = min(n_units, a.n_blocks_host);
+    } else {
+      n_units = a.n_blocks_host;
+      if (a.n_blocks != nullptr) n_units = min(n_units, max(a.n_blocks[0], 0));
+    }
+    total_tiles = n_units * n_tiles_n;
   }
+  const int tile_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int tile_step = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  // in pair mode every load credits the LEADER's full barrier
+  auto full_target = [&](int s) { return PAIR ? ptx::map_to_cta(full_bar(s), 0) : full_bar(s); };
 
   if (warp == 0) {
     // ------------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const Tile t = decode_tile<MAJOR, EPI>(a, tile, n_tiles_n);
+      for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
+        const Tile t = decode_tile<MAJOR, EPI, PAIR>(a, tile, n_tiles_n, pair_prefix);
         for (int kb = 0; kb < t.kb; ++kb, ++it) {
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-          ptx::mbar_expect_tx(full_bar(s), STAGE_BYTES);
+          if (leader) ptx::mbar_expect_tx(full_bar(s), PAIR ? 2 * STAGE_BYTES : STAGE_BYTES);
+          const uint32_t fb = full_target(s);
+          auto load2 = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1) {
+            if constexpr (PAIR) ptx::tma_load_2d_pair(dst, tm, fb, c0, c1); else ptx::tma_load_2d(dst, tm, fb, c0, c1);
+          };
+          auto load3 = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2) {
+            if constexpr (PAIR) ptx::tma_load_3d_pair(dst, tm, fb, c0, c1, c2); else ptx::tma_load_3d(dst, tm, fb, c0, c1, c2);
+          };
+          const int nb0 = t.n0 + (PAIR ? (int)cta_rank * (BN / 2) : 0);   // first B column/row held by this CTA
           if constexpr (MAJOR == TN) {
             const int r = t.row0 + (t.kb0 + kb) * BK;
+            const int ma0 = t.m0 + (int)cta_rank * BM;
 #pragma unroll
-            for (int c = 0; c < 2; ++c) ptx::tma_load_2d(sa + c * CHUNK_BYTES, &tm_a, full_bar(s), t.m0 + 64 * c, r);
+            for (int c = 0; c < 2; ++c) load2(sa + c * CHUNK_BYTES, &tm_a, ma0 + 64 * c, r);
 #pragma unroll
-            for (int c = 0; c < 4; ++c) ptx::tma_load_2d(sb + c * CHUNK_BYTES, &tm_b, full_bar(s), t.n0 + 64 * c, r);
+            for (int c = 0; c < B_CHUNKS; ++c) load2(sb + c * CHUNK_BYTES, &tm_b, nb0 + 64 * c, r);
           } else {
             int ka = kb * BK;
             if constexpr (MAJOR == NN) {
@@ -288,28 +367,31 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             } else {
               if (kb >= a.kb_split) ka = a.k2_offset + (kb - a.kb_split) * BK;
             }
-            ptx::tma_load_2d(sa, &tm_a, full_bar(s), ka, t.row0);
+            load2(sa, &tm_a, ka, t.row0 + (int)cta_rank * BM);
             if constexpr (MAJOR == NN) {
               if constexpr (EPI == SWIGLU) {
+                if constexpr (PAIR) {  // the leader's half of B is the gate tile, the peer's half the up tile
+                  const CUtensorMap* tm = leader ? &tm_b : &tm_b2;
 #pragma unroll
-                for (int c = 0; c < 2; ++c)
-                  ptx::tma_load_3d(sb + c * CHUNK_BYTES, &tm_b, full_bar(s), t.n0 + 64 * c, kb * BK, t.e);
+                  for (int c = 0; c < 2; ++c) load3(sb + c * CHUNK_BYTES, tm, t.n0 + 64 * c, kb * BK, t.e);
+                } else {
 #pragma unroll
-                for (int c = 0; c < 2; ++c)
-                  ptx::tma_load_3d(sb + (2 + c) * CHUNK_BYTES, &tm_b2, full_bar(s), t.n0 + 64 * c, kb * BK, t.e);
+                  for (int c = 0; c < 2; ++c) load3(sb + c * CHUNK_BYTES, &tm_b, t.n0 + 64 * c, kb * BK, t.e);
+#pragma unroll
+                  for (int c = 0; c < 2; ++c) load3(sb + (2 + c) * CHUNK_BYTES, &tm_b2, t.n0 + 64 * c, kb * BK, t.e);
+                }
               } else {
 #pragma unroll
-                for (int c = 0; c < 4; ++c)
-                  ptx::tma_load_3d(sb + c * CHUNK_BYTES, &tm_b, full_bar(s), t.n0 + 64 * c, kb * BK, t.e);
+                for (int c = 0; c < B_CHUNKS; ++c) load3(sb + c * CHUNK_BYTES, &tm_b, nb0 + 64 * c, kb * BK, t.e);
               }
             } else {  // NT
-              if (kb < a.kb_split) ptx::tma_load_3d(sb, &tm_b, full_bar(s), kb * BK, t.n0, t.e);
-              else ptx::tma_load_3d(sb, &tm_b2, full_bar(s), (kb - a.kb_split) * BK, t.n0, t.e);
+              if (kb < a.kb_split) load3(sb, &tm_b, kb * BK, nb0, t.e);
+              else load3(sb, &tm_b2, (kb - a.kb_split) * BK, nb0, t.e);
             }
           }
         }
       }
-      if (*abort_flag) {
+      if (*abort_flag && leader) {
         // give the copies already issued a bounded chance to land before shared memory is released
         const uint32_t first = it > STAGES ? it - STAGES : 0;
         for (uint32_t j = first; j < it; ++j) {
@@ -321,12 +403,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
     }
   } else if (warp == 1) {
-    // ------------------------------------------------------------------ MMA issuer
-    if (lane == 0) {
+    // ------------------------------------------------------------------ MMA issuer (leader CTA only in pair mode)
+    if (lane == 0 && leader) {
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-        const Tile t = decode_tile<MAJOR, EPI>(a, tile, n_tiles_n);
+      for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
+        const Tile t = decode_tile<MAJOR, EPI, PAIR>(a, tile, n_tiles_n, pair_prefix);
         if (t.kb == 0) continue;
         const uint32_t acc = acc_it & 1u, acc_ph = (acc_it >> 1) & 1u;
         if (!ptx::mbar_wait(tempty_bar(acc), acc_ph ^ 1u, abort_flag)) { ok = false; break; }
@@ -342,17 +424,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           for (int j = 0; j < BK / 16; ++j) {
             const uint64_t da = ptx::smem_desc(a.desc_hi_a, sa + j * a.kstep_a);
             const uint64_t db = ptx::smem_desc(a.desc_hi_b, sb + j * a.kstep_b);
-            ptx::mma_bf16(d_tmem, da, db, a.idesc, (kb > 0 || j > 0) ? 1u : 0u);
+            if constexpr (PAIR) ptx::mma_bf16_pair(d_tmem, da, db, a.idesc, (kb > 0 || j > 0) ? 1u : 0u);
+            else ptx::mma_bf16(d_tmem, da, db, a.idesc, (kb > 0 || j > 0) ? 1u : 0u);
           }
-          ptx::mma_commit(empty_bar(s));
+          if constexpr (PAIR) ptx::mma_commit_pair(empty_bar(s), 3);
+          else ptx::mma_commit(empty_bar(s));
         }
         if (!ok) break;
-        ptx::mma_commit(tfull_bar(acc));
+        if constexpr (PAIR) ptx::mma_commit_pair(tfull_bar(acc), 3);
+        else ptx::mma_commit(tfull_bar(acc));
         ++acc_it;
       }
       if (*abort_flag) {
         // wait (bounded) until the tensor core has finished what was issued
-        ptx::mma_commit(drain_bar);
+        if constexpr (PAIR) ptx::mma_commit_pair(drain_bar, 1);
+        else ptx::mma_commit(drain_bar);
         const unsigned long long t0 = ptx::globaltimer_ns();
         while (!ptx::mbar_try_wait(drain_bar, 0)) {
           if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
@@ -363,16 +449,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int lane_grp = warp & 3;           // TMEM lanes 32*lane_grp .. +31 are readable by this warp
     const int col_half = (warp - 2) >> 2;    // which half of the tile's columns this warp stores
-    uint8_t* stage = generic_base + STAGES * STAGE_BYTES + 256 + (warp - 2) * STAGING_PER_WARP;
+    uint8_t* stage = generic_base + RING_BYTES + 256 + PAIR_PREFIX_BYTES + (warp - 2) * STAGING_PER_WARP;
     uint32_t acc_it = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; ok && tile < total_tiles; tile += gridDim.x) {
-      const Tile t = decode_tile<MAJOR, EPI>(a, tile, n_tiles_n);
+    for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
+      const Tile t = decode_tile<MAJOR, EPI, PAIR>(a, tile, n_tiles_n, pair_prefix);
       const bool has_acc = t.kb > 0;
       // first row (of the output tensor) handled by this warp and how many of its 32 rows exist
-      const long long wrow0 = (MAJOR == TN ? (long long)t.m0 : (long long)t.row0) + lane_grp * 32;
+      const long long wrow0 = (MAJOR == TN ? (long long)t.m0 : (long long)t.row0) + (long long)cta_rank * BM + lane_grp * 32;
       const long long row_lim = MAJOR == TN ? (long long)a.Ma : a.rows;
-      const int rows_valid = (int)max(0LL, min(32LL, row_lim - wrow0));
+      int rows_valid = (int)max(0LL, min(32LL, row_lim - wrow0));
+      if (MAJOR != TN && cta_rank == 1 && !t.second) rows_valid = 0;   // this CTA's block belongs to the next expert
 
       // DSWIGLU: the first block of g/u is fetched before the accumulator is waited for
       [[maybe_unused]] uint4 pg[4], pu[4];
@@ -511,7 +598,10 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (has_acc) {
         ptx::tc_fence_before();
         __syncwarp();
-        if (lane == 0) ptx::mbar_arrive(tempty_bar(acc));
+        if (lane == 0) {
+          if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(acc), 0));
+          else ptx::mbar_arrive(tempty_bar(acc));
+        }
         ++acc_it;
       }
     }
@@ -519,10 +609,12 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   ptx::tc_fence_before();
   __syncthreads();
+  if constexpr (PAIR) ptx::cluster_sync();   // neither CTA leaves while the other may still touch its memory
   if (warp == 1) {
     __syncwarp();
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    if constexpr (PAIR) ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    else ptx::tmem_dealloc(tmem_base, TMEM_COLS);
   }
 }
 
@@ -598,13 +690,19 @@ inline DescGeometry& desc_geometry() {
   return g;
 }
 
-template <int MAJOR, int EPI>
+// Whether the CTA-pair (cta_group::2) kernels are used where the arguments allow it.
+inline bool& pair_mode() {
+  static bool on = true;
+  return on;
+}
+
+template <int MAJOR, int EPI, bool PAIR>
 inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, Args a,
                   long long max_tiles) {
   static bool attr_set[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return LEWI_ERR_CUDA;
-  auto kern = grouped_gemm_kernel<MAJOR, EPI>;
+  auto kern = grouped_gemm_kernel<MAJOR, EPI, PAIR>;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess) {
       (void)cudaGetLastError();
@@ -618,13 +716,42 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
   a.desc_hi_b = b_mn ? ptx::smem_desc_hi_sw128(g.mn_lbo, g.mn_sbo) : ptx::smem_desc_hi_sw128(g.k_lbo, g.k_sbo);
   a.kstep_a = a_mn ? g.mn_step : g.k_step;
   a.kstep_b = b_mn ? g.mn_step : g.k_step;
-  a.idesc = ptx::instr_desc_bf16(BM, BN, a_mn ? 1 : 0, b_mn ? 1 : 0);
+  a.idesc = ptx::instr_desc_bf16(PAIR ? 2 * BM : BM, BN, a_mn ? 1 : 0, b_mn ? 1 : 0);
   if (max_tiles <= 0) return LEWI_OK;
   long long grid = num_sms();
-  if (grid > max_tiles) grid = max_tiles;
-  kern<<<(int)grid, THREADS, SMEM_BYTES, st>>>(ta, tb, tb2, a);
+  if constexpr (PAIR) {
+    grid &= ~1LL;
+    if (grid > 2 * max_tiles) grid = 2 * max_tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(THREADS);
+    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, tb2, a) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return LEWI_ERR_CUDA;
+    }
+  } else {
+    if (grid > max_tiles) grid = max_tiles;
+    kern<<<(int)grid, THREADS, SMEM_BYTES, st>>>(ta, tb, tb2, a);
+  }
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
+}
+
+// Picks the CTA-pair kernel when enabled, else the single-CTA one.
+template <int MAJOR, int EPI>
+inline int launch_auto(bool pair, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2,
+                       const Args& a, long long max_tiles) {
+  if (pair) return launch<MAJOR, EPI, true>(st, ta, tb, tb2, a, max_tiles);
+  return launch<MAJOR, EPI, false>(st, ta, tb, tb2, a, max_tiles);
 }
 
 }  // namespace gg

@@ -252,9 +252,19 @@ namespace {
 struct RowGroupArgs {
   const int32_t* block_expert;
   const int32_t* n_blocks;
+  const int32_t* pad_offsets;
   int64_t rows;
   int E;
 };
+
+// The CTA-pair kernels derive a row block's expert from pad_offsets; the single-CTA ones read
+// block_expert.  One group (no tables at all) works with both.
+inline bool use_pair(const RowGroupArgs& r) {
+  if (!gg::pair_mode()) return false;
+  if (r.block_expert != nullptr && r.pad_offsets == nullptr) return false;
+  const long long nb = (r.rows + gg::BM - 1) / gg::BM;
+  return (nb + r.E) / 2 + 1 < 65535;   // pair prefixes are kept as 16-bit counts
+}
 
 inline int check_rows(const RowGroupArgs& r) {
   if (r.rows < 0 || r.E <= 0) return LEWI_ERR_ARG;
@@ -269,9 +279,10 @@ inline void fill_common(gg::Args& a, const RowGroupArgs& r) {
   a.row_scale = nullptr;
   a.block_expert = r.block_expert;
   a.n_blocks = r.n_blocks;
-  a.pad_offsets = nullptr;
+  a.pad_offsets = r.pad_offsets;
   a.rows = r.rows;
   a.n_blocks_host = (int)((r.rows + gg::BM - 1) / gg::BM);
+  if (use_pair(r)) a.n_blocks_host = (int)((a.n_blocks_host + r.E + 1) / 2);   // bound on row-block pairs
   a.K = 0;
   a.N = 0;
   a.Ma = 0;
@@ -330,7 +341,8 @@ int lewi_router_logits(void* stream, const void* x, const float* w_router, const
   CUtensorMap ta, tb;
   if (!gg::make_map(&ta, x, (uint64_t)d, (uint64_t)T, 0, 64, 128)) return LEWI_ERR_CUDA;
   if (!gg::make_map(&tb, w3, (uint64_t)E, (uint64_t)3 * d, 1, 64, 64)) return LEWI_ERR_CUDA;
-  RowGroupArgs r{nullptr, nullptr, T, 1};
+  RowGroupArgs r{nullptr, nullptr, nullptr, T, 1};
+  const bool pair = use_pair(r);
   gg::Args a;
   fill_common(a, r);
   a.out = logits;
@@ -341,15 +353,16 @@ int lewi_router_logits(void* stream, const void* x, const float* w_router, const
   a.a_k_wrap = d;
   a.col_bias = bias;
   const long long tiles = (long long)a.n_blocks_host * ((E + gg::BN - 1) / gg::BN);
-  return gg::launch<gg::NN, gg::PLAIN>(st, ta, tb, tb, a, tiles);
+  return gg::launch_auto<gg::NN, gg::PLAIN>(pair, st, ta, tb, tb, a, tiles);
 }
 
 int lewi_grouped_gemm_nn(void* stream, const void* a_ptr, const void* b_ptr, void* out, const float* row_scale,
-                         const int32_t* block_expert, const int32_t* n_blocks, int64_t rows, int K, int N, int E,
-                         int out_dtype) {
+                         const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows,
+                         int K, int N, int E, int out_dtype) {
   if (!a_ptr || !b_ptr || !out || K <= 0 || N <= 0) return LEWI_ERR_ARG;
   if (out_dtype != LEWI_BF16 && out_dtype != LEWI_F32) return LEWI_ERR_ARG;
-  RowGroupArgs r{block_expert, n_blocks, rows, E};
+  RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
+  const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
   if (K % 8 != 0 || N % 8 != 0 || !aligned16(a_ptr) || !aligned16(b_ptr) || !aligned16(out)) return LEWI_ERR_SHAPE;
   if (rows == 0) return LEWI_OK;
@@ -365,21 +378,22 @@ int lewi_grouped_gemm_nn(void* stream, const void* a_ptr, const void* b_ptr, voi
   a.N = N;
   a.out_f32 = out_dtype == LEWI_F32;
   const long long tiles = (long long)a.n_blocks_host * ((N + gg::BN - 1) / gg::BN);
-  return gg::launch<gg::NN, gg::PLAIN>(as_stream(stream), ta, tb, tb, a, tiles);
+  return gg::launch_auto<gg::NN, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb, a, tiles);
 }
 
 int lewi_grouped_gemm_nt(void* stream, const void* a_ptr, const void* b_ptr, void* out, const float* row_scale,
-                         const int32_t* block_expert, const int32_t* n_blocks, int64_t rows, int K, int N, int E,
-                         int out_dtype) {
+                         const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows,
+                         int K, int N, int E, int out_dtype) {
   if (!a_ptr || !b_ptr || !out || K <= 0 || N <= 0) return LEWI_ERR_ARG;
   if (out_dtype != LEWI_BF16 && out_dtype != LEWI_F32) return LEWI_ERR_ARG;
-  RowGroupArgs r{block_expert, n_blocks, rows, E};
+  RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
+  const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
   if (K % 8 != 0 || N % 8 != 0 || !aligned16(a_ptr) || !aligned16(b_ptr) || !aligned16(out)) return LEWI_ERR_SHAPE;
   if (rows == 0) return LEWI_OK;
   CUtensorMap ta, tb;
   if (!gg::make_map(&ta, a_ptr, (uint64_t)K, (uint64_t)rows, 0, 64, 128)) return LEWI_ERR_CUDA;
-  if (!gg::make_map(&tb, b_ptr, (uint64_t)K, (uint64_t)N, (uint64_t)E, 64, 256)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&tb, b_ptr, (uint64_t)K, (uint64_t)N, (uint64_t)E, 64, pair ? 128 : 256)) return LEWI_ERR_CUDA;
   gg::Args a;
   fill_common(a, r);
   a.out = out;
@@ -389,14 +403,15 @@ int lewi_grouped_gemm_nt(void* stream, const void* a_ptr, const void* b_ptr, voi
   a.N = N;
   a.out_f32 = out_dtype == LEWI_F32;
   const long long tiles = (long long)a.n_blocks_host * ((N + gg::BN - 1) / gg::BN);
-  return gg::launch<gg::NT, gg::PLAIN>(as_stream(stream), ta, tb, tb, a, tiles);
+  return gg::launch_auto<gg::NT, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb, a, tiles);
 }
 
 int64_t lewi_grouped_gemm_tn_workspace_bytes(int64_t rows, int Ma, int Nb, int E, int split_out) {
   if (rows < 0 || Ma <= 0 || Nb <= 0 || E <= 0) return LEWI_ERR_ARG;
   const long long n_tiles = split_out ? 2LL * ((Nb / 2 + gg::BN - 1) / gg::BN) : (Nb + gg::BN - 1) / gg::BN;
-  const long long tiles0 = (long long)E * ((Ma + gg::BM - 1) / gg::BM) * n_tiles;
-  const int s = tn_pick_splits(tiles0, rows);
+  const int tm = gg::pair_mode() ? 2 * gg::BM : gg::BM;
+  const long long tiles0 = (long long)E * ((Ma + tm - 1) / tm) * n_tiles;
+  const int s = tn_pick_splits(tiles0 * (gg::pair_mode() ? 2 : 1), rows);
   return s > 1 ? (int64_t)s * E * Ma * Nb * 4 : 0;
 }
 
@@ -411,7 +426,8 @@ int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, voi
     return LEWI_ERR_SHAPE;
   if (out2 != nullptr && (Nb / 2) % 8 != 0) return LEWI_ERR_SHAPE;
   if (pad_offsets == nullptr && E != 1) return LEWI_ERR_ARG;
-  RowGroupArgs r{nullptr, nullptr, rows, E};
+  RowGroupArgs r{nullptr, nullptr, nullptr, rows, E};
+  const bool pair = gg::pair_mode();
   gg::Args a;
   fill_common(a, r);
   a.out = out;
@@ -421,7 +437,8 @@ int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, voi
   a.Ma = Ma;
   a.out_f32 = out_dtype == LEWI_F32;
   const long long n_tiles = out2 ? 2LL * ((Nb / 2 + gg::BN - 1) / gg::BN) : (Nb + gg::BN - 1) / gg::BN;
-  const long long tiles0 = (long long)E * ((Ma + gg::BM - 1) / gg::BM) * n_tiles;
+  const int tm = pair ? 2 * gg::BM : gg::BM;
+  const long long tiles0 = (long long)E * ((Ma + tm - 1) / tm) * n_tiles;
   cudaStream_t st = as_stream(stream);
   if (rows == 0) {
     // no rows at all: the product is all zeros
@@ -433,7 +450,7 @@ int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, voi
   }
   int splits = 1;
   if (workspace != nullptr) {
-    splits = tn_pick_splits(tiles0, rows);
+    splits = tn_pick_splits(tiles0 * (pair ? 2 : 1), rows);
     const long long per = (long long)E * Ma * Nb * 4;
     if ((long long)splits * per > workspace_bytes) splits = (int)(workspace_bytes / per);
     if (splits < 2) splits = 1;
@@ -443,7 +460,7 @@ int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, voi
   CUtensorMap ta, tb;
   if (!gg::make_map(&ta, a_ptr, (uint64_t)Ma, (uint64_t)rows, 0, 64, 64)) return LEWI_ERR_CUDA;
   if (!gg::make_map(&tb, b_ptr, (uint64_t)Nb, (uint64_t)rows, 0, 64, 64)) return LEWI_ERR_CUDA;
-  if (int rc = gg::launch<gg::TN, gg::TNOUT>(st, ta, tb, tb, a, tiles0 * splits)) return rc;
+  if (int rc = gg::launch_auto<gg::TN, gg::TNOUT>(pair, st, ta, tb, tb, a, tiles0 * splits)) return rc;
   if (splits > 1) {
     const long long total4 = (long long)E * Ma * Nb / 4;
     long long grid = (total4 + 255) / 256;
@@ -455,10 +472,11 @@ int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, voi
 }
 
 int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_gate, const void* w_up, void* gu,
-                                    void* h, const int32_t* block_expert, const int32_t* n_blocks, int64_t rows,
-                                    int d, int f, int E) {
+                                    void* h, const int32_t* block_expert, const int32_t* n_blocks,
+                                    const int32_t* pad_offsets, int64_t rows, int d, int f, int E) {
   if (!xs || !w_gate || !w_up || !h || d <= 0 || f <= 0) return LEWI_ERR_ARG;
-  RowGroupArgs r{block_expert, n_blocks, rows, E};
+  RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
+  const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
   if (d % 8 != 0 || f % 8 != 0 || !aligned16(xs) || !aligned16(w_gate) || !aligned16(w_up) || !aligned16(gu) ||
       !aligned16(h))
@@ -476,14 +494,15 @@ int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_
   a.kb_total = (d + gg::BK - 1) / gg::BK;
   a.N = f;
   const long long tiles = (long long)a.n_blocks_host * ((f + gg::BN / 2 - 1) / (gg::BN / 2));
-  return gg::launch<gg::NN, gg::SWIGLU>(as_stream(stream), ta, tb, tb2, a, tiles);
+  return gg::launch_auto<gg::NN, gg::SWIGLU>(pair, as_stream(stream), ta, tb, tb2, a, tiles);
 }
 
 int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_down, const void* gu, void* dgu,
-                                 const int32_t* block_expert, const int32_t* n_blocks, int64_t rows, int d, int f,
-                                 int E) {
+                                 const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets,
+                                 int64_t rows, int d, int f, int E) {
   if (!dys || !w_down || !gu || !dgu || d <= 0 || f <= 0) return LEWI_ERR_ARG;
-  RowGroupArgs r{block_expert, n_blocks, rows, E};
+  RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
+  const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
   if (d % 8 != 0 || f % 8 != 0 || !aligned16(dys) || !aligned16(w_down) || !aligned16(gu) || !aligned16(dgu))
     return LEWI_ERR_SHAPE;
@@ -491,7 +510,7 @@ int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_do
   CUtensorMap ta, tb;
   if (!gg::make_map(&ta, dys, (uint64_t)d, (uint64_t)rows, 0, 64, 128)) return LEWI_ERR_CUDA;
   // w_down [E,f,d]: as the K-major B operand of dh[rows,f] = dys[rows,d] . w_down[e]^T
-  if (!gg::make_map(&tb, w_down, (uint64_t)d, (uint64_t)f, (uint64_t)E, 64, 256)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&tb, w_down, (uint64_t)d, (uint64_t)f, (uint64_t)E, 64, pair ? 128 : 256)) return LEWI_ERR_CUDA;
   gg::Args a;
   fill_common(a, r);
   a.out = dgu;
@@ -500,13 +519,15 @@ int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_do
   a.kb_total = (d + gg::BK - 1) / gg::BK;
   a.N = f;
   const long long tiles = (long long)a.n_blocks_host * ((f + gg::BN - 1) / gg::BN);
-  return gg::launch<gg::NT, gg::DSWIGLU>(as_stream(stream), ta, tb, tb, a, tiles);
+  return gg::launch_auto<gg::NT, gg::DSWIGLU>(pair, as_stream(stream), ta, tb, tb, a, tiles);
 }
 
 int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, const void* w_up, void* dxs,
-                         const int32_t* block_expert, const int32_t* n_blocks, int64_t rows, int d, int f, int E) {
+                         const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets,
+                         int64_t rows, int d, int f, int E) {
   if (!dgu || !w_gate || !w_up || !dxs || d <= 0 || f <= 0) return LEWI_ERR_ARG;
-  RowGroupArgs r{block_expert, n_blocks, rows, E};
+  RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
+  const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
   if (d % 8 != 0 || f % 8 != 0 || !aligned16(dgu) || !aligned16(w_gate) || !aligned16(w_up) || !aligned16(dxs))
     return LEWI_ERR_SHAPE;
@@ -514,8 +535,8 @@ int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, cons
   CUtensorMap ta, tb, tb2;
   if (!gg::make_map(&ta, dgu, (uint64_t)(2 * f), (uint64_t)rows, 0, 64, 128)) return LEWI_ERR_CUDA;
   // w_gate/w_up [E,d,f]: K-major B operands (contraction over f) of dxs[rows,d]
-  if (!gg::make_map(&tb, w_gate, (uint64_t)f, (uint64_t)d, (uint64_t)E, 64, 256)) return LEWI_ERR_CUDA;
-  if (!gg::make_map(&tb2, w_up, (uint64_t)f, (uint64_t)d, (uint64_t)E, 64, 256)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&tb, w_gate, (uint64_t)f, (uint64_t)d, (uint64_t)E, 64, pair ? 128 : 256)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&tb2, w_up, (uint64_t)f, (uint64_t)d, (uint64_t)E, 64, pair ? 128 : 256)) return LEWI_ERR_CUDA;
   gg::Args a;
   fill_common(a, r);
   a.out = dxs;
@@ -525,11 +546,17 @@ int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, cons
   a.k2_offset = f;
   a.kb_total = 2 * a.kb_split;
   const long long tiles = (long long)a.n_blocks_host * ((d + gg::BN - 1) / gg::BN);
-  return gg::launch<gg::NT, gg::PLAIN>(as_stream(stream), ta, tb, tb2, a, tiles);
+  return gg::launch_auto<gg::NT, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb2, a, tiles);
 }
 
 // Bring-up hook: override the shared-memory descriptor geometry (bytes).  A value of 0 keeps the
 // current setting.  Not part of the drop-in surface.
+// Bring-up hook: 0 forces the single-CTA (cta_group::1) GEMM kernels, 1 (default) allows CTA pairs.
+int lewi_debug_set_cta_pair(int on) {
+  gg::pair_mode() = on != 0;
+  return LEWI_OK;
+}
+
 int lewi_debug_set_desc(int k_lbo, int k_sbo, int k_step, int mn_lbo, int mn_sbo, int mn_step) {
   gg::DescGeometry& g = gg::desc_geometry();
   if (k_lbo > 0) g.k_lbo = (uint32_t)k_lbo;

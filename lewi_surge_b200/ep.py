@@ -93,15 +93,15 @@ class CudaBackend:
     return self.ops.gather_dot(y, pos, g)
 
   def experts_fwd(self, xs_pad, w_gate, w_up, w_down, t):
-    gu, h = self.layer.gateup_swiglu(xs_pad, w_gate, w_up, t["block_expert"], t["n_blocks"])
-    ys = self.ops.grouped_gemm_nn(h, w_down, t["block_expert"], t["n_blocks"])
+    gu, h = self.layer.gateup_swiglu(xs_pad, w_gate, w_up, t["block_expert"], t["n_blocks"], pad_offsets=t["pad_offsets"])
+    ys = self.ops.grouped_gemm_nn(h, w_down, t["block_expert"], t["n_blocks"], pad_offsets=t["pad_offsets"])
     return gu, h, ys
 
   def experts_bwd(self, dys_pad, xs_pad, gu, h, w_gate, w_up, w_down, t):
     e = w_gate.shape[0]
-    dgu = self.layer.dh_dswiglu(dys_pad, w_down, gu, t["block_expert"], t["n_blocks"])
+    dgu = self.layer.dh_dswiglu(dys_pad, w_down, gu, t["block_expert"], t["n_blocks"], pad_offsets=t["pad_offsets"])
     dw_down = self.ops.grouped_gemm_tn(h, dys_pad, t["pad_offsets"], e, out_dtype=w_down.dtype)
-    dxs = self.layer.dx_from_dgu(dgu, w_gate, w_up, t["block_expert"], t["n_blocks"])
+    dxs = self.layer.dx_from_dgu(dgu, w_gate, w_up, t["block_expert"], t["n_blocks"], pad_offsets=t["pad_offsets"])
     dw_gate, dw_up = self.ops.grouped_gemm_tn(xs_pad, dgu, t["pad_offsets"], e, out_dtype=w_gate.dtype, split=True)
     return dxs, dw_gate, dw_up, dw_down
 

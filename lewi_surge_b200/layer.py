@@ -129,7 +129,7 @@ def cast_bf16(src):
   return dst
 
 
-def gateup_swiglu(xs, w_gate, w_up, block_expert, n_blocks, want_gu=True):
+def gateup_swiglu(xs, w_gate, w_up, block_expert, n_blocks, want_gu=True, pad_offsets=None):
   """(gu [rows,2f], h [rows,f]) = fused gate/up projection + SwiGLU over the padded rows."""
   lib = _lib.load()
   rows, d = xs.shape
@@ -137,28 +137,28 @@ def gateup_swiglu(xs, w_gate, w_up, block_expert, n_blocks, want_gu=True):
   gu = torch.empty((rows, 2 * f), dtype=torch.bfloat16, device=xs.device) if want_gu else None
   h = torch.empty((rows, f), dtype=torch.bfloat16, device=xs.device)
   check(lib.lewi_grouped_gemm_gateup_swiglu(stream(), ptr(xs), ptr(w_gate), ptr(w_up), ptr(gu), ptr(h),
-                                            ptr(block_expert), ptr(n_blocks), rows, d, f, e),
+                                            ptr(block_expert), ptr(n_blocks), ptr(pad_offsets), rows, d, f, e),
         "lewi_grouped_gemm_gateup_swiglu")
   return gu, h
 
 
-def dh_dswiglu(dys, w_down, gu, block_expert, n_blocks):
+def dh_dswiglu(dys, w_down, gu, block_expert, n_blocks, pad_offsets=None):
   lib = _lib.load()
   rows, d = dys.shape
   e, f, _ = w_down.shape
   dgu = torch.empty((rows, 2 * f), dtype=torch.bfloat16, device=dys.device)
   check(lib.lewi_grouped_gemm_dh_dswiglu(stream(), ptr(dys), ptr(w_down), ptr(gu), ptr(dgu), ptr(block_expert),
-                                         ptr(n_blocks), rows, d, f, e), "lewi_grouped_gemm_dh_dswiglu")
+                                         ptr(n_blocks), ptr(pad_offsets), rows, d, f, e), "lewi_grouped_gemm_dh_dswiglu")
   return dgu
 
 
-def dx_from_dgu(dgu, w_gate, w_up, block_expert, n_blocks):
+def dx_from_dgu(dgu, w_gate, w_up, block_expert, n_blocks, pad_offsets=None):
   lib = _lib.load()
   rows = dgu.shape[0]
   e, d, f = w_gate.shape
   dxs = torch.empty((rows, d), dtype=torch.bfloat16, device=dgu.device)
   check(lib.lewi_grouped_gemm_dx(stream(), ptr(dgu), ptr(w_gate), ptr(w_up), ptr(dxs), ptr(block_expert),
-                                 ptr(n_blocks), rows, d, f, e), "lewi_grouped_gemm_dx")
+                                 ptr(n_blocks), ptr(pad_offsets), rows, d, f, e), "lewi_grouped_gemm_dx")
   return dxs
 
 
@@ -188,9 +188,9 @@ def moe_layer_fwd(x, w: MoEWeights, k, logits=None):
   xs = torch.empty((tb.mpad, d), dtype=x.dtype, device=x.device)
   ops.gather_rows(x, tb.row_slot, idx_div=k, out=xs, n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
   _mark("dispatch_gather")
-  gu, h = gateup_swiglu(xs, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks)
+  gu, h = gateup_swiglu(xs, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
   _mark("gemm_gateup_swiglu")
-  ys = ops.grouped_gemm_nn(h, w.w_down, tb.block_expert, tb.n_blocks)
+  ys = ops.grouped_gemm_nn(h, w.w_down, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
   _mark("gemm_down")
   gus = hs = ysh = None
   if w.ws_gate is not None:
@@ -218,11 +218,11 @@ def moe_layer_bwd(dout, w: MoEWeights, c: LayerCache):
                   n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
   _mark("combine_bwd_scaled_gather")
   # experts backward
-  dgu = dh_dswiglu(dys, w.w_down, c.gu, tb.block_expert, tb.n_blocks)
+  dgu = dh_dswiglu(dys, w.w_down, c.gu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
   _mark("gemm_dh_dswiglu")
   dw_down = ops.grouped_gemm_tn(c.h, dys, tb.pad_offsets, e, out_dtype=w.w_down.dtype)
   _mark("gemm_dw_down")
-  dxs = dx_from_dgu(dgu, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks)
+  dxs = dx_from_dgu(dgu, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
   _mark("gemm_dx")
   dw_gate, dw_up = ops.grouped_gemm_tn(c.xs, dgu, tb.pad_offsets, e, out_dtype=w.w_gate.dtype, split=True)
   _mark("gemm_dw_gateup")

@@ -238,19 +238,19 @@ def group_tables(group_sizes, m, block=BLOCK):
               row_of_padded=row_of_padded[:mpad], padded_of_row=padded_of_row[:m], mpad=mpad)
 
 
-def grouped_gemm_nn(a, b, block_expert, n_blocks, out_dtype=torch.bfloat16, row_scale=None, out=None):
-  """out[r] = a[r] . b[expert of r's block];  a (rows, K), b (E, K, N)."""
+def grouped_gemm_nn(a, b, block_expert, n_blocks, out_dtype=torch.bfloat16, row_scale=None, out=None, pad_offsets=None):
+  """out[r] = a[r] . b[expert of r's block];  a (rows, K), b (E, K, N).  With ``pad_offsets`` the CTA-pair kernel runs."""
   lib = _lib.load()
   rows, k = a.shape
   e, _, n = b.shape
   if out is None:
     out = torch.empty((rows, n), dtype=out_dtype, device=a.device)
   check(lib.lewi_grouped_gemm_nn(stream(), ptr(a), ptr(b), ptr(out), ptr(row_scale), ptr(block_expert),
-                                 ptr(n_blocks), rows, k, n, e, _dt(out)), "lewi_grouped_gemm_nn")
+                                 ptr(n_blocks), ptr(pad_offsets), rows, k, n, e, _dt(out)), "lewi_grouped_gemm_nn")
   return out
 
 
-def grouped_gemm_nt(a, b, block_expert, n_blocks, out_dtype=torch.bfloat16, row_scale=None, out=None):
+def grouped_gemm_nt(a, b, block_expert, n_blocks, out_dtype=torch.bfloat16, row_scale=None, out=None, pad_offsets=None):
   """out[r] = a[r] . b[expert]^T;  a (rows, K), b (E, N, K)."""
   lib = _lib.load()
   rows, k = a.shape
@@ -258,7 +258,7 @@ def grouped_gemm_nt(a, b, block_expert, n_blocks, out_dtype=torch.bfloat16, row_
   if out is None:
     out = torch.empty((rows, n), dtype=out_dtype, device=a.device)
   check(lib.lewi_grouped_gemm_nt(stream(), ptr(a), ptr(b), ptr(out), ptr(row_scale), ptr(block_expert),
-                                 ptr(n_blocks), rows, k, n, e, _dt(out)), "lewi_grouped_gemm_nt")
+                                 ptr(n_blocks), ptr(pad_offsets), rows, k, n, e, _dt(out)), "lewi_grouped_gemm_nt")
   return out
 
 
@@ -300,7 +300,7 @@ class _RaggedDot(torch.autograd.Function):
     a = lhs.to(torch.bfloat16).contiguous()
     b = rhs.to(torch.bfloat16).contiguous()
     buf = gather_rows(a, t["row_of_padded"])
-    out_pad = grouped_gemm_nn(buf, b, t["block_expert"], t["n_blocks"])
+    out_pad = grouped_gemm_nn(buf, b, t["block_expert"], t["n_blocks"], pad_offsets=t["pad_offsets"])
     out = gather_rows(out_pad, t["padded_of_row"])
     ctx.save_for_backward(buf, b, t["row_of_padded"], t["padded_of_row"], t["block_expert"], t["n_blocks"],
                           t["pad_offsets"])
@@ -312,7 +312,7 @@ class _RaggedDot(torch.autograd.Function):
     buf, b, row_of_padded, padded_of_row, block_expert, n_blocks, pad_offsets = ctx.saved_tensors
     g_pad = gather_rows(g.to(torch.bfloat16).contiguous(), row_of_padded)
     # dlhs = g . rhs[e]^T: rhs [E,K,N] read as the K-major operand with contraction over N
-    dl_pad = grouped_gemm_nt(g_pad, b, block_expert, n_blocks)
+    dl_pad = grouped_gemm_nt(g_pad, b, block_expert, n_blocks, pad_offsets=pad_offsets)
     dlhs = gather_rows(dl_pad, padded_of_row)
     drhs = grouped_gemm_tn(buf, g_pad, pad_offsets, ctx.e, out_dtype=torch.float32)
     return dlhs.to(ctx.lhs_dtype), drhs.to(ctx.rhs_dtype), None

@@ -54,9 +54,9 @@ def test_argument_rejection_without_gpu(lib):
   assert lib.lewi_gather_rows(None, None, None, None, None, 1, 1, 8, 0, 1, 0, None, 1) == -1
   assert lib.lewi_router_topk(None, None, 4, 8, 2, 128, None, None, None, None, None, None, None, None, None, None,
                               None, None, None, 0) == -1
-  assert lib.lewi_grouped_gemm_nn(None, None, None, None, None, None, None, 128, 64, 64, 1, 0) == -1
+  assert lib.lewi_grouped_gemm_nn(None, None, None, None, None, None, None, None, 128, 64, 64, 1, 0) == -1
   assert lib.lewi_grouped_gemm_tn(None, None, None, None, None, None, 128, 64, 64, 1, 0, None, 0) == -1
-  assert lib.lewi_grouped_gemm_nn(None, 16, 16, 16, None, None, None, 128, 60, 64, 1, 0) == -2  # K % 64
+  assert lib.lewi_grouped_gemm_nn(None, 16, 16, 16, None, None, None, None, 128, 60, 64, 1, 0) == -2  # K % 8
 
 
 def test_missing_library_fails_loudly(monkeypatch, tmp_path):

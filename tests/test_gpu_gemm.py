@@ -10,6 +10,16 @@ pytestmark = pytest.mark.gpu
 TOL = 1e-2  # bf16 outputs vs the float32 oracle: max|diff| / max|want|
 
 
+@pytest.fixture(params=[1, 0], ids=["cta_pair", "single_cta"])
+def cta_pair(request, cuda):
+  """Runs a test once with the CTA-pair (cta_group::2) kernels and once with the single-CTA ones."""
+  from lewi_surge_b200 import _lib
+  lib = _lib.load()
+  lib.lewi_debug_set_cta_pair(request.param)
+  yield request.param
+  lib.lewi_debug_set_cta_pair(1)
+
+
 def padded_problem(rng, gs, k_dim, block=128):
   """Rows in padded-block order for group sizes gs: returns (a_pad, tables, valid mask)."""
   gs = np.asarray(gs, np.int32)
@@ -36,6 +46,7 @@ def expected_nn(a, b, pad):
 
 CASES = [
     ([128], 64, 64),
+    ([256, 128, 384, 0, 129], 128, 256),       # even, odd and empty block counts: every pairing case
     ([70, 3], 96, 40),                         # extents that are multiples of 8 but not of the tile sizes
     ([128, 128], 128, 256),
     ([5, 0, 9, 3, 7, 1, 6, 4], 64, 64),        # group sizes of modal/te_run.py:72 (an empty group)
@@ -46,7 +57,7 @@ CASES = [
 
 
 @pytest.mark.parametrize("gs,k_dim,n_dim", CASES)
-def test_grouped_gemm_nn_nt_tn(cuda, gs, k_dim, n_dim):
+def test_grouped_gemm_nn_nt_tn(cuda, cta_pair, gs, k_dim, n_dim):
   from lewi_surge_b200 import ops, _lib
   rng = np.random.default_rng(len(gs) * 1000 + k_dim + n_dim)
   e = len(gs)
@@ -59,19 +70,19 @@ def test_grouped_gemm_nn_nt_tn(cuda, gs, k_dim, n_dim):
   PO = to_dev(pad, torch.int32, cuda)
   want = expected_nn(a, b, pad)
   _lib.last_status()
-  got = ops.grouped_gemm_nn(A, B, BE, NB)
+  got = ops.grouped_gemm_nn(A, B, BE, NB, pad_offsets=PO)
   assert _lib.last_status() == 0
   assert O.rel_err(to_np(got), want) <= TOL
   assert np.all(to_np(got)[~valid] == 0)              # padding rows stay exact zeros
-  got32 = ops.grouped_gemm_nn(A, B, BE, NB, out_dtype=torch.float32)
+  got32 = ops.grouped_gemm_nn(A, B, BE, NB, out_dtype=torch.float32, pad_offsets=PO)
   assert O.rel_err(to_np(got32), want) <= 1e-4
   # nt: same product with the weight stored transposed [E,N,K]
   Bt = to_dev(np.ascontiguousarray(b.transpose(0, 2, 1)), torch.bfloat16, cuda)
-  got_nt = ops.grouped_gemm_nt(A, Bt, BE, NB, out_dtype=torch.float32)
+  got_nt = ops.grouped_gemm_nt(A, Bt, BE, NB, out_dtype=torch.float32, pad_offsets=PO)
   assert O.rel_err(to_np(got_nt), want) <= 1e-4
   # row scale in the epilogue
   sc = rng.standard_normal(a.shape[0]).astype(np.float32)
-  got_sc = ops.grouped_gemm_nn(A, B, BE, NB, out_dtype=torch.float32, row_scale=to_dev(sc, torch.float32, cuda))
+  got_sc = ops.grouped_gemm_nn(A, B, BE, NB, out_dtype=torch.float32, row_scale=to_dev(sc, torch.float32, cuda), pad_offsets=PO)
   assert O.rel_err(to_np(got_sc), want * sc[:, None]) <= 1e-4
   # tn: per-expert a^T . g
   g = np.zeros((a.shape[0], n_dim), np.float32)
@@ -86,22 +97,23 @@ def test_grouped_gemm_nn_nt_tn(cuda, gs, k_dim, n_dim):
   assert _lib.last_status() == 0
 
 
-def test_live_block_count_is_read_from_the_device(cuda):
-  """Blocks past *n_blocks are not touched."""
+def test_live_block_count_is_read_from_the_device(cuda, cta_pair):
+  """Blocks past the live count (n_blocks / the end of pad_offsets) are not touched."""
   from lewi_surge_b200 import ops
   rng = np.random.default_rng(1)
   a, pad, be, valid = padded_problem(rng, [128, 128, 128], 64)
   b = O.bf16_round(rng.standard_normal((3, 64, 64)))
   out = torch.full((384, 64), 7.0, dtype=torch.bfloat16, device=cuda)
   ops.grouped_gemm_nn(to_dev(a, torch.bfloat16, cuda), to_dev(b, torch.bfloat16, cuda), to_dev(be, torch.int32, cuda),
-                      torch.tensor([2], dtype=torch.int32, device=cuda), out=out)
+                      torch.tensor([2], dtype=torch.int32, device=cuda), out=out,
+                      pad_offsets=torch.tensor([0, 128, 256, 256], dtype=torch.int32, device=cuda))
   assert O.rel_err(to_np(out)[:256], expected_nn(a, b, pad)[:256]) <= TOL
   assert bool((out[256:] == 7.0).all())
 
 
 @pytest.mark.parametrize("gs,d,f", [([128], 64, 64), ([100, 0, 300], 256, 192), ([440, 318], 1024, 512),
                                      ([260], 2048, 768)])
-def test_swiglu_forward_and_backward_kernels(cuda, gs, d, f):
+def test_swiglu_forward_and_backward_kernels(cuda, cta_pair, gs, d, f):
   from lewi_surge_b200 import ops, layer, _lib
   rng = np.random.default_rng(d + f)
   e = len(gs)
@@ -114,7 +126,7 @@ def test_swiglu_forward_and_backward_kernels(cuda, gs, d, f):
   NB = torch.tensor([xs.shape[0] // 128], dtype=torch.int32, device=cuda)
   PO = to_dev(pad, torch.int32, cuda)
   _lib.last_status()
-  gu, h = layer.gateup_swiglu(XS, WG, WU, BE, NB)
+  gu, h = layer.gateup_swiglu(XS, WG, WU, BE, NB, pad_offsets=PO)
   g_want, u_want = expected_nn(xs, wg, pad), expected_nn(xs, wu, pad)
   h_want = O.silu(g_want) * u_want
   assert O.rel_err(to_np(gu)[:, :f], g_want) <= TOL and O.rel_err(to_np(gu)[:, f:], u_want) <= TOL
@@ -125,7 +137,7 @@ def test_swiglu_forward_and_backward_kernels(cuda, gs, d, f):
   dys = np.zeros_like(xs)
   dys[valid] = O.bf16_round(rng.standard_normal((int(valid.sum()), d)))
   DYS = to_dev(dys, torch.bfloat16, cuda)
-  dgu = layer.dh_dswiglu(DYS, WD, gu, BE, NB)
+  dgu = layer.dh_dswiglu(DYS, WD, gu, BE, NB, pad_offsets=PO)
   dh = np.zeros((xs.shape[0], f), np.float32)
   for x in range(e):
     dh[pad[x]: pad[x + 1]] = dys[pad[x]: pad[x + 1]] @ wd[x].T
@@ -133,7 +145,7 @@ def test_swiglu_forward_and_backward_kernels(cuda, gs, d, f):
   assert O.rel_err(to_np(dgu)[:, :f], dh * ub * O.dsilu(gb)) <= TOL
   assert O.rel_err(to_np(dgu)[:, f:], dh * O.silu(gb)) <= TOL
   dgu_np = to_np(dgu)
-  dxs = layer.dx_from_dgu(dgu, WG, WU, BE, NB)
+  dxs = layer.dx_from_dgu(dgu, WG, WU, BE, NB, pad_offsets=PO)
   want_dx = np.zeros_like(xs)
   for x in range(e):
     s = slice(pad[x], pad[x + 1])
@@ -149,7 +161,7 @@ def test_swiglu_forward_and_backward_kernels(cuda, gs, d, f):
   assert _lib.last_status() == 0
 
 
-def test_single_group_with_ragged_row_count(cuda):
+def test_single_group_with_ragged_row_count(cuda, cta_pair):
   """The shared-expert form: one group, row count not a multiple of 128, no block table."""
   from lewi_surge_b200 import ops, layer
   rng = np.random.default_rng(2)
@@ -166,7 +178,7 @@ def test_single_group_with_ragged_row_count(cuda):
 
 
 @pytest.mark.parametrize("t,ma,nb,split", [(4096, 128, 128, False), (5000, 256, 512, True), (32768, 512, 1024, False)])
-def test_single_group_long_contraction_is_split(cuda, t, ma, nb, split):
+def test_single_group_long_contraction_is_split(cuda, cta_pair, t, ma, nb, split):
   """One group with many rows: the contraction is cut into parts and summed in a fixed order."""
   from lewi_surge_b200 import ops, _lib
   assert _lib.load().lewi_grouped_gemm_tn_workspace_bytes(t, ma, nb, 1, int(split)) > 0
@@ -232,8 +244,8 @@ def test_full_size_linearity_config2(cuda):
   xs = torch.zeros((tb.mpad, d), dtype=torch.bfloat16, device=cuda)
   ops.gather_rows(x, tb.row_slot, idx_div=k, out=xs, n_rows_dev=tb.n_blocks, rows_per_unit=128)
   w = (torch.randn((e, d, f), generator=g) * 0.02).to(torch.bfloat16).to(cuda)
-  y1 = ops.grouped_gemm_nn(xs, w, tb.block_expert, tb.n_blocks)
-  y2 = ops.grouped_gemm_nn(xs * 2, w, tb.block_expert, tb.n_blocks)
+  y1 = ops.grouped_gemm_nn(xs, w, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
+  y2 = ops.grouped_gemm_nn(xs * 2, w, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
   nb = int(tb.n_blocks.item())
   assert torch.equal(y2[: nb * 128].float(), y1[: nb * 128].float() * 2)
   # spot-check 16 random valid rows against a float64 product with the expert the table names
