@@ -228,6 +228,10 @@ int lewi_debug_set_desc(int k_lbo, int k_sbo, int k_step, int mn_lbo, int mn_sbo
 /* Bring-up hook: 0 forces the single-CTA GEMM kernels everywhere, 1 (default) allows CTA pairs. */
 int lewi_debug_set_cta_pair(int on);
 
+/* Bring-up hook for timing experiments: bit 0 epilogue without global I/O, bit 1 epilogue only returns the
+ * accumulator, bit 2 producer skips the B operand.  Any non-zero value makes results wrong; default 0. */
+int lewi_debug_set_flags(int flags);
+
 #ifdef __cplusplus
 }
 #endif

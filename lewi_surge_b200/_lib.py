@@ -44,6 +44,7 @@ SIGNATURES = {
     "lewi_grouped_gemm_dh_dswiglu": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dx": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_debug_set_cta_pair": (c_int, [c_int]),
+    "lewi_debug_set_flags": (c_int, [c_int]),
     "lewi_debug_set_desc": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
 }
 

@@ -70,6 +70,8 @@ struct Args {
   int k_splits;                 // TN: the contraction of every output tile is cut into this many parts
   float* partial;               // TN with k_splits > 1: f32 partial products [k_splits, E, Ma, N]
   const float* col_bias;        // PLAIN: optional f32 per output column
+  int dbg;                      // bring-up experiments only (0 in production): 1 no global I/O in the epilogue,
+                                // 2 epilogue only hands the accumulator back, 4 the producer skips the B operand
   uint64_t desc_hi_a, desc_hi_b;
   uint32_t kstep_a, kstep_b;    // bytes to advance the descriptor start per 16-wide k step
   uint32_t idesc;
@@ -344,12 +346,15 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const uint32_t ph = (it / STAGES) & 1u;
           if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-          if (leader) ptx::mbar_expect_tx(full_bar(s), PAIR ? 2 * STAGE_BYTES : STAGE_BYTES);
+          const bool skip_b = (a.dbg & 4) != 0;
+          const uint32_t cta_bytes = skip_b ? A_BYTES : STAGE_BYTES;
+          if (leader) ptx::mbar_expect_tx(full_bar(s), PAIR ? 2 * cta_bytes : cta_bytes);
           const uint32_t fb = full_target(s);
           auto load2 = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1) {
             if constexpr (PAIR) ptx::tma_load_2d_pair(dst, tm, fb, c0, c1); else ptx::tma_load_2d(dst, tm, fb, c0, c1);
           };
           auto load3 = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2) {
+            if (skip_b) return;   // every 3-D load is a B-operand load
             if constexpr (PAIR) ptx::tma_load_3d_pair(dst, tm, fb, c0, c1, c2); else ptx::tma_load_3d(dst, tm, fb, c0, c1, c2);
           };
           const int nb0 = t.n0 + (PAIR ? (int)cta_rank * (BN / 2) : 0);   // first B column/row held by this CTA
@@ -359,7 +364,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll
             for (int c = 0; c < 2; ++c) load2(sa + c * CHUNK_BYTES, &tm_a, ma0 + 64 * c, r);
 #pragma unroll
-            for (int c = 0; c < B_CHUNKS; ++c) load2(sb + c * CHUNK_BYTES, &tm_b, nb0 + 64 * c, r);
+            for (int c = 0; c < B_CHUNKS; ++c)
+              if (!skip_b) load2(sb + c * CHUNK_BYTES, &tm_b, nb0 + 64 * c, r);
           } else {
             int ka = kb * BK;
             if constexpr (MAJOR == NN) {
@@ -460,6 +466,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const long long row_lim = MAJOR == TN ? (long long)a.Ma : a.rows;
       int rows_valid = (int)max(0LL, min(32LL, row_lim - wrow0));
       if (MAJOR != TN && cta_rank == 1 && !t.second) rows_valid = 0;   // this CTA's block belongs to the next expert
+      if (a.dbg & 3) rows_valid = 0;
+      const int n_end = (a.dbg & 2) ? 0 : t.nlim;
 
       // DSWIGLU: the first block of g/u is fetched before the accumulator is waited for
       [[maybe_unused]] uint4 pg[4], pu[4];
@@ -489,7 +497,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll 1
         for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
           const int n = t.n0 + c * 32;
-          if (n >= a.N) break;  // uniform across the warp
+          if (n >= n_end) break;  // uniform across the warp
           const int cv = min(32, a.N - n);
           uint32_t r[32];
           float v[32];
@@ -511,7 +519,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll 1
         for (int c = col_half * 2; c < col_half * 2 + 2; ++c) {
           const int n = t.n0 + c * 32;
-          if (n >= f) break;
+          if (n >= n_end) break;
           const int cv = min(32, f - n);
           uint32_t rg[32], ru[32];
           if (has_acc) {
@@ -541,7 +549,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         for (int ci = 0; ci < 4; ++ci) {
           const int c = col_half * 4 + ci;
           const int n = t.n0 + c * 32;
-          if (n < f) {  // uniform across the warp
+          if (n < n_end) {  // uniform across the warp
             const int cv = min(32, f - n);
             float g[32], u[32];
             warp_own_row32_bf16(stage, lane, pg, g);
@@ -573,7 +581,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 #pragma unroll 1
         for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
           const int n = t.n0 + c * 32;
-          if (n >= t.nlim) break;
+          if (n >= n_end) break;
           const int cv = min(32, t.nlim - n);
           uint32_t r[32];
           float v[32];

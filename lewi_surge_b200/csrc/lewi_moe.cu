@@ -249,6 +249,8 @@ int lewi_gather_dot(void* stream, const void* y, const int32_t* pos, const void*
 
 namespace {
 
+int g_debug_flags = 0;
+
 struct RowGroupArgs {
   const int32_t* block_expert;
   const int32_t* n_blocks;
@@ -295,6 +297,7 @@ inline void fill_common(gg::Args& a, const RowGroupArgs& r) {
   a.k_splits = 1;
   a.partial = nullptr;
   a.col_bias = nullptr;
+  a.dbg = g_debug_flags;
 }
 
 // Number of contraction parts for a TN product with `tiles0` output tiles (1 = no split).
@@ -554,6 +557,12 @@ int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, cons
 // Bring-up hook: 0 forces the single-CTA (cta_group::1) GEMM kernels, 1 (default) allows CTA pairs.
 int lewi_debug_set_cta_pair(int on) {
   gg::pair_mode() = on != 0;
+  return LEWI_OK;
+}
+
+// Bring-up hook: timing experiments that switch off parts of the GEMM kernels (results become wrong).
+int lewi_debug_set_flags(int flags) {
+  g_debug_flags = flags;
   return LEWI_OK;
 }
 
