@@ -53,6 +53,7 @@ def kernel_work(c):
       "combine_gather_reduce": ("hbm", (m + 2 * T) * row),
       "combine_bwd_gather_dot": ("hbm", (m + T) * row + 4 * m),
       "combine_bwd_scaled_gather": ("hbm", (T + m) * row),
+      "combine_bwd_gather": ("hbm", (T + m) * row),
       "gemm_dh_dswiglu": ("tensor", 2 * m * d * f),
       "gemm_dw_down": ("tensor", 2 * m * d * f),
       "gemm_dx": ("tensor", 4 * m * d * f),
@@ -176,8 +177,12 @@ def run_reference(args, c, rank, world):
   cores = os.cpu_count() or 1
   sample = min(c["T"], 4096)
   step = cpu_oracle_step(c, sample)
-  for _ in range(min(args.warmup, 1)):
-    step()
+  t1 = step()                       # warm-up, also sizes the sample: the whole run should stay within ~2.5 minutes
+  budget = 150.0
+  while sample > 256 and t1 * args.steps > budget:
+    sample //= 2
+    step = cpu_oracle_step(c, sample)
+    t1 = step()
   times = [step() for _ in range(args.steps)]
   dt = sum(times) / len(times)
   val = sample / dt
@@ -367,11 +372,10 @@ def main():
                 "ms_per_launch": dk["ms"]}
   gemm_ms = sum(ms for n, ms in kernels.items() if work.get(n, ("", 0))[0] == "tensor" and n not in overlapped)
   gemm_flops = sum(work[n][1] for n in kernels if work.get(n, ("", 0))[0] == "tensor" and n not in overlapped)
-  mem_ms = sum(ms for n, ms in kernels.items() if n in ("dispatch_gather", "combine_gather_reduce",
-                                                         "combine_bwd_gather_dot", "combine_bwd_scaled_gather",
-                                                         "dispatch_bwd_gather_reduce"))
-  mem_bytes = sum(work[n][1] for n in ("dispatch_gather", "combine_gather_reduce", "combine_bwd_gather_dot",
-                                       "combine_bwd_scaled_gather", "dispatch_bwd_gather_reduce") if n in kernels)
+  mem_names = ("dispatch_gather", "combine_gather_reduce", "combine_bwd_gather_dot", "combine_bwd_scaled_gather",
+               "combine_bwd_gather", "dispatch_bwd_gather_reduce")
+  mem_ms = sum(ms for n, ms in kernels.items() if n in mem_names)
+  mem_bytes = sum(work[n][1] for n in mem_names if n in kernels)
   summary = {
       "layer_tflops": round(layer_flops(c) / (ms_step * 1e-3) / 1e12, 1),
       "layer_frac_of_bf16_peak": round(layer_flops(c) / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], 4),

@@ -127,6 +127,13 @@ int lewi_sort_indices(void* stream, const int32_t* flat_experts, int64_t M, int 
 int lewi_router_topk_bwd(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
                          float* dlogits, void* dlogits_bf16, int64_t T, int E, int k);
 
+/* Same, with the routing-weight gradient given as pieces: dw[t,j] = sum_p dw_partial[pad_pos[t*k+j], p]
+ * (the pieces are written by lewi_grouped_gemm_dh_dswiglu_gather).  dw may then be null; dw_out [T,k]
+ * (optional) receives the summed gradient. */
+int lewi_router_topk_bwd_partial(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
+                                 const float* dw_partial, int dw_parts, const int32_t* pad_pos, float* dw_out,
+                                 float* dlogits, void* dlogits_bf16, int64_t T, int E, int k);
+
 /* dst (bf16) = round-to-nearest-even(src (f32)), n elements.  Used for the bf16 copy of the f32 router
  * weight (the reference casts rhs to the lhs dtype before its GEMMs: modal/padded_gmm.py:67). */
 int lewi_cast_f32_to_bf16(void* stream, const float* src, void* dst, int64_t n);
@@ -209,12 +216,49 @@ int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_
                                     const int32_t* block_expert, const int32_t* n_blocks,
                                     const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
 
+/* lewi_grouped_gemm_gateup_swiglu with the dispatch gather fused into the operand load: xs is the
+ * UNPERMUTED source [src_rows,d]; padded row r reads xs[row_idx[r] / idx_div] (row_idx[r] < 0: zero row),
+ * i.e. row_idx = row_slot and idx_div = k replace `_route_activations` (modal/moe_permute.py:399-404)
+ * without materialising the permuted rows (row_idx null: xs is already in padded order).
+ * h_scale_src (optional, f32 indexed by scale_idx[r]; scale_idx defaults to row_idx) multiplies h: with
+ * the router weights there, the down projection yields already-weighted expert outputs and the combine
+ * needs no weights.  Measured note: the in-kernel row gather is correct but slower than gathering first
+ * on B200; the scale is free. */
+int lewi_grouped_gemm_gateup_swiglu_gather(void* stream, const void* xs, const int32_t* row_idx, int idx_div,
+                                           int64_t src_rows, const int32_t* scale_idx,
+                                           const float* h_scale_src, const void* w_gate,
+                                           const void* w_up, void* gu, void* h,
+                                           const int32_t* block_expert, const int32_t* n_blocks,
+                                           const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
+
 /* Backward of the down projection fused with the SwiGLU derivative:
  * dh = dys.Wd[e]^T; dg = dh*u*silu'(g); du = dh*silu(g).  dys [rows,d], w_down [E,f,d],
  * gu [rows,2f], dgu [rows,2f] (dg | du). */
 int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_down, const void* gu,
                                  void* dgu, const int32_t* block_expert, const int32_t* n_blocks,
                                  const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
+
+/* Same with the upstream-gradient gather fused in (dys [src_rows,d] unpermuted, picked through row_idx /
+ * idx_div; null: dys is in padded order), dh multiplied by scale_src[scale_idx[r]] (the router weight;
+ * scale_idx defaults to row_idx), and, if dw_partial is not null,
+ * dw_partial[r, p] = sum over a column range of dh_unscaled * silu(g) * u: the pieces of the routing-weight
+ * gradient <dout[t], y[row]> (reference: gather_dot in `_combine_bwd`, modal/moe_permute.py:303-309).
+ * dw_partial is [rows, lewi_dw_partial_parts(f)] f32. */
+int lewi_dw_partial_parts(int f);
+int lewi_grouped_gemm_dh_dswiglu_gather(void* stream, const void* dys, const int32_t* row_idx, int idx_div,
+                                        int64_t src_rows, const int32_t* scale_idx,
+                                        const float* scale_src, float* dw_partial,
+                                        const void* w_down, const void* gu, void* dgu,
+                                        const int32_t* block_expert, const int32_t* n_blocks,
+                                        const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
+
+/* lewi_grouped_gemm_tn where the contraction rows of a and/or b are picked through row_idx / idx_div
+ * from an unpermuted source of src_rows rows (gather_a / gather_b non-zero). */
+int lewi_grouped_gemm_tn_gather(void* stream, const void* a, const void* b, void* out, void* out2,
+                                const int32_t* pad_offsets, int64_t rows, int Ma, int Nb, int E,
+                                int out_dtype, void* workspace, int64_t workspace_bytes,
+                                const int32_t* row_idx, int idx_div, int64_t src_rows, int gather_a,
+                                int gather_b);
 
 /* dxs = dg.Wg[e]^T + du.Wu[e]^T.  dgu [rows,2f], w_gate/w_up [E,d,f], dxs [rows,d] bf16. */
 int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, const void* w_up,

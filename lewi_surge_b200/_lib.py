@@ -32,6 +32,11 @@ SIGNATURES = {
     "lewi_sort_indices": (c_int, [P, P, c_int64, c_int, c_int, P, P, P, P, P, P, P, P, P, P, c_int64]),
     "lewi_router_topk_bwd": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int]),
     "lewi_cast_f32_to_bf16": (c_int, [P, P, P, c_int64]),
+    "lewi_router_topk_bwd_partial": (c_int, [P, P, P, P, P, c_int, P, P, P, P, c_int64, c_int, c_int]),
+    "lewi_grouped_gemm_gateup_swiglu_gather": (c_int, [P, P, P, c_int, c_int64, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_dw_partial_parts": (c_int, [c_int]),
+    "lewi_grouped_gemm_dh_dswiglu_gather": (c_int, [P, P, P, c_int, c_int64, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_grouped_gemm_tn_gather": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, P, c_int64, P, c_int, c_int64, c_int, c_int]),
     "lewi_group_tables": (c_int, [P, P, c_int64, c_int, c_int, P, P, P, P, P]),
     "lewi_gather_rows": (c_int, [P, P, P, P, P, c_int64, c_int64, c_int, c_int, c_int, c_int, P, c_int]),
     "lewi_gather_reduce": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64]),

@@ -126,16 +126,25 @@ int lewi_sort_indices(void* stream, const int32_t* flat_experts, int64_t M, int 
 
 int lewi_router_topk_bwd(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
                          float* dlogits, void* dlogits_bf16, int64_t T, int E, int k) {
-  if (!logits || !topk_idx || !dw || (!dlogits && !dlogits_bf16) || T < 0 || E <= 0 || k <= 0) return LEWI_ERR_ARG;
+  return lewi_router_topk_bwd_partial(stream, logits, topk_idx, dw, nullptr, 0, nullptr, nullptr, dlogits, dlogits_bf16,
+                                      T, E, k);
+}
+
+int lewi_router_topk_bwd_partial(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
+                                 const float* dw_partial, int dw_parts, const int32_t* pad_pos, float* dw_out,
+                                 float* dlogits, void* dlogits_bf16, int64_t T, int E, int k) {
+  if (!logits || !topk_idx || (!dw && !dw_partial) || (!dlogits && !dlogits_bf16) || T < 0 || E <= 0 || k <= 0)
+    return LEWI_ERR_ARG;
+  if (dw_partial != nullptr && (dw_parts <= 0 || pad_pos == nullptr)) return LEWI_ERR_ARG;
   __nv_bfloat16* dlb = reinterpret_cast<__nv_bfloat16*>(dlogits_bf16);
   if (E > kMaxExperts || k > kMaxTopK || k > E) return LEWI_ERR_LIMIT;
   if (T == 0) return LEWI_OK;
   const int grid = gather_grid(T);
   cudaStream_t st = as_stream(stream);
-  if (E <= 64) router_topk_bwd_kernel<2><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dlogits, dlb, T, E, k);
-  else if (E <= 128) router_topk_bwd_kernel<4><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dlogits, dlb, T, E, k);
-  else if (E <= 256) router_topk_bwd_kernel<8><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dlogits, dlb, T, E, k);
-  else router_topk_bwd_kernel<16><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dlogits, dlb, T, E, k);
+  if (E <= 64) router_topk_bwd_kernel<2><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, dlb, T, E, k);
+  else if (E <= 128) router_topk_bwd_kernel<4><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, dlb, T, E, k);
+  else if (E <= 256) router_topk_bwd_kernel<8><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, dlb, T, E, k);
+  else router_topk_bwd_kernel<16><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, dlb, T, E, k);
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
 }
@@ -297,6 +306,17 @@ inline void fill_common(gg::Args& a, const RowGroupArgs& r) {
   a.k_splits = 1;
   a.partial = nullptr;
   a.col_bias = nullptr;
+  a.scale_src = nullptr;
+  a.scale_idx = nullptr;
+  a.dw_partial = nullptr;
+  a.dw_parts = 0;
+  a.ga_ptr = nullptr;
+  a.gb_ptr = nullptr;
+  a.ga_ld = 0;
+  a.gb_ld = 0;
+  a.g_idx = nullptr;
+  a.g_div = 1;
+  a.g_src_rows = 0;
   a.dbg = g_debug_flags;
 }
 
@@ -421,7 +441,17 @@ int64_t lewi_grouped_gemm_tn_workspace_bytes(int64_t rows, int Ma, int Nb, int E
 int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, void* out, void* out2,
                          const int32_t* pad_offsets, int64_t rows, int Ma, int Nb, int E, int out_dtype,
                          void* workspace, int64_t workspace_bytes) {
+  return lewi_grouped_gemm_tn_gather(stream, a_ptr, b_ptr, out, out2, pad_offsets, rows, Ma, Nb, E, out_dtype, workspace,
+                                     workspace_bytes, nullptr, 1, 0, 0, 0);
+}
+
+int lewi_grouped_gemm_tn_gather(void* stream, const void* a_ptr, const void* b_ptr, void* out, void* out2,
+                                const int32_t* pad_offsets, int64_t rows, int Ma, int Nb, int E, int out_dtype,
+                                void* workspace, int64_t workspace_bytes, const int32_t* row_idx, int idx_div,
+                                int64_t src_rows, int gather_a, int gather_b) {
   if (!a_ptr || !b_ptr || !out || Ma <= 0 || Nb <= 0 || rows < 0 || E <= 0) return LEWI_ERR_ARG;
+  if ((gather_a || gather_b) && (!row_idx || idx_div <= 0 || src_rows <= 0 || src_rows > 0x7fffffffLL))
+    return LEWI_ERR_ARG;
   if (out_dtype != LEWI_BF16 && out_dtype != LEWI_F32) return LEWI_ERR_ARG;
   if (rows > 0x7fffff00LL) return LEWI_ERR_LIMIT;
   if (Ma % 8 != 0 || Nb % 8 != 0 || !aligned16(a_ptr) || !aligned16(b_ptr) || !aligned16(out) || !aligned16(out2) ||
@@ -461,8 +491,17 @@ int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, voi
   a.k_splits = splits;
   a.partial = splits > 1 ? reinterpret_cast<float*>(workspace) : nullptr;
   CUtensorMap ta, tb;
-  if (!gg::make_map(&ta, a_ptr, (uint64_t)Ma, (uint64_t)rows, 0, 64, 64)) return LEWI_ERR_CUDA;
-  if (!gg::make_map(&tb, b_ptr, (uint64_t)Nb, (uint64_t)rows, 0, 64, 64)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&ta, a_ptr, (uint64_t)Ma, (uint64_t)(gather_a ? src_rows : rows), 0, 64, 64))
+    return LEWI_ERR_CUDA;
+  if (!gg::make_map(&tb, b_ptr, (uint64_t)Nb, (uint64_t)(gather_b ? src_rows : rows), 0, 64, 64))
+    return LEWI_ERR_CUDA;
+  if (gather_a || gather_b) {   // the contraction rows of that operand are picked through row_idx
+    a.g_idx = row_idx;
+    a.g_div = idx_div;
+    a.g_src_rows = (int)src_rows;
+    if (gather_a) { a.ga_ptr = a_ptr; a.ga_ld = Ma; }
+    if (gather_b) { a.gb_ptr = b_ptr; a.gb_ld = Nb; }
+  }
   if (int rc = gg::launch_auto<gg::TN, gg::TNOUT>(pair, st, ta, tb, tb, a, tiles0 * splits)) return rc;
   if (splits > 1) {
     const long long total4 = (long long)E * Ma * Nb / 4;
@@ -477,7 +516,20 @@ int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, voi
 int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_gate, const void* w_up, void* gu,
                                     void* h, const int32_t* block_expert, const int32_t* n_blocks,
                                     const int32_t* pad_offsets, int64_t rows, int d, int f, int E) {
+  return lewi_grouped_gemm_gateup_swiglu_gather(stream, xs, nullptr, 1, rows, nullptr, nullptr, w_gate, w_up, gu, h,
+                                                block_expert, n_blocks, pad_offsets, rows, d, f, E);
+}
+
+int lewi_grouped_gemm_gateup_swiglu_gather(void* stream, const void* xs, const int32_t* row_idx, int idx_div,
+                                           int64_t src_rows, const int32_t* scale_idx, const float* h_scale_src,
+                                           const void* w_gate,
+                                           const void* w_up, void* gu, void* h, const int32_t* block_expert,
+                                           const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows, int d,
+                                           int f, int E) {
   if (!xs || !w_gate || !w_up || !h || d <= 0 || f <= 0) return LEWI_ERR_ARG;
+  if (row_idx != nullptr && (idx_div <= 0 || src_rows <= 0 || src_rows > 0x7fffffffLL)) return LEWI_ERR_ARG;
+  if (scale_idx == nullptr) scale_idx = row_idx;
+  if (h_scale_src != nullptr && scale_idx == nullptr) return LEWI_ERR_ARG;
   RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
   const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
@@ -486,11 +538,21 @@ int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_
     return LEWI_ERR_SHAPE;
   if (rows == 0) return LEWI_OK;
   CUtensorMap ta, tb, tb2;
-  if (!gg::make_map(&ta, xs, (uint64_t)d, (uint64_t)rows, 0, 64, 128)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&ta, xs, (uint64_t)d, (uint64_t)(row_idx ? src_rows : rows), 0, 64, 128))
+    return LEWI_ERR_CUDA;
   if (!gg::make_map(&tb, w_gate, (uint64_t)f, (uint64_t)d, (uint64_t)E, 64, 64)) return LEWI_ERR_CUDA;
   if (!gg::make_map(&tb2, w_up, (uint64_t)f, (uint64_t)d, (uint64_t)E, 64, 64)) return LEWI_ERR_CUDA;
   gg::Args a;
   fill_common(a, r);
+  if (row_idx != nullptr) {   // rows of xs are picked through row_idx instead of being materialised first
+    a.ga_ptr = xs;
+    a.ga_ld = d;
+    a.g_idx = row_idx;
+    a.g_div = idx_div;
+    a.g_src_rows = (int)src_rows;
+  }
+  a.scale_src = h_scale_src;
+  a.scale_idx = scale_idx;
   a.out = h;
   a.out2 = gu;
   a.K = d;
@@ -503,7 +565,22 @@ int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_
 int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_down, const void* gu, void* dgu,
                                  const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets,
                                  int64_t rows, int d, int f, int E) {
+  return lewi_grouped_gemm_dh_dswiglu_gather(stream, dys, nullptr, 1, rows, nullptr, nullptr, nullptr, w_down, gu, dgu,
+                                             block_expert, n_blocks, pad_offsets, rows, d, f, E);
+}
+
+int lewi_dw_partial_parts(int f) { return f > 0 ? 2 * ((f + gg::BN - 1) / gg::BN) : LEWI_ERR_ARG; }
+
+int lewi_grouped_gemm_dh_dswiglu_gather(void* stream, const void* dys, const int32_t* row_idx, int idx_div,
+                                        int64_t src_rows, const int32_t* scale_idx, const float* scale_src,
+                                        float* dw_partial,
+                                        const void* w_down, const void* gu, void* dgu, const int32_t* block_expert,
+                                        const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows, int d,
+                                        int f, int E) {
   if (!dys || !w_down || !gu || !dgu || d <= 0 || f <= 0) return LEWI_ERR_ARG;
+  if (row_idx != nullptr && (idx_div <= 0 || src_rows <= 0 || src_rows > 0x7fffffffLL)) return LEWI_ERR_ARG;
+  if (scale_idx == nullptr) scale_idx = row_idx;
+  if (scale_src != nullptr && scale_idx == nullptr) return LEWI_ERR_ARG;
   RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
   const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
@@ -511,11 +588,23 @@ int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_do
     return LEWI_ERR_SHAPE;
   if (rows == 0) return LEWI_OK;
   CUtensorMap ta, tb;
-  if (!gg::make_map(&ta, dys, (uint64_t)d, (uint64_t)rows, 0, 64, 128)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&ta, dys, (uint64_t)d, (uint64_t)(row_idx ? src_rows : rows), 0, 64, 128))
+    return LEWI_ERR_CUDA;
   // w_down [E,f,d]: as the K-major B operand of dh[rows,f] = dys[rows,d] . w_down[e]^T
   if (!gg::make_map(&tb, w_down, (uint64_t)d, (uint64_t)f, (uint64_t)E, 64, pair ? 128 : 256)) return LEWI_ERR_CUDA;
   gg::Args a;
   fill_common(a, r);
+  if (row_idx != nullptr) {
+    a.ga_ptr = dys;
+    a.ga_ld = d;
+    a.g_idx = row_idx;
+    a.g_div = idx_div;
+    a.g_src_rows = (int)src_rows;
+  }
+  a.scale_src = scale_src;
+  a.scale_idx = scale_idx;
+  a.dw_partial = dw_partial;
+  a.dw_parts = lewi_dw_partial_parts(f);
   a.out = dgu;
   a.gu = reinterpret_cast<const __nv_bfloat16*>(gu);
   a.K = d;
@@ -562,7 +651,8 @@ int lewi_debug_set_cta_pair(int on) {
 
 // Bring-up hook: timing experiments that switch off parts of the GEMM kernels (results become wrong).
 int lewi_debug_set_flags(int flags) {
-  g_debug_flags = flags;
+  g_debug_flags = flags & 7;
+  route_wide() = (flags & 8) != 0;
   return LEWI_OK;
 }
 

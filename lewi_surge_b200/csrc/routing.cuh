@@ -17,6 +17,7 @@ namespace lewi {
 
 constexpr int kRouteThreads = 256;
 constexpr int kRouteWarps = kRouteThreads / kWarp;
+constexpr int kRouteTopkThreads = 1024;  // the soft-max/top-k phase uses 32 warps; histogram phases use the first 8
 constexpr int kRouteChunkTokens = 128;  // tokens per chunk when fed logits
 constexpr int kSortChunkSlots = 1024;   // slots per chunk when fed expert ids
 constexpr int kMaxExperts = 512;
@@ -126,7 +127,7 @@ struct RouteChunkArgs {
 };
 
 template <int ER>
-__global__ void __launch_bounds__(kRouteThreads) route_chunk_kernel(RouteChunkArgs a) {
+__global__ void __launch_bounds__(kRouteTopkThreads) route_chunk_kernel(RouteChunkArgs a) {
   extern __shared__ int s_mem[];
   int* s_e = s_mem;                                 // [chunk_slots]
   int* s_run = s_mem + a.chunk_slots;               // [kRouteWarps][E]
@@ -136,9 +137,10 @@ __global__ void __launch_bounds__(kRouteThreads) route_chunk_kernel(RouteChunkAr
   const long long slot0 = chunk * a.chunk_slots;
   const int n_slots = (int)min((long long)a.chunk_slots, a.num_slots - slot0);
 
-  for (int i = tid; i < kRouteWarps * a.E; i += kRouteThreads) s_run[i] = 0;
+  const int nthreads = blockDim.x, nwarps = blockDim.x >> 5;
+  for (int i = tid; i < kRouteWarps * a.E; i += nthreads) s_run[i] = 0;
   if (a.row_slot != nullptr) {
-    for (long long r = (long long)blockIdx.x * kRouteThreads + tid; r < a.mpad; r += (long long)gridDim.x * kRouteThreads)
+    for (long long r = (long long)blockIdx.x * nthreads + tid; r < a.mpad; r += (long long)gridDim.x * nthreads)
       a.row_slot[r] = -1;
   }
 
@@ -148,7 +150,7 @@ __global__ void __launch_bounds__(kRouteThreads) route_chunk_kernel(RouteChunkAr
     for (int r = 0; r < ER; ++r) pacc[r] = 0.f;
     const int n_tok = n_slots / a.k;
     const long long tok0 = slot0 / a.k;
-    for (int t = warp; t < n_tok; t += kRouteWarps) {
+    for (int t = warp; t < n_tok; t += nwarps) {
       float p[ER];
       int idx;
       float w;
@@ -163,14 +165,23 @@ __global__ void __launch_bounds__(kRouteThreads) route_chunk_kernel(RouteChunkAr
       }
     }
     if (a.chunk_probs != nullptr) {
+      // warps w, w+8, w+16, ... fold their column sums into row w % 8 one after the other (fixed order)
+      for (int round = 0; round * kRouteWarps < nwarps; ++round) {
+        if (warp / kRouteWarps == round) {
 #pragma unroll
-      for (int r = 0; r < ER; ++r) {
-        int e = lane + r * kWarp;
-        if (e < a.E) s_prob[warp * a.E + e] = pacc[r];
+          for (int r = 0; r < ER; ++r) {
+            int e = lane + r * kWarp;
+            if (e < a.E) {
+              float* dst = &s_prob[(warp % kRouteWarps) * a.E + e];
+              *dst = (round == 0 ? 0.f : *dst) + pacc[r];
+            }
+          }
+        }
+        __syncthreads();
       }
     }
   } else {
-    for (int i = tid; i < n_slots; i += kRouteThreads) {
+    for (int i = tid; i < n_slots; i += nthreads) {
       int e = a.flat_in[slot0 + i];
       if (e < 0 || e >= a.E) {
         raise_status(LEWI_STATUS_BAD_INDEX);
@@ -182,18 +193,20 @@ __global__ void __launch_bounds__(kRouteThreads) route_chunk_kernel(RouteChunkAr
   __syncthreads();
 
   const int spw = ((a.chunk_slots + kRouteWarps - 1) / kRouteWarps + kWarp - 1) / kWarp * kWarp;
-  const int begin = min(warp * spw, n_slots), end = min(begin + spw, n_slots);
-  warp_histogram(s_e, begin, end, s_run + warp * a.E, lane);
+  if (warp < kRouteWarps) {
+    const int begin = min(warp * spw, n_slots), end = min(begin + spw, n_slots);
+    warp_histogram(s_e, begin, end, s_run + warp * a.E, lane);
+  }
   __syncthreads();
-  for (int e = tid; e < a.E; e += kRouteThreads) {
+  for (int e = tid; e < a.E; e += nthreads) {
     int tot = 0;
 #pragma unroll
     for (int w = 0; w < kRouteWarps; ++w) tot += s_run[w * a.E + e];
     a.chunk_hist[chunk * a.E + e] = tot;
     if (a.logits != nullptr && a.chunk_probs != nullptr) {
       float ps = 0.f;
-#pragma unroll
-      for (int w = 0; w < kRouteWarps; ++w) ps += s_prob[w * a.E + e];
+      const int rows = min(nwarps, kRouteWarps);
+      for (int w = 0; w < rows; ++w) ps += s_prob[w * a.E + e];
       a.chunk_probs[chunk * a.E + e] = ps;
     }
   }
@@ -280,10 +293,18 @@ __global__ void __launch_bounds__(kScanThreads) route_scan_kernel(RouteScanArgs 
     }
   }
   if (a.probs_sum != nullptr && a.chunk_probs != nullptr) {
-    for (int x = tid; x < a.E; x += kScanThreads) {
-      float s = 0.f;
-      for (int c = 0; c < a.n_chunks; ++c) s += a.chunk_probs[(long long)c * a.E + x];
-      a.probs_sum[x] = s;
+    // same (expert, part) split as the histogram; parts are added in a fixed order
+    __syncthreads();
+    float ps = 0.f;
+    if (active) {
+      for (int c = c0; c < c1; ++c) ps += a.chunk_probs[(long long)c * a.E + e];
+    }
+    s_part[tid] = __float_as_int(active ? ps : 0.f);
+    __syncthreads();
+    if (tid < a.E) {
+      float tot_p = 0.f;
+      for (int q = 0; q < P; ++q) tot_p += __int_as_float(s_part[q * a.E + tid]);
+      a.probs_sum[tid] = tot_p;
     }
   }
 }
@@ -361,6 +382,9 @@ template <int ER>
 __global__ void __launch_bounds__(256) router_topk_bwd_kernel(const float* __restrict__ logits,
                                                               const int32_t* __restrict__ topk_idx,
                                                               const float* __restrict__ dw,
+                                                              const float* __restrict__ dw_partial, int dw_parts,
+                                                              const int32_t* __restrict__ pad_pos,
+                                                              float* __restrict__ dw_out,
                                                               float* __restrict__ dlogits,
                                                               __nv_bfloat16* __restrict__ dlogits_bf16, long long T,
                                                               int E, int k) {
@@ -395,7 +419,13 @@ __global__ void __launch_bounds__(256) router_topk_bwd_kernel(const float* __res
       my_e = topk_idx[t * k + lane];
       my_e = min(max(my_e, 0), E - 1);
       my_v = expf(row[my_e] - mx) * inv;
-      my_dw = dw[t * k + lane];
+      if (dw != nullptr) {
+        my_dw = dw[t * k + lane];
+      } else {  // the routing-weight gradient arrives as per-row pieces written by the dH GEMM's epilogue
+        const long long pr = pad_pos[t * k + lane];
+        for (int p = 0; p < dw_parts; ++p) my_dw += dw_partial[pr * dw_parts + p];
+      }
+      if (dw_out != nullptr) dw_out[t * k + lane] = my_dw;
     }
     const float S = warp_sum(my_v);
     const float wj = my_v / S;
@@ -518,13 +548,20 @@ __global__ void __launch_bounds__(256) split3_bf16_kernel(const float* __restric
 
 // ------------------------------------------------------------------------------------------------ host
 
+// Bring-up switch: run the soft-max/top-k phase with 32 warps per CTA instead of 8 (measured: no gain, and
+// 1024-thread CTAs cannot share an SM with a GEMM CTA).
+inline bool& route_wide() {
+  static bool v = false;
+  return v;
+}
+
 inline int route_n_chunks(long long num_slots, int chunk_slots) {
   return (int)((num_slots + chunk_slots - 1) / chunk_slots);
 }
 
 template <int ER>
 inline void launch_route_chunk(cudaStream_t st, const RouteChunkArgs& a, int n_chunks, size_t smem) {
-  route_chunk_kernel<ER><<<n_chunks, kRouteThreads, smem, st>>>(a);
+  route_chunk_kernel<ER><<<n_chunks, (a.logits && route_wide()) ? kRouteTopkThreads : kRouteThreads, smem, st>>>(a);
 }
 
 inline int route_common(cudaStream_t st, const float* logits, const int32_t* flat_in, long long T, long long M,

@@ -45,6 +45,14 @@ def _mark(name):
 # The shared expert depends only on x (forward) / dout (backward), so it runs on a side stream next to the
 # memory-bound routing and gather kernels of the routed path and is joined before the combine.
 OVERLAP_SHARED = True
+# Carry the router weight through h (the down projection then yields weighted outputs and the combine needs no
+# weights), scale dh by it in the dH epilogue and take the routing-weight gradient from that epilogue instead of a
+# separate gather_dot pass.
+FUSED_EPILOGUE = True
+# Additionally pick the rows of x / dout inside the GEMM producer warp instead of materialising permuted copies.
+# Correct (bit-identical) but measured 3-5x slower on B200: one producer warp cannot keep enough 16-byte copies in
+# flight, and TMA gather4 moves only ~85 rows per microsecond per SM.  Kept for experiments, off by default.
+FUSED_GATHER = False
 _SIDE = {}
 
 
@@ -155,15 +163,23 @@ def router_topk(logits, k, block=BLOCK):
   return tb
 
 
-def router_topk_bwd(logits, topk_idx, dw, want_f32=True, want_bf16=False):
+def router_topk_bwd(logits, topk_idx, dw, want_f32=True, want_bf16=False, dw_partial=None, pad_pos=None):
+  """dlogits (f32 and/or bf16).  ``dw`` [T,k], or its pieces ``dw_partial`` [rows,parts] + ``pad_pos``; in
+  the latter case the summed dw is returned as a third value."""
   lib = _lib.load()
   t, e = logits.shape
   k = topk_idx.shape[1]
   dl = torch.empty_like(logits) if want_f32 else None
   dlb = torch.empty((t, e), dtype=torch.bfloat16, device=logits.device) if want_bf16 else None
-  check(lib.lewi_router_topk_bwd(stream(), ptr(logits), ptr(topk_idx), ptr(dw.contiguous()), ptr(dl), ptr(dlb), t, e, k),
-        "lewi_router_topk_bwd")
-  return dl, dlb
+  if dw_partial is None:
+    check(lib.lewi_router_topk_bwd(stream(), ptr(logits), ptr(topk_idx), ptr(dw.contiguous()), ptr(dl), ptr(dlb), t, e, k),
+          "lewi_router_topk_bwd")
+    return dl, dlb
+  dw_out = torch.empty((t, k), dtype=torch.float32, device=logits.device)
+  check(lib.lewi_router_topk_bwd_partial(stream(), ptr(logits), ptr(topk_idx), None, ptr(dw_partial),
+                                         dw_partial.shape[1], ptr(pad_pos), ptr(dw_out), ptr(dl), ptr(dlb), t, e, k),
+        "lewi_router_topk_bwd_partial")
+  return dl, dlb, dw_out
 
 
 def cast_bf16(src):
@@ -173,27 +189,44 @@ def cast_bf16(src):
   return dst
 
 
-def gateup_swiglu(xs, w_gate, w_up, block_expert, n_blocks, want_gu=True, pad_offsets=None):
-  """(gu [rows,2f], h [rows,f]) = fused gate/up projection + SwiGLU over the padded rows."""
+def gateup_swiglu(xs, w_gate, w_up, block_expert, n_blocks, want_gu=True, pad_offsets=None, row_idx=None, idx_div=1,
+                  rows=None, h_scale_src=None, scale_idx=None):
+  """(gu [rows,2f], h [rows,f]) = fused gate/up projection + SwiGLU over the padded rows.
+
+  With ``row_idx`` the dispatch gather is fused in: ``xs`` is the unpermuted source, padded row r reads
+  ``xs[row_idx[r] // idx_div]`` and ``rows`` is the padded row count; ``h_scale_src[row_idx[r]]`` scales h."""
   lib = _lib.load()
-  rows, d = xs.shape
-  e, _, f = w_gate.shape
+  e, d, f = w_gate.shape
+  src_rows = xs.shape[0]
+  rows = src_rows if row_idx is None else int(rows)
   gu = torch.empty((rows, 2 * f), dtype=torch.bfloat16, device=xs.device) if want_gu else None
   h = torch.empty((rows, f), dtype=torch.bfloat16, device=xs.device)
-  check(lib.lewi_grouped_gemm_gateup_swiglu(stream(), ptr(xs), ptr(w_gate), ptr(w_up), ptr(gu), ptr(h),
-                                            ptr(block_expert), ptr(n_blocks), ptr(pad_offsets), rows, d, f, e),
+  check(lib.lewi_grouped_gemm_gateup_swiglu_gather(stream(), ptr(xs), ptr(row_idx), int(idx_div), src_rows,
+                                                   ptr(scale_idx), ptr(h_scale_src), ptr(w_gate), ptr(w_up), ptr(gu), ptr(h),
+                                                   ptr(block_expert), ptr(n_blocks), ptr(pad_offsets), rows, d, f, e),
         "lewi_grouped_gemm_gateup_swiglu")
   return gu, h
 
 
-def dh_dswiglu(dys, w_down, gu, block_expert, n_blocks, pad_offsets=None):
+def dh_dswiglu(dys, w_down, gu, block_expert, n_blocks, pad_offsets=None, row_idx=None, idx_div=1, scale_src=None,
+               want_dw_partial=False, scale_idx=None):
+  """dgu [rows,2f] = SwiGLU'(gu) applied to dh = dys . w_down[e]^T.
+
+  With ``row_idx`` the upstream-gradient gather is fused in (``dys`` is the unpermuted [T,d] gradient),
+  ``scale_src[row_idx[r]]`` multiplies dh, and ``want_dw_partial`` also returns the routing-weight
+  gradient pieces [rows, parts] f32."""
   lib = _lib.load()
-  rows, d = dys.shape
-  e, f, _ = w_down.shape
+  e, f, d = w_down.shape
+  rows = gu.shape[0]
   dgu = torch.empty((rows, 2 * f), dtype=torch.bfloat16, device=dys.device)
-  check(lib.lewi_grouped_gemm_dh_dswiglu(stream(), ptr(dys), ptr(w_down), ptr(gu), ptr(dgu), ptr(block_expert),
-                                         ptr(n_blocks), ptr(pad_offsets), rows, d, f, e), "lewi_grouped_gemm_dh_dswiglu")
-  return dgu
+  dwp = None
+  if want_dw_partial:
+    dwp = torch.empty((rows, int(lib.lewi_dw_partial_parts(f))), dtype=torch.float32, device=dys.device)
+  check(lib.lewi_grouped_gemm_dh_dswiglu_gather(stream(), ptr(dys), ptr(row_idx), int(idx_div), dys.shape[0],
+                                                ptr(scale_idx), ptr(scale_src), ptr(dwp), ptr(w_down), ptr(gu), ptr(dgu),
+                                                ptr(block_expert), ptr(n_blocks), ptr(pad_offsets), rows, d, f, e),
+        "lewi_grouped_gemm_dh_dswiglu")
+  return (dgu, dwp) if want_dw_partial else dgu
 
 
 def dx_from_dgu(dgu, w_gate, w_up, block_expert, n_blocks, pad_offsets=None):
@@ -218,6 +251,7 @@ class LayerCache:
   gus: Optional[torch.Tensor]
   hs: Optional[torch.Tensor]
   k: int
+  fused: bool = False
 
 
 def moe_layer_fwd(x, w: MoEWeights, k, logits=None):
@@ -237,17 +271,26 @@ def moe_layer_fwd(x, w: MoEWeights, k, logits=None):
   tb = router_topk(logits, k)
   _mark("router_topk")
   # dispatch: padded row r holds token row_slot[r] // k (zero row where row_slot[r] < 0)
-  xs = torch.empty((tb.mpad, d), dtype=x.dtype, device=x.device)
-  ops.gather_rows(x, tb.row_slot, idx_div=k, out=xs, n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
-  _mark("dispatch_gather")
-  gu, h = gateup_swiglu(xs, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
+  fused = FUSED_EPILOGUE or FUSED_GATHER
+  wflat = tb.topk_w.view(-1)
+  if FUSED_GATHER:
+    # rows of x are picked by the producer warp; h carries the router weight, so ys is already weighted
+    xs = None
+    gu, h = gateup_swiglu(x, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets,
+                          row_idx=tb.row_slot, idx_div=k, rows=tb.mpad, h_scale_src=wflat)
+  else:
+    xs = torch.empty((tb.mpad, d), dtype=x.dtype, device=x.device)
+    ops.gather_rows(x, tb.row_slot, idx_div=k, out=xs, n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
+    _mark("dispatch_gather")
+    gu, h = gateup_swiglu(xs, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets,
+                          scale_idx=tb.row_slot if fused else None, h_scale_src=wflat if fused else None)
   _mark("gemm_gateup_swiglu")
   ys = ops.grouped_gemm_nn(h, w.w_down, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
   _mark("gemm_down")
   fork.join(gus, hs, ysh)
-  out = ops.gather_reduce(ys, tb.pad_pos.view(t, k), tb.topk_w, x.dtype, add0=ysh)
+  out = ops.gather_reduce(ys, tb.pad_pos.view(t, k), None if fused else tb.topk_w, x.dtype, add0=ysh)
   _mark("combine_gather_reduce")
-  return out, LayerCache(x=x, logits=logits, tables=tb, xs=xs, gu=gu, h=h, ys=ys, gus=gus, hs=hs, k=k)
+  return out, LayerCache(x=x, logits=logits, tables=tb, xs=xs, gu=gu, h=h, ys=ys, gus=gus, hs=hs, k=k, fused=fused)
 
 
 def moe_layer_bwd(dout, w: MoEWeights, c: LayerCache):
@@ -272,26 +315,62 @@ def moe_layer_bwd(dout, w: MoEWeights, c: LayerCache):
       dws_gate, dws_up = ops.grouped_gemm_tn(x, dgus, None, 1, out_dtype=w.ws_gate.dtype, split=True)
       _mark("shared_dw_gateup")
       shared_grads = dict(dws_gate=dws_gate[0], dws_up=dws_up[0], dws_down=dws_down)
-  # combine backward: dw = <g, y>, dy = w * g (scaled gather into padded order)
-  dw = ops.gather_dot(c.ys, pad_pos, dout)
-  _mark("combine_bwd_gather_dot")
-  dys = torch.empty_like(c.ys)
-  ops.gather_rows(dout, tb.row_slot, tb.topk_w.view(-1), idx_div=k, scale_by_idx=True, out=dys,
-                  n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
-  _mark("combine_bwd_scaled_gather")
-  # experts backward
-  dgu = dh_dswiglu(dys, w.w_down, c.gu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
-  _mark("gemm_dh_dswiglu")
-  dw_down = ops.grouped_gemm_tn(c.h, dys, tb.pad_offsets, e, out_dtype=w.w_down.dtype)
-  _mark("gemm_dw_down")
-  dxs = dx_from_dgu(dgu, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
-  _mark("gemm_dx")
-  dw_gate, dw_up = ops.grouped_gemm_tn(c.xs, dgu, tb.pad_offsets, e, out_dtype=w.w_gate.dtype, split=True)
-  _mark("gemm_dw_gateup")
+  dw = dw_partial = None
+  wflat = tb.topk_w.view(-1)
+  if c.fused and c.xs is not None:
+    # unscaled gather of dout into padded order; the router weight scales dh in the dH epilogue, which also emits
+    # the pieces of the routing-weight gradient <dout[t], y[row]> = sum_n dh[row,n] * h[row,n]
+    dys = torch.empty_like(c.ys)
+    ops.gather_rows(dout, tb.row_slot, idx_div=k, out=dys, n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
+    _mark("combine_bwd_gather")
+    dgu, dw_partial = dh_dswiglu(dys, w.w_down, c.gu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets,
+                                 scale_idx=tb.row_slot, scale_src=wflat, want_dw_partial=True)
+    _mark("gemm_dh_dswiglu")
+    dw_down = ops.grouped_gemm_tn(c.h, dys, tb.pad_offsets, e, out_dtype=w.w_down.dtype)
+    _mark("gemm_dw_down")
+    dxs = dx_from_dgu(dgu, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
+    _mark("gemm_dx")
+    dw_gate, dw_up = ops.grouped_gemm_tn(c.xs, dgu, tb.pad_offsets, e, out_dtype=w.w_gate.dtype, split=True)
+    _mark("gemm_dw_gateup")
+  elif c.fused:
+    # dout rows are picked by the producer warps
+    dgu, dw_partial = dh_dswiglu(dout, w.w_down, c.gu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets,
+                                 row_idx=tb.row_slot, idx_div=k, scale_src=wflat, want_dw_partial=True)
+    _mark("gemm_dh_dswiglu")
+    dw_down = ops.grouped_gemm_tn(c.h, dout, tb.pad_offsets, e, out_dtype=w.w_down.dtype, row_idx=tb.row_slot,
+                                  idx_div=k, gather_b=True, rows=tb.mpad)
+    _mark("gemm_dw_down")
+    dxs = dx_from_dgu(dgu, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
+    _mark("gemm_dx")
+    dw_gate, dw_up = ops.grouped_gemm_tn(x, dgu, tb.pad_offsets, e, out_dtype=w.w_gate.dtype, split=True,
+                                         row_idx=tb.row_slot, idx_div=k, gather_a=True, rows=tb.mpad)
+    _mark("gemm_dw_gateup")
+  else:
+    # combine backward: dw = <g, y>, dy = w * g (scaled gather into padded order)
+    dw = ops.gather_dot(c.ys, pad_pos, dout)
+    _mark("combine_bwd_gather_dot")
+    dys = torch.empty_like(c.ys)
+    ops.gather_rows(dout, tb.row_slot, tb.topk_w.view(-1), idx_div=k, scale_by_idx=True, out=dys,
+                    n_rows_dev=tb.n_blocks, rows_per_unit=BLOCK)
+    _mark("combine_bwd_scaled_gather")
+    # experts backward
+    dgu = dh_dswiglu(dys, w.w_down, c.gu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
+    _mark("gemm_dh_dswiglu")
+    dw_down = ops.grouped_gemm_tn(c.h, dys, tb.pad_offsets, e, out_dtype=w.w_down.dtype)
+    _mark("gemm_dw_down")
+    dxs = dx_from_dgu(dgu, w.w_gate, w.w_up, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
+    _mark("gemm_dx")
+    dw_gate, dw_up = ops.grouped_gemm_tn(c.xs, dgu, tb.pad_offsets, e, out_dtype=w.w_gate.dtype, split=True)
+    _mark("gemm_dw_gateup")
   grads = dict(dw_gate=dw_gate, dw_up=dw_up, dw_down=dw_down, dw=dw)
   grads.update(shared_grads)
   # router backward
-  _, dlb = router_topk_bwd(c.logits, tb.topk_idx, dw, want_f32=False, want_bf16=True)
+  if dw_partial is not None:
+    _, dlb, dw = router_topk_bwd(c.logits, tb.topk_idx, None, want_f32=False, want_bf16=True, dw_partial=dw_partial,
+                                 pad_pos=tb.pad_pos)
+    grads["dw"] = dw
+  else:
+    _, dlb = router_topk_bwd(c.logits, tb.topk_idx, dw, want_f32=False, want_bf16=True)
   _mark("router_topk_bwd")
   w_r_bf16 = cast_bf16(w.w_router)                                  # [d,E] = K-major operand over E
   dx_r = ops.grouped_gemm_nt(dlb, w_r_bf16[None], None, None)        # [T,d] = dlogits . W_r^T

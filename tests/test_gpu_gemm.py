@@ -200,6 +200,57 @@ def test_single_group_long_contraction_is_split(cuda, cta_pair, t, ma, nb, split
   assert O.rel_err(got16, want) <= TOL
 
 
+@pytest.mark.parametrize("t,d,e,f,k", [(300, 128, 8, 64, 2), (2048, 1024, 64, 512, 6), (777, 256, 16, 192, 4)])
+def test_gather_fused_kernels_equal_materialised_ones(cuda, cta_pair, t, d, e, f, k):
+  """Picking rows through row_slot inside the producer warp gives bit-identical results to gathering first."""
+  from lewi_surge_b200 import ops, layer, _lib
+  g = torch.Generator(device="cpu").manual_seed(t + d)
+  rn = lambda *s, std=1.0: (torch.randn(s, generator=g) * std)
+  x = rn(t, d).to(torch.bfloat16).to(cuda)
+  dout = rn(t, d).to(torch.bfloat16).to(cuda)
+  wg, wu = (rn(e, d, f, std=0.05).to(torch.bfloat16).to(cuda) for _ in range(2))
+  wd = rn(e, f, d, std=0.05).to(torch.bfloat16).to(cuda)
+  tb = layer.router_topk(rn(t, e).to(cuda), k)
+  _lib.last_status()
+  xs = torch.zeros((tb.mpad, d), dtype=torch.bfloat16, device=cuda)
+  ops.gather_rows(x, tb.row_slot, idx_div=k, out=xs, n_rows_dev=tb.n_blocks, rows_per_unit=128)
+  nb = int(tb.n_blocks.item()) * 128
+  gu0, h0 = layer.gateup_swiglu(xs, wg, wu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
+  gu1, h1 = layer.gateup_swiglu(x, wg, wu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets, row_idx=tb.row_slot,
+                                idx_div=k, rows=tb.mpad)
+  assert torch.equal(gu0[:nb], gu1[:nb]) and torch.equal(h0[:nb], h1[:nb])
+  # h scaled by the slot's router weight
+  wflat = tb.topk_w.view(-1)
+  _, h2 = layer.gateup_swiglu(x, wg, wu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets, row_idx=tb.row_slot,
+                              idx_div=k, rows=tb.mpad, h_scale_src=wflat)
+  rs = tb.row_slot[:nb].long()
+  sc = torch.where(rs >= 0, wflat[rs.clamp(min=0)], torch.zeros_like(wflat[:1]))
+  gf = gu0[:nb, :f].float()
+  want_h2 = (gf * torch.sigmoid(gf) * gu0[:nb, f:].float()) * sc[:, None]   # from the bf16-rounded g|u: 1e-2 is ample
+  assert float((h2[:nb].float() - want_h2).abs().max() / (want_h2.abs().max() + 1e-6)) <= 1e-2
+  # dH with gathered, scaled upstream gradient + routing-weight gradient pieces
+  dys = torch.zeros((tb.mpad, d), dtype=torch.bfloat16, device=cuda)
+  ops.gather_rows(dout, tb.row_slot, idx_div=k, out=dys, n_rows_dev=tb.n_blocks, rows_per_unit=128)
+  dgu0 = layer.dh_dswiglu(dys, wd, gu0, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
+  dgu1, dwp = layer.dh_dswiglu(dout, wd, gu0, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets,
+                               row_idx=tb.row_slot, idx_div=k, want_dw_partial=True)
+  assert torch.equal(dgu0[:nb], dgu1[:nb])
+  ys = ops.grouped_gemm_nn(h0, wd, tb.block_expert, tb.n_blocks, out_dtype=torch.float32, pad_offsets=tb.pad_offsets)
+  dw_want = ops.gather_dot(ys, tb.pad_pos.view(t, k), dout.float())
+  dw_got = dwp.sum(1)[tb.pad_pos.long()].view(t, k)
+  assert float((dw_got - dw_want).abs().max() / (dw_want.abs().max() + 1e-6)) <= 1e-2
+  # weight gradients with gathered contraction rows
+  a0 = ops.grouped_gemm_tn(xs, dgu0, tb.pad_offsets, e, out_dtype=torch.float32)
+  a1 = ops.grouped_gemm_tn(x, dgu0, tb.pad_offsets, e, out_dtype=torch.float32, row_idx=tb.row_slot, idx_div=k,
+                           gather_a=True, rows=tb.mpad)
+  assert torch.equal(a0, a1)
+  b0 = ops.grouped_gemm_tn(h0, dys, tb.pad_offsets, e, out_dtype=torch.float32)
+  b1 = ops.grouped_gemm_tn(h0, dout, tb.pad_offsets, e, out_dtype=torch.float32, row_idx=tb.row_slot, idx_div=k,
+                           gather_b=True, rows=tb.mpad)
+  assert torch.equal(b0, b1)
+  assert _lib.last_status() == 0
+
+
 def test_ragged_dot_drop_in_known_answer(cuda):
   """The reference's own check of ragged_dot semantics (modal/te_run.py:68-80): forward, dlhs, drhs on
   out[:S] with group sizes [5,0,9,3,7,1,6,4] and three tail rows outside every group."""
