@@ -204,7 +204,8 @@ def workload_config(args, c, world):
                       f"SwiGLU ffn {c['f']}, top-{c['k']} + 1 shared expert (ffn {c['fs']}), padded block 128"
                       + (", Zipf(1.2) router logit bias" if c["bias"] else ""),
           "tokens_per_gpu": c["T"], "global_tokens": c["T"] * world,
-          "parallelism": "single GPU" if world == 1 else f"expert-parallel x{world} (all-to-all dispatch/combine)",
+          "parallelism": "single GPU" if world == 1 else
+                         f"expert-parallel x{world} ({'peer-memory push/pull kernels' if args.ep_impl == 'p2p' else 'NCCL all-to-all'})",
           "l2": "inputs larger than L2 (weights 0.4 GB + activations > 2 GB per step)"}
 
 
@@ -218,6 +219,9 @@ def main():
   ap.add_argument("--no-cpu-baseline", action="store_true")
   ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
   ap.add_argument("--tokens", type=int, default=None, help="override tokens per GPU (profiling a smaller case)")
+  ap.add_argument("--ep-impl", default="p2p", choices=["p2p", "nccl"],
+                  help="N > 1: dispatch/combine as kernels over peer memory (default) or as NCCL all-to-all")
+  ap.add_argument("--ep-capacity", type=float, default=None, help="receive-buffer rows as a multiple of T*k")
   ap.add_argument("--dbg-flags", type=int, default=0, help="timing experiments only: results become wrong")
   ap.add_argument("--single-cta", action="store_true", help="A/B switch: force the cta_group::1 GEMM kernels")
   args = ap.parse_args()
@@ -255,7 +259,10 @@ def main():
   w = layer.MoEWeights(router_bias=bias, **wd)
   if world > 1:
     from lewi_surge_b200 import ep
-    runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
+    if args.ep_impl == "p2p":
+      runner = ep.ExpertParallelP2P(w, c["k"], c["E"], c["T"], c["d"], dist.group.WORLD, capacity=args.ep_capacity)
+    else:
+      runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
     step_fn = lambda: runner.step(x, dout)
   else:
     def step_fn():

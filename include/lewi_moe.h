@@ -41,6 +41,7 @@ extern "C" {
 /* device status bits (lewi_last_status) */
 #define LEWI_STATUS_WAIT_TIMEOUT 1 /* a bounded device-side wait ran out */
 #define LEWI_STATUS_BAD_INDEX 2    /* an index read from a table was out of range and skipped */
+#define LEWI_STATUS_EP_OVERFLOW 4  /* expert-parallel receive buffer too small for the routed rows (rows dropped) */
 
 int lewi_version(void);
 const char* lewi_error_string(int code);
@@ -220,7 +221,8 @@ int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_
  * UNPERMUTED source [src_rows,d]; padded row r reads xs[row_idx[r] / idx_div] (row_idx[r] < 0: zero row),
  * i.e. row_idx = row_slot and idx_div = k replace `_route_activations` (modal/moe_permute.py:399-404)
  * without materialising the permuted rows (row_idx null: xs is already in padded order).
- * h_scale_src (optional, f32 indexed by scale_idx[r]; scale_idx defaults to row_idx) multiplies h: with
+ * h_scale_src (optional, f32 indexed by scale_idx[r]; scale_idx defaults to row_idx, and to r itself when
+ * both are null) multiplies h: with
  * the router weights there, the down projection yields already-weighted expert outputs and the combine
  * needs no weights.  Measured note: the in-kernel row gather is correct but slower than gathering first
  * on B200; the scale is free. */
@@ -264,6 +266,51 @@ int lewi_grouped_gemm_tn_gather(void* stream, const void* a, const void* b, void
 int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, const void* w_up,
                          void* dxs, const int32_t* block_expert, const int32_t* n_blocks,
                          const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
+
+/* ------------------------------------------------------------------------------------------------
+ * Expert parallelism over peer memory (one process per GPU on an NVSwitch node).  The reference never ran
+ * expert parallelism (configs/stage1.yml:102 keeps ici_expert_parallelism at 1), so these entry points
+ * have no counterpart there; they implement the sharded form of `_route_activations` / `unpermute`.
+ * Buffers that peers write or read are allocated with lewi_ep_alloc (cudaMalloc) and shared through
+ * CUDA IPC handles (64 bytes each, exchanged by the host code).  `peers` arguments are HOST arrays of G
+ * device pointers (index = rank; the rank's own buffer at its own index).  G <= 8.
+ * ---------------------------------------------------------------------------------------------- */
+int lewi_ep_alloc(int64_t bytes, void** out_host);
+int lewi_ep_free(void* ptr);
+int lewi_ep_ipc_export(void* ptr, void* handle64_host);
+int lewi_ep_ipc_import(const void* handle64_host, void** out_host);
+int lewi_ep_ipc_release(void* ptr);
+
+/* From all ranks' expert histograms counts_all i32 [G,E] (device) computes, for rank `me`:
+ *   dst_base i32 [E]            first row, in the owner's padded buffer, of this rank's rows of expert e
+ *   pad_offsets i32 [E/G + 1]   this rank's own padded layout as an owner (rows source-major inside an expert)
+ *   valid_end i32 [E/G]         end of the real rows of each local expert (the rest of its last block is padding)
+ *   n_blocks i32 [1], block_expert i32 [rmax_pad/block] (may be null), recv_rows i32 [1]
+ * Raises LEWI_STATUS_EP_OVERFLOW if the padded rows exceed rmax_pad. */
+int lewi_ep_plan(void* stream, const int32_t* counts_all, int G, int E, int me, int block, int64_t rmax_pad,
+                 int32_t* dst_base, int32_t* pad_offsets, int32_t* valid_end, int32_t* n_blocks,
+                 int32_t* block_expert, int32_t* recv_rows);
+
+/* Dispatch fused with the exchange: sorted position p (slot order[p], token order[p]/k, expert
+ * flat_expert[slot]) is stored to row dst_base[e] + (p - offsets[e]) of peers_rows[owner].  slot_w (optional,
+ * f32 per slot) is stored to peers_w[owner][row].  slot_rank / slot_row i32 [M] record where every slot went. */
+int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const int32_t* flat_expert,
+                      const int32_t* offsets, const int32_t* dst_base, const float* slot_w,
+                      void* const* peers_rows_host, void* const* peers_w_host, int32_t* slot_rank,
+                      int32_t* slot_row, int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T);
+
+/* Zero rows [valid_end[el], pad_offsets[el+1]) of buf [rmax_pad,d] bf16 for every local expert. */
+int lewi_ep_zero_pad(void* stream, void* buf, const int32_t* valid_end, const int32_t* pad_offsets, int E_local,
+                     int d, int64_t rmax_pad);
+
+/* Combine fused with the exchange: out[t] = sum_j peers_rows[slot_rank[t,j]][slot_row[t,j]] (+ add0 + add1), bf16. */
+int lewi_ep_pull_reduce(void* stream, void* const* peers_rows_host, const int32_t* slot_rank,
+                        const int32_t* slot_row, const void* add0, const void* add1, void* out, int64_t T, int k,
+                        int d, int G, int64_t rmax_pad);
+
+/* dw[slot] = sum_p peers_partial[slot_rank][slot_row, p]  (pieces written by the owners' dH epilogues). */
+int lewi_ep_pull_dw(void* stream, void* const* peers_partial_host, const int32_t* slot_rank,
+                    const int32_t* slot_row, float* dw, int64_t M, int parts, int G, int64_t rmax_pad);
 
 /* Bring-up hook (not part of the drop-in surface): overrides the shared-memory matrix-descriptor
  * geometry in bytes for K-major and MN-major operands; 0 keeps a value. */

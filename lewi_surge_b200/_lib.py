@@ -12,7 +12,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "liblewi_moe.so")
 
 BF16, F32 = 0, 1
-STATUS_WAIT_TIMEOUT, STATUS_BAD_INDEX = 1, 2
+STATUS_WAIT_TIMEOUT, STATUS_BAD_INDEX, STATUS_EP_OVERFLOW = 1, 2, 4
 
 P = c_void_p  # every device pointer crosses the boundary as an integer address
 
@@ -48,6 +48,16 @@ SIGNATURES = {
     "lewi_grouped_gemm_gateup_swiglu": (c_int, [P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dh_dswiglu": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dx": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_ep_alloc": (c_int, [c_int64, P]),
+    "lewi_ep_free": (c_int, [P]),
+    "lewi_ep_ipc_export": (c_int, [P, P]),
+    "lewi_ep_ipc_import": (c_int, [P, P]),
+    "lewi_ep_ipc_release": (c_int, [P]),
+    "lewi_ep_plan": (c_int, [P, P, c_int, c_int, c_int, c_int, c_int64, P, P, P, P, P, P]),
+    "lewi_ep_push_rows": (c_int, [P, P, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64, c_int64]),
+    "lewi_ep_zero_pad": (c_int, [P, P, P, P, c_int, c_int, c_int64]),
+    "lewi_ep_pull_reduce": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int64]),
+    "lewi_ep_pull_dw": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int64]),
     "lewi_debug_set_cta_pair": (c_int, [c_int]),
     "lewi_debug_set_flags": (c_int, [c_int]),
     "lewi_debug_set_desc": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),

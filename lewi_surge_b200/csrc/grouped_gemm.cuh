@@ -71,7 +71,7 @@ struct Args {
   int k_splits;                 // TN: the contraction of every output tile is cut into this many parts
   float* partial;               // TN with k_splits > 1: f32 partial products [k_splits, E, Ma, N]
   const float* col_bias;        // PLAIN: optional f32 per output column
-  const int32_t* scale_idx;     // SWIGLU / DSWIGLU: padded row -> index into scale_src (negative: scale 0)
+  const int32_t* scale_idx;     // SWIGLU / DSWIGLU: padded row -> index into scale_src (negative: scale 0; null: the row itself)
   const float* scale_src;       // SWIGLU / DSWIGLU: optional f32 table indexed by scale_idx[row] (router weight of the
                                 // row's slot); SWIGLU stores h * scale, DSWIGLU multiplies dh by it
   float* dw_partial;            // DSWIGLU: optional [rows, dw_parts] f32, sum over this warp's columns of
@@ -655,7 +655,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (a.scale_src != nullptr) {
           hsc = 0.f;
           if (lane < rows_valid) {
-            const int gi = a.scale_idx[wrow0 + lane];
+            const long long gi = a.scale_idx != nullptr ? (long long)a.scale_idx[wrow0 + lane] : wrow0 + lane;
             if (gi >= 0) hsc = a.scale_src[gi];
           }
         }
@@ -692,7 +692,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (a.scale_src != nullptr) {
           dsc = 0.f;
           if (lane < rows_valid) {
-            const int gi = a.scale_idx[wrow0 + lane];
+            const long long gi = a.scale_idx != nullptr ? (long long)a.scale_idx[wrow0 + lane] : wrow0 + lane;
             if (gi >= 0) dsc = a.scale_src[gi];
           }
         }

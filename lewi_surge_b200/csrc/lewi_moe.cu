@@ -1,10 +1,12 @@
 // liblewi_moe.so: C ABI over the sm_100a kernels (declarations and contracts: include/lewi_moe.h).
 #include "common.cuh"
+#include "ep.cuh"
 #include "gather.cuh"
 #include "grouped_gemm.cuh"
 #include "router_gemm.cuh"
 #include "routing.cuh"
 
+#include <cstring>
 #include <mutex>
 
 using namespace lewi;
@@ -528,8 +530,7 @@ int lewi_grouped_gemm_gateup_swiglu_gather(void* stream, const void* xs, const i
                                            int f, int E) {
   if (!xs || !w_gate || !w_up || !h || d <= 0 || f <= 0) return LEWI_ERR_ARG;
   if (row_idx != nullptr && (idx_div <= 0 || src_rows <= 0 || src_rows > 0x7fffffffLL)) return LEWI_ERR_ARG;
-  if (scale_idx == nullptr) scale_idx = row_idx;
-  if (h_scale_src != nullptr && scale_idx == nullptr) return LEWI_ERR_ARG;
+  if (scale_idx == nullptr) scale_idx = row_idx;   // still null: the scale table is indexed by the padded row itself
   RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
   const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
@@ -579,8 +580,7 @@ int lewi_grouped_gemm_dh_dswiglu_gather(void* stream, const void* dys, const int
                                         int f, int E) {
   if (!dys || !w_down || !gu || !dgu || d <= 0 || f <= 0) return LEWI_ERR_ARG;
   if (row_idx != nullptr && (idx_div <= 0 || src_rows <= 0 || src_rows > 0x7fffffffLL)) return LEWI_ERR_ARG;
-  if (scale_idx == nullptr) scale_idx = row_idx;
-  if (scale_src != nullptr && scale_idx == nullptr) return LEWI_ERR_ARG;
+  if (scale_idx == nullptr) scale_idx = row_idx;   // still null: the scale table is indexed by the padded row itself
   RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
   const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
@@ -643,6 +643,135 @@ int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, cons
 
 // Bring-up hook: override the shared-memory descriptor geometry (bytes).  A value of 0 keeps the
 // current setting.  Not part of the drop-in surface.
+// ------------------------------------------------------------------------------------------------ expert parallel
+
+int lewi_ep_alloc(int64_t bytes, void** out_host) {
+  if (bytes <= 0 || !out_host) return LEWI_ERR_ARG;
+  void* p = nullptr;
+  if (cudaMalloc(&p, (size_t)bytes) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return LEWI_ERR_CUDA;
+  }
+  *out_host = p;
+  return LEWI_OK;
+}
+
+int lewi_ep_free(void* ptr) { return cudaFree(ptr) == cudaSuccess ? LEWI_OK : LEWI_ERR_CUDA; }
+
+int lewi_ep_ipc_export(void* ptr, void* handle64_host) {
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (!ptr || !handle64_host) return LEWI_ERR_ARG;
+  if (cudaIpcGetMemHandle(reinterpret_cast<cudaIpcMemHandle_t*>(handle64_host), ptr) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return LEWI_ERR_CUDA;
+  }
+  return LEWI_OK;
+}
+
+int lewi_ep_ipc_import(const void* handle64_host, void** out_host) {
+  if (!handle64_host || !out_host) return LEWI_ERR_ARG;
+  cudaIpcMemHandle_t h;
+  memcpy(&h, handle64_host, sizeof(h));
+  void* p = nullptr;
+  if (cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+    (void)cudaGetLastError();
+    return LEWI_ERR_CUDA;
+  }
+  *out_host = p;
+  return LEWI_OK;
+}
+
+int lewi_ep_ipc_release(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? LEWI_OK : LEWI_ERR_CUDA; }
+
+namespace {
+inline bool fill_peers(PeerPtrs& pp, void* const* host, int G, bool required) {
+  for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = nullptr;
+  if (host == nullptr) return !required;
+  for (int i = 0; i < G; ++i) {
+    if (host[i] == nullptr) return false;
+    pp.p[i] = host[i];
+  }
+  return true;
+}
+}  // namespace
+
+int lewi_ep_plan(void* stream, const int32_t* counts_all, int G, int E, int me, int block, int64_t rmax_pad,
+                 int32_t* dst_base, int32_t* pad_offsets, int32_t* valid_end, int32_t* n_blocks,
+                 int32_t* block_expert, int32_t* recv_rows) {
+  if (!counts_all || !dst_base || !pad_offsets || !valid_end || !n_blocks || !recv_rows) return LEWI_ERR_ARG;
+  if (G <= 0 || G > kMaxPeers || E <= 0 || E % G != 0 || me < 0 || me >= G || block <= 0 || rmax_pad <= 0)
+    return LEWI_ERR_ARG;
+  if (E > kMaxExperts) return LEWI_ERR_LIMIT;
+  ep_plan_kernel<<<1, 1024, 0, as_stream(stream)>>>(counts_all, G, E, me, block, rmax_pad, (int)(rmax_pad / block),
+                                                    dst_base, pad_offsets, valid_end, n_blocks, block_expert,
+                                                    recv_rows);
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const int32_t* flat_expert,
+                      const int32_t* offsets, const int32_t* dst_base, const float* slot_w,
+                      void* const* peers_rows_host, void* const* peers_w_host, int32_t* slot_rank,
+                      int32_t* slot_row, int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T) {
+  if (!x || !order || !flat_expert || !offsets || !dst_base || M < 0 || k <= 0 || d <= 0 || T < 0) return LEWI_ERR_ARG;
+  if (G <= 0 || G > kMaxPeers || E % G != 0) return LEWI_ERR_ARG;
+  PeerPtrs rows, w;
+  if (!fill_peers(rows, peers_rows_host, G, true)) return LEWI_ERR_ARG;
+  if (!fill_peers(w, peers_w_host, G, slot_w != nullptr)) return LEWI_ERR_ARG;
+  const int vpl = pick_vpl(d, 2);
+  if (vpl == 0) return LEWI_ERR_SHAPE;
+  if (M == 0) return LEWI_OK;
+  const int grid = gather_grid(M);
+  cudaStream_t st = as_stream(stream);
+  LEWI_DISPATCH_VPL(vpl, (ep_push_rows_kernel<VPL><<<grid, kGatherThreads, 0, st>>>(
+                             reinterpret_cast<const __nv_bfloat16*>(x), order, flat_expert, offsets, dst_base, slot_w, rows,
+                             w, slot_rank, slot_row, M, k, d, E / G, G, rmax_pad, T)));
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+int lewi_ep_zero_pad(void* stream, void* buf, const int32_t* valid_end, const int32_t* pad_offsets, int E_local,
+                     int d, int64_t rmax_pad) {
+  if (!buf || !valid_end || !pad_offsets || E_local <= 0 || d <= 0 || d % 8 != 0) return LEWI_ERR_ARG;
+  ep_zero_pad_kernel<<<E_local, 256, 0, as_stream(stream)>>>(reinterpret_cast<__nv_bfloat16*>(buf), valid_end,
+                                                             pad_offsets, d, rmax_pad);
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+int lewi_ep_pull_reduce(void* stream, void* const* peers_rows_host, const int32_t* slot_rank,
+                        const int32_t* slot_row, const void* add0, const void* add1, void* out, int64_t T, int k,
+                        int d, int G, int64_t rmax_pad) {
+  if (!slot_rank || !slot_row || !out || T < 0 || k <= 0 || k > kWarp || d <= 0 || G <= 0 || G > kMaxPeers)
+    return LEWI_ERR_ARG;
+  PeerPtrs rows;
+  if (!fill_peers(rows, peers_rows_host, G, true)) return LEWI_ERR_ARG;
+  const int vpl = pick_vpl(d, 2);
+  if (vpl == 0) return LEWI_ERR_SHAPE;
+  if (T == 0) return LEWI_OK;
+  const int grid = gather_grid(T);
+  cudaStream_t st = as_stream(stream);
+  LEWI_DISPATCH_VPL(vpl, (ep_pull_reduce_kernel<VPL><<<grid, kGatherThreads, 0, st>>>(
+                             rows, slot_rank, slot_row, reinterpret_cast<const __nv_bfloat16*>(add0),
+                             reinterpret_cast<const __nv_bfloat16*>(add1), reinterpret_cast<__nv_bfloat16*>(out), T, k, d,
+                             G, rmax_pad)));
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+int lewi_ep_pull_dw(void* stream, void* const* peers_partial_host, const int32_t* slot_rank,
+                    const int32_t* slot_row, float* dw, int64_t M, int parts, int G, int64_t rmax_pad) {
+  if (!slot_rank || !slot_row || !dw || M < 0 || parts <= 0 || G <= 0 || G > kMaxPeers) return LEWI_ERR_ARG;
+  PeerPtrs pp;
+  if (!fill_peers(pp, peers_partial_host, G, true)) return LEWI_ERR_ARG;
+  if (M == 0) return LEWI_OK;
+  long long grid = (M + 255) / 256;
+  if (grid > (long long)num_sms() * 8) grid = (long long)num_sms() * 8;
+  ep_pull_dw_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(pp, slot_rank, slot_row, dw, M, parts, G, rmax_pad);
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
 // Bring-up hook: 0 forces the single-CTA (cta_group::1) GEMM kernels, 1 (default) allows CTA pairs.
 int lewi_debug_set_cta_pair(int on) {
   gg::pair_mode() = on != 0;

@@ -21,7 +21,7 @@ def _free_port():
   return p
 
 
-def _worker(rank, world, port, cfg, out_dir):
+def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
   sys.path.insert(0, HERE)
   sys.path.insert(0, os.path.dirname(HERE))
   os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
@@ -41,9 +41,16 @@ def _worker(rank, world, port, cfg, out_dir):
     w = MoEWeights(tt(inp["w_router"], torch.float32), tt(inp["w_gate"][rank * el:(rank + 1) * el]),
                    tt(inp["w_up"][rank * el:(rank + 1) * el]), tt(inp["w_down"][rank * el:(rank + 1) * el]),
                    tt(inp["ws_gate"]), tt(inp["ws_up"]), tt(inp["ws_down"]))
-    lay = ep.ExpertParallelLayer(w, k, e)
+    if impl == "p2p":
+      lay = ep.ExpertParallelP2P(w, k, e, t, d, capacity=float(world))
+    else:
+      lay = ep.ExpertParallelLayer(w, k, e)
     sl = slice(rank * t, (rank + 1) * t)
-    out, grads = lay.step(tt(inp["x"][sl]), tt(inp["dout"][sl]))
+    xr, gr = tt(inp["x"][sl]), tt(inp["dout"][sl])
+    out, grads = lay.step(xr, gr)
+    if impl == "p2p":     # a second step over the same buffers must give the same answer
+      out2, grads2 = lay.step(xr, gr)
+      assert torch.equal(out, out2) and torch.equal(grads["dx"], grads2["dx"])
     assert _lib.last_status() == 0
     np.savez(os.path.join(out_dir, f"r{rank}.npz"), out=out.float().cpu().numpy(),
              **{n: g.float().cpu().numpy() for n, g in grads.items()})
@@ -52,15 +59,25 @@ def _worker(rank, world, port, cfg, out_dir):
     dist.destroy_process_group()
 
 
+def test_peer_memory_layer_on_one_gpu(cuda, tmp_path):
+  """World size 1: the push / pull kernels and the plan run against this GPU's own buffers."""
+  _check(cuda, tmp_path, (512, 256, 16, 128, 128, 4), 1, "p2p")
+
+
+@pytest.mark.parametrize("impl", ["nccl", "p2p"])
 @pytest.mark.parametrize("cfg", [(512, 256, 16, 128, 128, 4), (1024, 1024, 64, 512, 512, 6)])
-def test_expert_parallel_matches_single_gpu(cuda, tmp_path, cfg):
+def test_expert_parallel_matches_single_gpu(cuda, tmp_path, cfg, impl):
   world = min(torch.cuda.device_count(), 4)
   if world < 2:
     pytest.skip("needs at least 2 GPUs")
+  _check(cuda, tmp_path, cfg, world, impl)
+
+
+def _check(cuda, tmp_path, cfg, world, impl):
   import torch.multiprocessing as mp
   import oracle as O
   from lewi_surge_b200 import layer
-  mp.spawn(_worker, args=(world, _free_port(), cfg, str(tmp_path)), nprocs=world, join=True)
+  mp.spawn(_worker, args=(world, _free_port(), cfg, str(tmp_path), impl), nprocs=world, join=True)
   t, d, e, f, fs, k = cfg
   inp = O.make_inputs(t * world, d, e, f, fs, seed=5)
   inp["w_router"] = inp["w_router"] * 5
