@@ -222,6 +222,9 @@ def main():
   ap.add_argument("--ep-impl", default="p2p", choices=["p2p", "nccl"],
                   help="N > 1: dispatch/combine as kernels over peer memory (default) or as NCCL all-to-all")
   ap.add_argument("--ep-capacity", type=float, default=None, help="receive-buffer rows as a multiple of T*k")
+  ap.add_argument("--timeline", default=None, help="write the last timed step's event marks (rank 0) to this file")
+  ap.add_argument("--ep-sync", choices=["flags", "nccl"], default="flags", help="how the exchange orders the ranks")
+  ap.add_argument("--ep-phases", type=int, default=None, help="ranges of local experts the exchange is pipelined over")
   ap.add_argument("--dbg-flags", type=int, default=0, help="timing experiments only: results become wrong")
   ap.add_argument("--single-cta", action="store_true", help="A/B switch: force the cta_group::1 GEMM kernels")
   args = ap.parse_args()
@@ -260,7 +263,8 @@ def main():
   if world > 1:
     from lewi_surge_b200 import ep
     if args.ep_impl == "p2p":
-      runner = ep.ExpertParallelP2P(w, c["k"], c["E"], c["T"], c["d"], dist.group.WORLD, capacity=args.ep_capacity)
+      runner = ep.ExpertParallelP2P(w, c["k"], c["E"], c["T"], c["d"], dist.group.WORLD, capacity=args.ep_capacity,
+                                    phases=args.ep_phases, sync=args.ep_sync)
     else:
       runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
     step_fn = lambda: runner.step(x, dout)
@@ -292,9 +296,11 @@ def main():
   ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   barrier()
   ev0.record()
+  host0 = time.perf_counter()
   for _ in range(args.steps):
-    hook("step_begin")
+    hook("bench_step")
     step_fn()
+  host_ms = (time.perf_counter() - host0) * 1e3 / args.steps   # time the host needs to queue one step
   ev1.record()
   barrier()
   launches = lib.lewi_launch_count() - launches0
@@ -317,12 +323,19 @@ def main():
   for name, ev, sid in marks:
     prev = last.get(sid)
     last[sid] = ev
-    if name in ("step_begin", "side_begin") or prev is None:
+    if name in ("bench_step", "step_begin", "side_begin") or prev is None:
       continue
     per.setdefault(name, []).append(prev.elapsed_time(ev))
     if sid != main_sid:
       overlapped.add(name)   # elapsed time on the side stream includes waiting for SMs: not a kernel duration
   kernels = {n: sum(v) / len(v) for n, v in per.items()}
+  if args.timeline and rank == 0:
+    # every mark of the last timed step: milliseconds since the step began, stream, name (a mark follows its kernel)
+    start = max(i for i, mk in enumerate(marks) if mk[0] == "bench_step")
+    sids = {}
+    with open(args.timeline, "w") as fh:
+      for name, ev, sid in marks[start:]:
+        fh.write(f"{marks[start][1].elapsed_time(ev):9.3f}  s{sids.setdefault(sid, len(sids))}  {name}\n")
 
   # ---- end-to-end through the public API with host buffers (pinned), copies inside the timed region
   e2e = None
@@ -405,7 +418,8 @@ def main():
       "metric": METRIC, "value": c["T"] * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
       "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
       "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, c, world),
-      "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "roofline": roofline, "cpu_baseline": cpu_baseline,
+      "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "host_enqueue_ms_per_step": round(host_ms, 3),
+      "roofline": roofline, "cpu_baseline": cpu_baseline,
       "summary": summary, "kernels": table,
   }
   print(json.dumps(line), flush=True)

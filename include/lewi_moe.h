@@ -42,6 +42,7 @@ extern "C" {
 #define LEWI_STATUS_WAIT_TIMEOUT 1 /* a bounded device-side wait ran out */
 #define LEWI_STATUS_BAD_INDEX 2    /* an index read from a table was out of range and skipped */
 #define LEWI_STATUS_EP_OVERFLOW 4  /* expert-parallel receive buffer too small for the routed rows (rows dropped) */
+#define LEWI_STATUS_SMEM_LAYOUT 8  /* a GEMM kernel found its shared memory not 1024-byte aligned and did nothing */
 
 int lewi_version(void);
 const char* lewi_error_string(int code);
@@ -292,25 +293,49 @@ int lewi_ep_plan(void* stream, const int32_t* counts_all, int G, int E, int me, 
                  int32_t* block_expert, int32_t* recv_rows);
 
 /* Dispatch fused with the exchange: sorted position p (slot order[p], token order[p]/k, expert
- * flat_expert[slot]) is stored to row dst_base[e] + (p - offsets[e]) of peers_rows[owner].  slot_w (optional,
- * f32 per slot) is stored to peers_w[owner][row].  slot_rank / slot_row i32 [M] record where every slot went. */
+ * flat_expert[slot]) is stored to row dst_base[e] + (p - offsets[e]) of peers_rows[owner]; offsets i32 [E+1].
+ * With the row go slot_w[slot] (optional, f32) to peers_w[owner][row] and the row's return address
+ * (me << 28 | slot, i32) to peers_ret[owner][row] (optional).  Only the rows of local experts (e mod E/G) in
+ * [el_lo, el_hi) are moved: launching once per range of local experts lets the owners start on the first
+ * range while the next one is still in flight.  M = T*k < 2^28.  The kernel is one small CTA per SM that
+ * fits beside a resident grouped-GEMM CTA, so it overlaps GEMMs running on another stream. */
 int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const int32_t* flat_expert,
                       const int32_t* offsets, const int32_t* dst_base, const float* slot_w,
-                      void* const* peers_rows_host, void* const* peers_w_host, int32_t* slot_rank,
-                      int32_t* slot_row, int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T);
+                      void* const* peers_rows_host, void* const* peers_w_host, void* const* peers_ret_host, int me,
+                      int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T, int el_lo, int el_hi);
 
-/* Zero rows [valid_end[el], pad_offsets[el+1]) of buf [rmax_pad,d] bf16 for every local expert. */
-int lewi_ep_zero_pad(void* stream, void* buf, const int32_t* valid_end, const int32_t* pad_offsets, int E_local,
-                     int d, int64_t rmax_pad);
+/* Owner side of the way back: rows [pad_offsets[el_lo], pad_offsets[el_hi]) of `rows` [rmax_pad,d] bf16 are
+ * stored to row `slot` of peers_slot_rows[source] ([M,d] bf16 on every rank), slot and source taken from the
+ * return addresses ret i32 [rmax_pad] (-1 = padding row, skipped).  `pieces` f32 [rmax_pad,parts] (optional)
+ * go to peers_slot_pieces[source][slot, :parts].  Either of rows / pieces may be null.  On the source rank
+ * the combine is then a sum over k consecutive rows (lewi_gather_reduce with the identity index). */
+int lewi_ep_return_rows(void* stream, const void* rows, const float* pieces, const int32_t* ret,
+                        const int32_t* pad_offsets, int el_lo, int el_hi, void* const* peers_slot_rows_host,
+                        void* const* peers_slot_pieces_host, int d, int parts, int G, int64_t M, int64_t rmax_pad);
 
-/* Combine fused with the exchange: out[t] = sum_j peers_rows[slot_rank[t,j]][slot_row[t,j]] (+ add0 + add1), bf16. */
-int lewi_ep_pull_reduce(void* stream, void* const* peers_rows_host, const int32_t* slot_rank,
-                        const int32_t* slot_row, const void* add0, const void* add1, void* out, int64_t T, int k,
-                        int d, int G, int64_t rmax_pad);
+/* Zero rows [valid_end[el], pad_offsets[el+1]) of buf [rmax_pad,d] bf16 for every local expert and, with
+ * ret (i32 [rmax_pad], optional), mark them as having no return address. */
+int lewi_ep_zero_pad(void* stream, void* buf, int32_t* ret, const int32_t* valid_end, const int32_t* pad_offsets,
+                     int E_local, int d, int64_t rmax_pad);
 
-/* dw[slot] = sum_p peers_partial[slot_rank][slot_row, p]  (pieces written by the owners' dH epilogues). */
-int lewi_ep_pull_dw(void* stream, void* const* peers_partial_host, const int32_t* slot_rank,
-                    const int32_t* slot_row, float* dw, int64_t M, int parts, int G, int64_t rmax_pad);
+/* 1: the grouped-GEMM CTAs launched from now on leave room on their SM (1 KB of shared memory, 2 warps of 40
+ * registers per scheduler) for one CTA of an exchange kernel running on another stream, so that transfers overlap
+ * the GEMMs; 0 (default): a GEMM CTA has its SM to itself, which measured faster when nothing needs to overlap.
+ * Host-side switch read at launch time; not thread-safe against concurrent launches. */
+int lewi_set_sm_sharing(int on);
+
+/* All-gather of a small table by peer stores: src i32 [n] goes to elements [dst_offset, dst_offset+n) of every
+ * peer's buffer (used for the expert histograms: dst_offset = me*E).  Follow it with lewi_ep_barrier. */
+int lewi_ep_put_i32(void* stream, const int32_t* src, void* const* peers_dst_host, int64_t dst_offset, int n, int G);
+
+/* Barrier between the G ranks in stream order: adds one to *epoch_counter (i32 on this device, zero-initialised;
+ * it counts this rank's barriers), stores the new epoch into slot `me` of every peer's flag array (peers_flags[g],
+ * i32 [G], zero-initialised, lewi_ep_alloc'ed) and waits until my_flags[g] >= epoch for every g.  Every rank must
+ * run the same sequence of barriers.  Nothing is passed from the host per call, so a captured launch can be
+ * replayed.  The wait gives up after timeout_ms (<= 10000) with LEWI_STATUS_WAIT_TIMEOUT in lewi_last_status();
+ * the kernel then returns normally. */
+int lewi_ep_barrier(void* stream, void* const* peers_flags_host, int32_t* my_flags, int32_t* epoch_counter, int me,
+                    int G, int64_t timeout_ms);
 
 /* Bring-up hook (not part of the drop-in surface): overrides the shared-memory matrix-descriptor
  * geometry in bytes for K-major and MN-major operands; 0 keeps a value. */

@@ -43,7 +43,10 @@ constexpr int EPI_WARPS = 8;      // two warps per TMEM lane quarter, each takes
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int STAGING_PER_WARP = 4096;  // epilogue transposition buffer of one warp
-constexpr size_t SMEM_BYTES = (size_t)RING_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/ + PAIR_PREFIX_BYTES + GATHER_ROWS_BYTES +
+// 231,184 bytes.  An SM has 233,472 and every resident CTA reserves 1,024 of them, so exactly one more CTA that
+// uses no shared memory (a gather or exchange kernel from another stream) fits beside a GEMM CTA.  That is why
+// there is no slack for aligning the ring: the kernel asks for a 1024-byte aligned base and checks it.
+constexpr size_t SMEM_BYTES = (size_t)RING_BYTES + 256 /*barriers*/ + PAIR_PREFIX_BYTES + GATHER_ROWS_BYTES +
                               (size_t)EPI_WARPS * STAGING_PER_WARP;
 
 enum Major { NN = 0, NT = 1, TN = 2 };
@@ -249,15 +252,28 @@ __device__ __forceinline__ Tile decode_tile(const Args& a, int tile, int n_tiles
   return t;
 }
 
+// 144 registers per thread: the register file is split over the SM's four schedulers (16,384 each), three of this
+// CTA's ten warps land on one scheduler, and 3 x 144 x 32 leaves it room for two 40-register warps of an exchange
+// CTA from another stream.  At the 168 the compiler would take by itself nothing else fits on the SM.  The
+// dSwiGLU epilogue spills under that cap (measured 0.09 ms per step), so that kernel keeps 168 and shares nothing.
+#ifndef LEWI_GEMM_MAX_REGS
+#define LEWI_GEMM_MAX_REGS 144
+#endif
+constexpr int max_regs(int epi) { return epi == 2 /* DSWIGLU */ ? 168 : LEWI_GEMM_MAX_REGS; }
+
 template <int MAJOR, int EPI, bool PAIR>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __maxnreg__(max_regs(EPI))
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
                     const __grid_constant__ CUtensorMap tm_b2, const Args a) {
   constexpr int STAGES = Cfg<PAIR>::STAGES;
   constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
   constexpr int B_CHUNKS = PAIR ? 2 : 4;   // 64-column boxes of an MN-major B operand held by one CTA
-  extern __shared__ uint8_t smem_raw[];
-  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const uint32_t smem_base = ptx::smem_u32(smem_raw);
+  if ((smem_base & 1023u) != 0) {   // 128-byte swizzled tiles need it; nothing has been set up yet, so just leave
+    if (threadIdx.x == 0) raise_status(LEWI_STATUS_SMEM_LAYOUT);
+    return;
+  }
   const uint32_t bar_base = smem_base + RING_BYTES;
   // barrier layout (8 bytes each): full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], drain
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -266,7 +282,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 2 + b); };
   const uint32_t drain_bar = bar_base + 8u * (2 * MAX_STAGES + 4);
   auto gfull_bar = [&](int s) { return bar_base + 176u + 8u * s; };   // peer CTA: its own gathered rows of stage s
-  uint8_t* generic_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  uint8_t* generic_base = smem_raw;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(generic_base + RING_BYTES + 160);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + RING_BYTES + 168);
   uint16_t* pair_prefix = reinterpret_cast<uint16_t*>(generic_base + RING_BYTES + 256);
@@ -861,6 +877,14 @@ inline bool& pair_mode() {
   return on;
 }
 
+// Whether a GEMM CTA leaves its SM's last kilobytes of shared memory to a CTA of another kernel (see SMEM_BYTES).
+// Off: the launch asks for 1 KB it does not use, so a GEMM CTA has its SM to itself.
+inline bool& sm_sharing() {
+  static bool on = false;
+  return on;
+}
+constexpr size_t SMEM_EXCLUSIVE_PAD = 1024;
+
 template <int MAJOR, int EPI, bool PAIR>
 inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, Args a,
                   long long max_tiles) {
@@ -869,7 +893,8 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
   if (cudaGetDevice(&dev) != cudaSuccess) return LEWI_ERR_CUDA;
   auto kern = grouped_gemm_kernel<MAJOR, EPI, PAIR>;
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) != cudaSuccess) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                             (int)(SMEM_BYTES + SMEM_EXCLUSIVE_PAD)) != cudaSuccess) {
       (void)cudaGetLastError();
       return LEWI_ERR_CUDA;
     }
@@ -883,6 +908,7 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
   a.kstep_b = b_mn ? g.mn_step : g.k_step;
   a.idesc = ptx::instr_desc_bf16(PAIR ? 2 * BM : BM, BN, a_mn ? 1 : 0, b_mn ? 1 : 0);
   if (max_tiles <= 0) return LEWI_OK;
+  const size_t smem = SMEM_BYTES + (sm_sharing() ? 0 : SMEM_EXCLUSIVE_PAD);
   long long grid = num_sms();
   if constexpr (PAIR) {
     grid &= ~1LL;
@@ -890,7 +916,7 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3((unsigned)grid);
     cfg.blockDim = dim3(THREADS);
-    cfg.dynamicSmemBytes = SMEM_BYTES;
+    cfg.dynamicSmemBytes = smem;
     cfg.stream = st;
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -905,7 +931,7 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
     }
   } else {
     if (grid > max_tiles) grid = max_tiles;
-    kern<<<(int)grid, THREADS, SMEM_BYTES, st>>>(ta, tb, tb2, a);
+    kern<<<(int)grid, THREADS, smem, st>>>(ta, tb, tb2, a);
   }
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;

@@ -684,6 +684,17 @@ int lewi_ep_ipc_import(const void* handle64_host, void** out_host) {
 int lewi_ep_ipc_release(void* ptr) { return cudaIpcCloseMemHandle(ptr) == cudaSuccess ? LEWI_OK : LEWI_ERR_CUDA; }
 
 namespace {
+// The exchange kernels use no shared memory; without this the SMs they run on are switched to an L1-heavy
+// split, and a GEMM CTA (which needs the largest shared-memory split) could not join them until they drain.
+inline void prefer_shared_carveout(const void* kern, bool* done) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64 || done[dev]) return;
+  if (cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared) !=
+      cudaSuccess)
+    (void)cudaGetLastError();
+  done[dev] = true;
+}
+
 inline bool fill_peers(PeerPtrs& pp, void* const* host, int G, bool required) {
   for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = nullptr;
   if (host == nullptr) return !required;
@@ -702,6 +713,8 @@ int lewi_ep_plan(void* stream, const int32_t* counts_all, int G, int E, int me, 
   if (G <= 0 || G > kMaxPeers || E <= 0 || E % G != 0 || me < 0 || me >= G || block <= 0 || rmax_pad <= 0)
     return LEWI_ERR_ARG;
   if (E > kMaxExperts) return LEWI_ERR_LIMIT;
+  static bool carve[64] = {false};
+  prefer_shared_carveout(reinterpret_cast<const void*>(ep_plan_kernel), carve);
   ep_plan_kernel<<<1, 1024, 0, as_stream(stream)>>>(counts_all, G, E, me, block, rmax_pad, (int)(rmax_pad / block),
                                                     dst_base, pad_offsets, valid_end, n_blocks, block_expert,
                                                     recv_rows);
@@ -711,64 +724,84 @@ int lewi_ep_plan(void* stream, const int32_t* counts_all, int G, int E, int me, 
 
 int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const int32_t* flat_expert,
                       const int32_t* offsets, const int32_t* dst_base, const float* slot_w,
-                      void* const* peers_rows_host, void* const* peers_w_host, int32_t* slot_rank,
-                      int32_t* slot_row, int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T) {
+                      void* const* peers_rows_host, void* const* peers_w_host, void* const* peers_ret_host, int me,
+                      int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T, int el_lo, int el_hi) {
   if (!x || !order || !flat_expert || !offsets || !dst_base || M < 0 || k <= 0 || d <= 0 || T < 0) return LEWI_ERR_ARG;
-  if (G <= 0 || G > kMaxPeers || E % G != 0) return LEWI_ERR_ARG;
-  PeerPtrs rows, w;
+  if (G <= 0 || G > kMaxPeers || E <= 0 || E % G != 0 || me < 0 || me >= G || d % 8 != 0) return LEWI_ERR_ARG;
+  if (el_lo < 0 || el_hi > E / G || el_lo > el_hi) return LEWI_ERR_ARG;
+  if (M >= (1ll << kEpSlotBits)) return LEWI_ERR_LIMIT;
+  PeerPtrs rows, w, ret;
   if (!fill_peers(rows, peers_rows_host, G, true)) return LEWI_ERR_ARG;
   if (!fill_peers(w, peers_w_host, G, slot_w != nullptr)) return LEWI_ERR_ARG;
-  const int vpl = pick_vpl(d, 2);
-  if (vpl == 0) return LEWI_ERR_SHAPE;
-  if (M == 0) return LEWI_OK;
-  const int grid = gather_grid(M);
-  cudaStream_t st = as_stream(stream);
-  LEWI_DISPATCH_VPL(vpl, (ep_push_rows_kernel<VPL><<<grid, kGatherThreads, 0, st>>>(
-                             reinterpret_cast<const __nv_bfloat16*>(x), order, flat_expert, offsets, dst_base, slot_w, rows,
-                             w, slot_rank, slot_row, M, k, d, E / G, G, rmax_pad, T)));
+  if (!fill_peers(ret, peers_ret_host, G, false)) return LEWI_ERR_ARG;
+  if (M == 0 || el_lo == el_hi) return LEWI_OK;
+  static bool carve[64] = {false};
+  prefer_shared_carveout(reinterpret_cast<const void*>(ep_push_rows_kernel), carve);
+  ep_push_rows_kernel<<<num_sms(), kEpThreads, 0, as_stream(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), order, flat_expert, offsets, dst_base, slot_w, rows, w, ret, M, k, d, E / G,
+      G, rmax_pad, T, el_lo, el_hi, me);
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
 }
 
-int lewi_ep_zero_pad(void* stream, void* buf, const int32_t* valid_end, const int32_t* pad_offsets, int E_local,
-                     int d, int64_t rmax_pad) {
+int lewi_ep_return_rows(void* stream, const void* rows, const float* pieces, const int32_t* ret,
+                        const int32_t* pad_offsets, int el_lo, int el_hi, void* const* peers_slot_rows_host,
+                        void* const* peers_slot_pieces_host, int d, int parts, int G, int64_t M, int64_t rmax_pad) {
+  if (!ret || !pad_offsets || (!rows && !pieces) || d <= 0 || d % 8 != 0 || G <= 0 || G > kMaxPeers || M < 0)
+    return LEWI_ERR_ARG;
+  if (el_lo < 0 || el_lo > el_hi || (pieces && parts <= 0)) return LEWI_ERR_ARG;
+  PeerPtrs pr, pp;
+  if (!fill_peers(pr, peers_slot_rows_host, G, rows != nullptr)) return LEWI_ERR_ARG;
+  if (!fill_peers(pp, peers_slot_pieces_host, G, pieces != nullptr)) return LEWI_ERR_ARG;
+  if (el_lo == el_hi) return LEWI_OK;
+  static bool carve[64] = {false};
+  prefer_shared_carveout(reinterpret_cast<const void*>(ep_return_rows_kernel), carve);
+  ep_return_rows_kernel<<<num_sms(), kEpThreads, 0, as_stream(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(rows), pieces, ret, pad_offsets, el_lo, el_hi, pr, pp, d, parts, G, M,
+      rmax_pad);
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+int lewi_ep_zero_pad(void* stream, void* buf, int32_t* ret, const int32_t* valid_end, const int32_t* pad_offsets,
+                     int E_local, int d, int64_t rmax_pad) {
   if (!buf || !valid_end || !pad_offsets || E_local <= 0 || d <= 0 || d % 8 != 0) return LEWI_ERR_ARG;
-  ep_zero_pad_kernel<<<E_local, 256, 0, as_stream(stream)>>>(reinterpret_cast<__nv_bfloat16*>(buf), valid_end,
+  static bool carve[64] = {false};
+  prefer_shared_carveout(reinterpret_cast<const void*>(ep_zero_pad_kernel), carve);
+  ep_zero_pad_kernel<<<E_local, 256, 0, as_stream(stream)>>>(reinterpret_cast<__nv_bfloat16*>(buf), ret, valid_end,
                                                              pad_offsets, d, rmax_pad);
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
 }
 
-int lewi_ep_pull_reduce(void* stream, void* const* peers_rows_host, const int32_t* slot_rank,
-                        const int32_t* slot_row, const void* add0, const void* add1, void* out, int64_t T, int k,
-                        int d, int G, int64_t rmax_pad) {
-  if (!slot_rank || !slot_row || !out || T < 0 || k <= 0 || k > kWarp || d <= 0 || G <= 0 || G > kMaxPeers)
-    return LEWI_ERR_ARG;
-  PeerPtrs rows;
-  if (!fill_peers(rows, peers_rows_host, G, true)) return LEWI_ERR_ARG;
-  const int vpl = pick_vpl(d, 2);
-  if (vpl == 0) return LEWI_ERR_SHAPE;
-  if (T == 0) return LEWI_OK;
-  const int grid = gather_grid(T);
-  cudaStream_t st = as_stream(stream);
-  LEWI_DISPATCH_VPL(vpl, (ep_pull_reduce_kernel<VPL><<<grid, kGatherThreads, 0, st>>>(
-                             rows, slot_rank, slot_row, reinterpret_cast<const __nv_bfloat16*>(add0),
-                             reinterpret_cast<const __nv_bfloat16*>(add1), reinterpret_cast<__nv_bfloat16*>(out), T, k, d,
-                             G, rmax_pad)));
+int lewi_ep_put_i32(void* stream, const int32_t* src, void* const* peers_dst_host, int64_t dst_offset, int n, int G) {
+  if (!src || n < 0 || dst_offset < 0 || G <= 0 || G > kMaxPeers) return LEWI_ERR_ARG;
+  PeerPtrs pd;
+  if (!fill_peers(pd, peers_dst_host, G, true)) return LEWI_ERR_ARG;
+  if (n == 0) return LEWI_OK;
+  static bool carve[64] = {false};
+  prefer_shared_carveout(reinterpret_cast<const void*>(ep_put_i32_kernel), carve);
+  ep_put_i32_kernel<<<1, 256, 0, as_stream(stream)>>>(src, pd, dst_offset, n, G);
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
 }
 
-int lewi_ep_pull_dw(void* stream, void* const* peers_partial_host, const int32_t* slot_rank,
-                    const int32_t* slot_row, float* dw, int64_t M, int parts, int G, int64_t rmax_pad) {
-  if (!slot_rank || !slot_row || !dw || M < 0 || parts <= 0 || G <= 0 || G > kMaxPeers) return LEWI_ERR_ARG;
-  PeerPtrs pp;
-  if (!fill_peers(pp, peers_partial_host, G, true)) return LEWI_ERR_ARG;
-  if (M == 0) return LEWI_OK;
-  long long grid = (M + 255) / 256;
-  if (grid > (long long)num_sms() * 8) grid = (long long)num_sms() * 8;
-  ep_pull_dw_kernel<<<(int)grid, 256, 0, as_stream(stream)>>>(pp, slot_rank, slot_row, dw, M, parts, G, rmax_pad);
+int lewi_ep_barrier(void* stream, void* const* peers_flags_host, int32_t* my_flags, int32_t* epoch_counter, int me,
+                    int G, int64_t timeout_ms) {
+  if (!my_flags || !epoch_counter || G <= 0 || G > kMaxPeers || me < 0 || me >= G || timeout_ms <= 0 || timeout_ms > 10000)
+    return LEWI_ERR_ARG;
+  PeerPtrs pf;
+  if (!fill_peers(pf, peers_flags_host, G, true)) return LEWI_ERR_ARG;
+  static bool carve[64] = {false};
+  prefer_shared_carveout(reinterpret_cast<const void*>(ep_barrier_kernel), carve);
+  ep_barrier_kernel<<<1, 32, 0, as_stream(stream)>>>(pf, my_flags, epoch_counter, me, G,
+                                                     (unsigned long long)timeout_ms * 1000000ull);
   LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+int lewi_set_sm_sharing(int on) {
+  gg::sm_sharing() = on != 0;
   return LEWI_OK;
 }
 

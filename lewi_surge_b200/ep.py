@@ -270,20 +270,30 @@ class _SymmetricBuffer:
 class ExpertParallelP2P:
   """Expert-parallel MoE layer whose dispatch and combine are kernels over peer memory.
 
-  Every rank routes its own tokens and all-gathers the expert histogram (the only data-dependent
-  collective, 4*E bytes per rank); `lewi_ep_plan` turns it into row offsets on every owner.  Rows are then
-  pushed straight into the owners' padded buffers (`lewi_ep_push_rows`), the owners run the grouped GEMMs in
-  place, and the sources pull and sum their results (`lewi_ep_pull_reduce`).  The backward pass pushes the
-  upstream gradient rows the same way and pulls dx and the routing-weight gradient pieces.  Ordering between
-  ranks is a one-element all-reduce on the compute stream (stream-ordered: it completes on a rank only when
-  every rank has reached it, i.e. has finished the kernels queued before it).  No host synchronisation.
+  Every rank routes its own tokens and shares its expert histogram (4*E bytes, stored into every peer's table);
+  `lewi_ep_plan` turns the histograms into row offsets on every owner.  Rows are then pushed straight into the
+  owners' padded buffers together with their return address (`lewi_ep_push_rows`), the owners run the grouped
+  GEMMs in place and push every output row back into the source's slot-ordered buffer
+  (`lewi_ep_return_rows`), where the combine is a sum over k consecutive rows.  The backward pass moves the
+  upstream gradient rows, dx and the routing-weight gradient pieces the same way.
+
+  The local experts are worked on in `phases` ranges.  The exchange kernels run on their own stream and are small
+  enough to share an SM with a grouped-GEMM CTA, so the rows of range p+1 arrive, and the outputs of range p-1
+  leave, while the GEMMs of range p run.  (More than one range needs the CTA-pair GEMM kernels, which find a row
+  block's expert from pad_offsets alone.)
+
+  Ordering between ranks (`sync`): "flags" uses `lewi_ep_barrier`, a one-warp kernel that exchanges epoch flags
+  through peer memory with a bounded wait; "nccl" uses a one-element all-reduce.  Both are stream-ordered: a rank
+  passes only when every rank has finished the kernels queued before it.  No host synchronisation.
 
   `capacity` bounds the rows a rank can receive as a multiple of its own routed rows (M = T*k); the buffers are
   allocated once for that bound.  More rows than that raise LEWI_STATUS_EP_OVERFLOW (rows are dropped, not
   written out of bounds).
   """
 
-  def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None):
+  BARRIER_TIMEOUT_MS = 4000
+
+  def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None, phases=None, sync="flags"):
     from . import _lib, layer, ops
     self.lib, self.layer, self.ops, self._lib = _lib.load(), layer, ops, _lib
     self.w, self.k, self.e, self.d, self.t = w, k, num_experts, d, tokens
@@ -293,121 +303,277 @@ class ExpertParallelP2P:
       raise ValueError("num_experts must be divisible by the number of ranks")
     if self.world > 8:
       raise ValueError("at most 8 ranks (one NVSwitch node)")
+    if sync not in ("flags", "nccl"):
+      raise ValueError("sync must be 'flags' or 'nccl'")
+    self.sync = sync
     self.el = num_experts // self.world
     self.f = w.w_gate.shape[2]
     self.dev = w.w_gate.device
     self.m = tokens * k
+    want = int(phases) if phases is not None else (1 if self.world == 1 else 4)
+    self.phases = max(1, min(want, self.el))
+    self.bounds = [self.el * p // self.phases for p in range(self.phases + 1)]
     cap = float(capacity) if capacity is not None else min(float(self.world), 2.0)
     rows = int(self.m * cap)
     self.rmax = (rows + self.el * (BLOCK - 1)) // BLOCK * BLOCK
     self.parts = int(self.lib.lewi_dw_partial_parts(self.f))
-    bf = torch.bfloat16
-    sb = lambda nbytes: _SymmetricBuffer(nbytes, group, self.dev)
-    self.s_x, self.s_w = sb(self.rmax * d * 2), sb(self.rmax * 4)
-    self.s_ys, self.s_dy, self.s_dxs = sb(self.rmax * d * 2), sb(self.rmax * d * 2), sb(self.rmax * d * 2)
-    self.s_dwp = sb(self.rmax * self.parts * 4)
-    self.recv_x = self.s_x.local.tensor((self.rmax, d), bf)
-    self.recv_w = self.s_w.local.tensor((self.rmax,), torch.float32)
-    self.ys = self.s_ys.local.tensor((self.rmax, d), bf)
-    self.recv_dy = self.s_dy.local.tensor((self.rmax, d), bf)
-    self.dxs = self.s_dxs.local.tensor((self.rmax, d), bf)
-    self.dwp = self.s_dwp.local.tensor((self.rmax, self.parts), torch.float32)
+    bf, f32 = torch.bfloat16, torch.float32
     i32 = dict(dtype=torch.int32, device=self.dev)
-    self.counts_all = torch.zeros(self.world * num_experts, **i32)
+    sb = lambda nbytes: _SymmetricBuffer(nbytes, group, self.dev)
+    # written by peers: received rows, their router weights and return addresses; returned rows in slot order
+    self.s_x, self.s_w, self.s_ret = sb(self.rmax * d * 2), sb(self.rmax * 4), sb(self.rmax * 4)
+    self.s_dy = sb(self.rmax * d * 2)
+    self.s_yslot, self.s_dxslot = sb(max(self.m, 1) * d * 2), sb(max(self.m, 1) * d * 2)
+    self.s_dwslot = sb(max(self.m, 1) * self.parts * 4)
+    self.s_counts, self.s_flags = sb(self.world * num_experts * 4), sb(self.world * 4)
+    self.recv_x = self.s_x.local.tensor((self.rmax, d), bf)
+    self.recv_w = self.s_w.local.tensor((self.rmax,), f32)
+    self.ret = self.s_ret.local.tensor((self.rmax,), torch.int32)
+    self.recv_dy = self.s_dy.local.tensor((self.rmax, d), bf)
+    self.y_slot = self.s_yslot.local.tensor((max(self.m, 1), d), bf)[:self.m]
+    self.dx_slot = self.s_dxslot.local.tensor((max(self.m, 1), d), bf)[:self.m]
+    self.dw_slot = self.s_dwslot.local.tensor((max(self.m, 1), self.parts), f32)[:self.m]
+    self.counts_all = self.s_counts.local.tensor((self.world * num_experts,), torch.int32)
+    self.flags = self.s_flags.local.tensor((self.world,), torch.int32)
+    # local to the owner
+    self.ys = torch.empty((self.rmax, d), dtype=bf, device=self.dev)
+    self.dxs = torch.empty((self.rmax, d), dtype=bf, device=self.dev)
+    self.dwp = torch.zeros((self.rmax, self.parts), dtype=f32, device=self.dev)
     self.dst_base = torch.zeros(num_experts, **i32)
     self.pad_offsets = torch.zeros(self.el + 1, **i32)
     self.valid_end = torch.zeros(self.el, **i32)
     self.n_blocks = torch.zeros(1, **i32)
     self.block_expert = torch.zeros(self.rmax // BLOCK, **i32)
     self.recv_rows = torch.zeros(1, **i32)
-    self.slot_rank = torch.zeros(self.m, **i32)
-    self.slot_row = torch.zeros(self.m, **i32)
-    self._flag = torch.zeros(1, dtype=torch.float32, device=self.dev)
+    self.slot_ids = torch.arange(max(self.m, 1), **i32)[:self.m].view(tokens, k)
+    self._flag = torch.zeros(1, dtype=f32, device=self.dev)
+    self._epoch = torch.zeros(1, **i32)   # barriers passed so far, counted on the device
+    # Exchange kernels and whatever orders them between ranks run on their own stream, the GEMMs on the caller's.
+    self.comm = torch.cuda.Stream(self.dev)
     self.recv_w.zero_()
+    self.ret.fill_(-1)
+    self.flags.zero_()
+    self.counts_all.zero_()
     torch.cuda.synchronize(self.dev)
     dist.barrier(group=group)
 
   def _sync_ranks(self):
-    dist.all_reduce(self._flag, group=self.group)
+    """Barrier between the ranks in the order of the current stream."""
+    if self.sync == "nccl":
+      dist.all_reduce(self._flag, group=self.group)
+      return
+    self._lib.check(self.lib.lewi_ep_barrier(self._lib.stream(), self.s_flags.c_ptrs, self._lib.ptr(self.flags),
+                                             self._lib.ptr(self._epoch), self.rank, self.world, self.BARRIER_TIMEOUT_MS),
+                    "lewi_ep_barrier")
+
+  def _range(self, p):
+    """(lo, hi, pad_offsets, block_expert, n_blocks) of local-expert range p."""
+    lo, hi = self.bounds[p], self.bounds[p + 1]
+    if self.phases == 1:
+      return lo, hi, self.pad_offsets, self.block_expert, self.n_blocks
+    # a sub-range has no block table of its own: the CTA-pair kernels read pad_offsets alone
+    return lo, hi, self.pad_offsets[lo:hi + 1], None, None
 
   def forward(self, x):
+    self.lib.lewi_set_sm_sharing(1)   # exchange CTAs run beside the GEMM CTAs
+    try:
+      return self._forward(x)
+    finally:
+      self.lib.lewi_set_sm_sharing(0)
+
+  def _pipeline(self, push, gemms, give_back, first=None):
+    """Issue order of one pass.  On the exchange stream: push 0, push 1, then for every range p >= 1 push p+1 followed
+    by the return of range p-1, last the return of the final range and a barrier.  On the caller's stream: the GEMMs of
+    range p once its rows have arrived.  So while range p is being multiplied, range p+1 is arriving and range p-1 is
+    on its way back.  Returns with the caller's stream waiting for the final barrier."""
+    L, P = self.layer, self.phases
+    main, comm = torch.cuda.current_stream(self.dev), self.comm
+    arrived, done = {}, {}
+
+    def do_push(p):
+      with torch.cuda.stream(comm):
+        push(p)
+        self._sync_ranks()   # the rows of this range have arrived everywhere
+        L._mark("ep_barrier")
+        arrived[p] = comm.record_event()
+
+    def do_return(p):
+      with torch.cuda.stream(comm):
+        comm.wait_event(done[p])
+        L._mark("side_begin")
+        give_back(p)
+
+    do_push(0)
+    if P > 1:
+      do_push(1)
+    if first is not None:
+      first()   # work of the caller's stream that needs no rows from other ranks
+    for p in range(P):
+      if p >= 1:
+        if p + 1 < P:
+          do_push(p + 1)
+        do_return(p - 1)
+      main.wait_event(arrived[p])
+      L._mark("step_begin")
+      gemms(p, lambda: done.__setitem__(p, main.record_event()))
+    do_return(P - 1)
+    with torch.cuda.stream(comm):
+      self._sync_ranks()   # everything is back at its source
+      L._mark("ep_barrier")
+      returned = comm.record_event()
+    main.wait_event(returned)
+    L._mark("step_begin")
+
+  def _forward(self, x):
     lib, L, ops, _lib, w, k = self.lib, self.layer, self.ops, self._lib, self.w, self.k
     st, ptr, check = _lib.stream, _lib.ptr, _lib.check
     t, d = x.shape
+    f, G = self.f, self.world
+    main, comm = torch.cuda.current_stream(self.dev), self.comm
     logits = L.router_logits(x, w.w_router, w.router_bias)
+    L._mark("router_logits")
     tb = L.router_topk(logits, k)
-    dist.all_gather_into_tensor(self.counts_all, tb.counts, group=self.group)
-    check(lib.lewi_ep_plan(st(), ptr(self.counts_all), self.world, self.e, self.rank, BLOCK, self.rmax, ptr(self.dst_base),
-                           ptr(self.pad_offsets), ptr(self.valid_end), ptr(self.n_blocks), ptr(self.block_expert),
-                           ptr(self.recv_rows)), "lewi_ep_plan")
-    self._sync_ranks()   # every rank is done reading the buffers of the previous step
-    check(lib.lewi_ep_push_rows(st(), ptr(x), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
-                                ptr(tb.topk_w), self.s_x.c_ptrs, self.s_w.c_ptrs, ptr(self.slot_rank), ptr(self.slot_row),
-                                self.m, k, d, self.e, self.world, self.rmax, t), "lewi_ep_push_rows")
-    check(lib.lewi_ep_zero_pad(st(), ptr(self.recv_x), ptr(self.valid_end), ptr(self.pad_offsets), self.el, d, self.rmax),
-          "lewi_ep_zero_pad")
-    # the shared expert needs nothing from other ranks: it fills the time the rows are in flight
-    shared = None
-    if w.ws_gate is not None:
+    L._mark("router_topk")
+    routed = main.record_event()
+    with torch.cuda.stream(comm):
+      comm.wait_event(routed)
+      L._mark("side_begin")
+      check(lib.lewi_ep_put_i32(st(), ptr(tb.counts), self.s_counts.c_ptrs, self.rank * self.e, self.e, G),
+            "lewi_ep_put_i32")
+      L._mark("ep_put_counts")
+      self._sync_ranks()   # histograms are everywhere; every rank is done with the buffers of the previous step
+      L._mark("ep_barrier")
+      check(lib.lewi_ep_plan(st(), ptr(self.counts_all), G, self.e, self.rank, BLOCK, self.rmax, ptr(self.dst_base),
+                             ptr(self.pad_offsets), ptr(self.valid_end), ptr(self.n_blocks), ptr(self.block_expert),
+                             ptr(self.recv_rows)), "lewi_ep_plan")
+      L._mark("ep_plan")
+      check(lib.lewi_ep_zero_pad(st(), ptr(self.recv_x), ptr(self.ret), ptr(self.valid_end), ptr(self.pad_offsets),
+                                 self.el, d, self.rmax), "lewi_ep_zero_pad")
+      L._mark("ep_zero_pad")
+    gu = torch.empty((self.rmax, 2 * f), dtype=torch.bfloat16, device=self.dev)
+    h = torch.empty((self.rmax, f), dtype=torch.bfloat16, device=self.dev)
+    shared = []
+
+    def push(p):
+      check(lib.lewi_ep_push_rows(st(), ptr(x), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
+                                  ptr(tb.topk_w), self.s_x.c_ptrs, self.s_w.c_ptrs, self.s_ret.c_ptrs, self.rank, self.m,
+                                  k, d, self.e, G, self.rmax, t, self.bounds[p], self.bounds[p + 1]), "lewi_ep_push_rows")
+      L._mark("ep_push_x")
+
+    def gemms(p, mark_done):
+      lo, hi, po, be, nb = self._range(p)
+      check(lib.lewi_grouped_gemm_gateup_swiglu_gather(st(), ptr(self.recv_x), None, 1, self.rmax, None, ptr(self.recv_w),
+                                                       ptr(w.w_gate[lo:hi]), ptr(w.w_up[lo:hi]), ptr(gu), ptr(h), ptr(be),
+                                                       ptr(nb), ptr(po), self.rmax, d, f, hi - lo),
+            "lewi_grouped_gemm_gateup_swiglu")
+      L._mark("gemm_gateup_swiglu")
+      ops.grouped_gemm_nn(h, w.w_down[lo:hi], be, nb, pad_offsets=po, out=self.ys)
+      L._mark("gemm_down")
+      mark_done()
+
+    def give_back(p):
+      check(lib.lewi_ep_return_rows(st(), ptr(self.ys), None, ptr(self.ret), ptr(self.pad_offsets), self.bounds[p],
+                                    self.bounds[p + 1], self.s_yslot.c_ptrs, None, d, self.parts, G, self.m, self.rmax),
+            "lewi_ep_return_rows")
+      L._mark("ep_return_y")
+
+    def shared_expert():   # needs nothing from other ranks: it fills the time the first rows are in flight
+      if w.ws_gate is None:
+        return
       gus, hs = L.gateup_swiglu(x, w.ws_gate[None], w.ws_up[None], None, None)
-      shared = (gus, hs, ops.grouped_gemm_nn(hs, w.ws_down[None], None, None))
-    self._sync_ranks()   # all rows have arrived
-    po = self.pad_offsets
-    gu, h = L.gateup_swiglu(self.recv_x, w.w_gate, w.w_up, self.block_expert, self.n_blocks, pad_offsets=po,
-                            h_scale_src=self.recv_w)
-    ops.grouped_gemm_nn(h, w.w_down, self.block_expert, self.n_blocks, pad_offsets=po, out=self.ys)
-    self._sync_ranks()   # all expert outputs are written
-    out = torch.empty_like(x)
-    check(lib.lewi_ep_pull_reduce(st(), self.s_ys.c_ptrs, ptr(self.slot_rank), ptr(self.slot_row),
-                                  ptr(shared[2]) if shared else None, None, ptr(out), t, k, d, self.world, self.rmax),
-          "lewi_ep_pull_reduce")
-    return out, dict(x=x, logits=logits, tb=tb, gu=gu, h=h, shared=shared)
+      L._mark("shared_gateup_swiglu")
+      shared.extend((gus, hs, ops.grouped_gemm_nn(hs, w.ws_down[None], None, None)))
+      L._mark("shared_down")
+
+    self._pipeline(push, gemms, give_back, first=shared_expert)
+    out = ops.gather_reduce(self.y_slot, self.slot_ids, None, x.dtype, add0=shared[2] if shared else None)
+    L._mark("combine_reduce")
+    return out, dict(x=x, logits=logits, tb=tb, gu=gu, h=h, shared=tuple(shared) or None)
 
   def backward(self, dout, c):
+    self.lib.lewi_set_sm_sharing(1)
+    try:
+      return self._backward(dout, c)
+    finally:
+      self.lib.lewi_set_sm_sharing(0)
+
+  def _backward(self, dout, c):
     lib, L, ops, _lib, w, k = self.lib, self.layer, self.ops, self._lib, self.w, self.k
     st, ptr, check = _lib.stream, _lib.ptr, _lib.check
     x, tb = c["x"], c["tb"]
     t, d = x.shape
+    f, G = self.f, self.world
+    main, comm = torch.cuda.current_stream(self.dev), self.comm
     dout = dout.contiguous()
-    check(lib.lewi_ep_push_rows(st(), ptr(dout), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
-                                None, self.s_dy.c_ptrs, None, None, None, self.m, k, d, self.e, self.world, self.rmax, t),
-          "lewi_ep_push_rows")
-    check(lib.lewi_ep_zero_pad(st(), ptr(self.recv_dy), ptr(self.valid_end), ptr(self.pad_offsets), self.el, d, self.rmax),
-          "lewi_ep_zero_pad")
+    ready = main.record_event()
+    with torch.cuda.stream(comm):
+      comm.wait_event(ready)
+      L._mark("side_begin")
+      check(lib.lewi_ep_zero_pad(st(), ptr(self.recv_dy), None, ptr(self.valid_end), ptr(self.pad_offsets), self.el, d,
+                                 self.rmax), "lewi_ep_zero_pad")
+      L._mark("ep_zero_pad")
     grads = {}
-    dxsh = None
-    if c["shared"] is not None:
+    dxsh = []
+
+    def shared_expert():
+      if c["shared"] is None:
+        return
       gus, hs, _ = c["shared"]
       dgus = L.dh_dswiglu(dout, w.ws_down[None], gus, None, None)
+      L._mark("shared_dh_dswiglu")
       grads["dws_down"] = ops.grouped_gemm_tn(hs, dout, None, 1, out_dtype=w.ws_down.dtype)[0]
-      dxsh = L.dx_from_dgu(dgus, w.ws_gate[None], w.ws_up[None], None, None)
+      L._mark("shared_dw_down")
+      dxsh.append(L.dx_from_dgu(dgus, w.ws_gate[None], w.ws_up[None], None, None))
+      L._mark("shared_dx")
       g1, g2 = ops.grouped_gemm_tn(x, dgus, None, 1, out_dtype=w.ws_gate.dtype, split=True)
+      L._mark("shared_dw_gateup")
       grads["dws_gate"], grads["dws_up"] = g1[0], g2[0]
-    self._sync_ranks()   # all upstream-gradient rows have arrived
-    po = self.pad_offsets
-    lib_parts = self.parts
-    dgu = torch.empty((self.rmax, 2 * self.f), dtype=torch.bfloat16, device=self.dev)
-    check(lib.lewi_grouped_gemm_dh_dswiglu_gather(st(), ptr(self.recv_dy), None, 1, self.rmax, None, ptr(self.recv_w),
-                                                  ptr(self.dwp), ptr(w.w_down), ptr(c["gu"]), ptr(dgu),
-                                                  ptr(self.block_expert), ptr(self.n_blocks), ptr(po), self.rmax, d, self.f,
-                                                  self.el), "lewi_grouped_gemm_dh_dswiglu")
-    grads["dw_down"] = ops.grouped_gemm_tn(c["h"], self.recv_dy, po, self.el, out_dtype=w.w_down.dtype)
-    check(lib.lewi_grouped_gemm_dx(st(), ptr(dgu), ptr(w.w_gate), ptr(w.w_up), ptr(self.dxs), ptr(self.block_expert),
-                                   ptr(self.n_blocks), ptr(po), self.rmax, d, self.f, self.el), "lewi_grouped_gemm_dx")
-    grads["dw_gate"], grads["dw_up"] = ops.grouped_gemm_tn(self.recv_x, dgu, po, self.el, out_dtype=w.w_gate.dtype,
-                                                           split=True)
-    self._sync_ranks()   # dxs and the routing-weight gradient pieces are written everywhere
-    dw = torch.empty((t, k), dtype=torch.float32, device=self.dev)
-    check(lib.lewi_ep_pull_dw(st(), self.s_dwp.c_ptrs, ptr(self.slot_rank), ptr(self.slot_row), ptr(dw), self.m,
-                              lib_parts, self.world, self.rmax), "lewi_ep_pull_dw")
+
+    dgu = torch.empty((self.rmax, 2 * f), dtype=torch.bfloat16, device=self.dev)
+    grads["dw_down"] = torch.empty_like(w.w_down)
+    grads["dw_gate"], grads["dw_up"] = torch.empty_like(w.w_gate), torch.empty_like(w.w_up)
+
+    def push(p):
+      check(lib.lewi_ep_push_rows(st(), ptr(dout), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
+                                  None, self.s_dy.c_ptrs, None, None, self.rank, self.m, k, d, self.e, G, self.rmax, t,
+                                  self.bounds[p], self.bounds[p + 1]), "lewi_ep_push_rows")
+      L._mark("ep_push_dout")
+
+    def gemms(p, mark_done):
+      lo, hi, po, be, nb = self._range(p)
+      check(lib.lewi_grouped_gemm_dh_dswiglu_gather(st(), ptr(self.recv_dy), None, 1, self.rmax, None, ptr(self.recv_w),
+                                                    ptr(self.dwp), ptr(w.w_down[lo:hi]), ptr(c["gu"]), ptr(dgu), ptr(be),
+                                                    ptr(nb), ptr(po), self.rmax, d, f, hi - lo),
+            "lewi_grouped_gemm_dh_dswiglu")
+      L._mark("gemm_dh_dswiglu")
+      check(lib.lewi_grouped_gemm_dx(st(), ptr(dgu), ptr(w.w_gate[lo:hi]), ptr(w.w_up[lo:hi]), ptr(self.dxs), ptr(be),
+                                     ptr(nb), ptr(po), self.rmax, d, f, hi - lo), "lewi_grouped_gemm_dx")
+      L._mark("gemm_dx")
+      mark_done()   # the weight gradients below are of no interest to the other ranks
+      ops.grouped_gemm_tn(c["h"], self.recv_dy, po, hi - lo, out=grads["dw_down"][lo:hi])
+      L._mark("gemm_dw_down")
+      ops.grouped_gemm_tn(self.recv_x, dgu, po, hi - lo, out=grads["dw_gate"][lo:hi], out2=grads["dw_up"][lo:hi],
+                          split=True)
+      L._mark("gemm_dw_gateup")
+
+    def give_back(p):
+      check(lib.lewi_ep_return_rows(st(), ptr(self.dxs), ptr(self.dwp), ptr(self.ret), ptr(self.pad_offsets),
+                                    self.bounds[p], self.bounds[p + 1], self.s_dxslot.c_ptrs, self.s_dwslot.c_ptrs, d,
+                                    self.parts, G, self.m, self.rmax), "lewi_ep_return_rows")
+      L._mark("ep_return_dx")
+
+    self._pipeline(push, gemms, give_back, first=shared_expert)
+    _, dlb, dw = L.router_topk_bwd(c["logits"], tb.topk_idx, None, want_f32=False, want_bf16=True, dw_partial=self.dw_slot,
+                                   pad_pos=self.slot_ids)
+    L._mark("router_topk_bwd")
     grads["dw"] = dw
-    _, dlb = L.router_topk_bwd(c["logits"], tb.topk_idx, dw, want_f32=False, want_bf16=True)
     dx_r = ops.grouped_gemm_nt(dlb, L.cast_bf16(w.w_router)[None], None, None)
+    L._mark("router_dx")
     grads["dw_router"] = ops.grouped_gemm_tn(x, dlb, None, 1, out_dtype=torch.float32)[0]
-    dx = torch.empty_like(x)
-    check(lib.lewi_ep_pull_reduce(st(), self.s_dxs.c_ptrs, ptr(self.slot_rank), ptr(self.slot_row), ptr(dxsh), ptr(dx_r),
-                                  ptr(dx), t, k, d, self.world, self.rmax), "lewi_ep_pull_reduce")
-    grads["dx"] = dx
+    L._mark("router_dw")
+    grads["dx"] = ops.gather_reduce(self.dx_slot, self.slot_ids, None, x.dtype, add0=dxsh[0] if dxsh else None,
+                                    add1=dx_r)
+    L._mark("combine_bwd_reduce")
     return grads
 
   def step(self, x, dout):

@@ -41,14 +41,18 @@ def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
     w = MoEWeights(tt(inp["w_router"], torch.float32), tt(inp["w_gate"][rank * el:(rank + 1) * el]),
                    tt(inp["w_up"][rank * el:(rank + 1) * el]), tt(inp["w_down"][rank * el:(rank + 1) * el]),
                    tt(inp["ws_gate"]), tt(inp["ws_up"]), tt(inp["ws_down"]))
-    if impl == "p2p":
-      lay = ep.ExpertParallelP2P(w, k, e, t, d, capacity=float(world))
+    if impl.startswith("p2p"):
+      # "p2p": one exchange per pass; "p2p-phased": pipelined over ranges of local experts; "p2p-nccl": ranks
+      # ordered by a one-element all-reduce instead of the flag barrier
+      phases = {"p2p": 1, "p2p-phased": 4, "p2p-nccl": 2}[impl]
+      lay = ep.ExpertParallelP2P(w, k, e, t, d, capacity=float(world), phases=phases,
+                                 sync="nccl" if impl == "p2p-nccl" else "flags")
     else:
       lay = ep.ExpertParallelLayer(w, k, e)
     sl = slice(rank * t, (rank + 1) * t)
     xr, gr = tt(inp["x"][sl]), tt(inp["dout"][sl])
     out, grads = lay.step(xr, gr)
-    if impl == "p2p":     # a second step over the same buffers must give the same answer
+    if impl.startswith("p2p"):     # a second step over the same buffers must give the same answer
       out2, grads2 = lay.step(xr, gr)
       assert torch.equal(out, out2) and torch.equal(grads["dx"], grads2["dx"])
     assert _lib.last_status() == 0
@@ -59,12 +63,13 @@ def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
     dist.destroy_process_group()
 
 
-def test_peer_memory_layer_on_one_gpu(cuda, tmp_path):
+@pytest.mark.parametrize("impl", ["p2p", "p2p-phased"])
+def test_peer_memory_layer_on_one_gpu(cuda, tmp_path, impl):
   """World size 1: the push / pull kernels and the plan run against this GPU's own buffers."""
-  _check(cuda, tmp_path, (512, 256, 16, 128, 128, 4), 1, "p2p")
+  _check(cuda, tmp_path, (512, 256, 16, 128, 128, 4), 1, impl)
 
 
-@pytest.mark.parametrize("impl", ["nccl", "p2p"])
+@pytest.mark.parametrize("impl", ["nccl", "p2p", "p2p-phased", "p2p-nccl"])
 @pytest.mark.parametrize("cfg", [(512, 256, 16, 128, 128, 4), (1024, 1024, 64, 512, 512, 6)])
 def test_expert_parallel_matches_single_gpu(cuda, tmp_path, cfg, impl):
   world = min(torch.cuda.device_count(), 4)
