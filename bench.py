@@ -37,12 +37,22 @@ def layer_flops(c):
   return 18 * m * c["d"] * c["f"] + 18 * c["T"] * c["d"] * c["fs"] + 6 * c["T"] * c["d"] * c["E"]
 
 
-def kernel_work(c):
-  """Algorithmic work per launch of each kernel of the step: (bound, amount) in flops or bytes."""
+# One-directional peer copy measured on this pool's NVLink 5 / NVSwitch (900 GB/s nominal per direction).
+NVLINK_GBS = 770.0
+
+
+def kernel_work(c, world=1):
+  """Algorithmic work per step of each kernel name: (bound, amount) in flops or bytes.  For the exchange kernels of
+  the expert-parallel layer the amount is the bytes that must cross NVLink: the rows routed to other ranks."""
   T, d, E, f, k, fs = c["T"], c["d"], c["E"], c["f"], c["k"], c["fs"]
   m = T * k
   row = 2 * d
+  away = m * row * (world - 1) / world
   return {
+      "ep_push_x": ("nvlink", away), "ep_push_dout": ("nvlink", away),
+      "ep_return_y": ("nvlink", away), "ep_return_dx": ("nvlink", away),
+      "combine_reduce": ("hbm", (m + 2 * T) * row),
+      "combine_bwd_reduce": ("hbm", (m + 4 * T) * row),
       "router_logits": ("hbm", T * row + T * E * 4 + d * E * 4),
       "router_topk": ("hbm", T * E * 4 + m * 4 * 6),
       "dispatch_gather": ("hbm", (T + m) * row),
@@ -222,6 +232,7 @@ def main():
   ap.add_argument("--ep-impl", default="p2p", choices=["p2p", "nccl"],
                   help="N > 1: dispatch/combine as kernels over peer memory (default) or as NCCL all-to-all")
   ap.add_argument("--ep-capacity", type=float, default=None, help="receive-buffer rows as a multiple of T*k")
+  ap.add_argument("--no-graph", action="store_true", help="queue every timed step eagerly instead of replaying a CUDA graph")
   ap.add_argument("--timeline", default=None, help="write the last timed step's event marks (rank 0) to this file")
   ap.add_argument("--ep-sync", choices=["flags", "nccl"], default="flags", help="how the exchange orders the ranks")
   ap.add_argument("--ep-phases", type=int, default=None, help="ranges of local experts the exchange is pipelined over")
@@ -282,60 +293,125 @@ def main():
     step_fn()
   barrier()
 
-  # ---- timed region: K steps, CUDA events on the launching stream, per-kernel events inside it
-  marks = []
-  def hook(name):
-    ev = torch.cuda.Event(enable_timing=True)
-    ev.record()
-    marks.append((name, ev, torch.cuda.current_stream().cuda_stream))
+  # ---- timed region: K steps between two CUDA events on the launching stream.  The step is replayed from a CUDA
+  # graph when it can be captured (no host synchronisation inside), so that a busy host does not show up in the
+  # number; --no-graph queues every step eagerly.
+  timed_fn, timed_with = step_fn, "eager launches"
+  capturable = world == 1 or (args.ep_impl == "p2p" and args.ep_sync == "flags")
+  if capturable and not args.no_graph:
+    try:
+      timed_fn = layer.CapturedStep(step_fn)
+      timed_with = "cuda graph replay"
+      for _ in range(2):
+        timed_fn()
+    except Exception as exc:   # keep going eagerly; the line says so
+      timed_fn, timed_with = step_fn, f"eager launches (capture failed: {type(exc).__name__})"
+    barrier()
   sampler = ClockSampler(local_rank)
   if rank == 0:
     sampler.start()
-  layer.set_profile_hook(hook)
-  launches0 = lib.lewi_launch_count()
   ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
   barrier()
   ev0.record()
-  host0 = time.perf_counter()
   for _ in range(args.steps):
-    hook("bench_step")
-    step_fn()
-  host_ms = (time.perf_counter() - host0) * 1e3 / args.steps   # time the host needs to queue one step
+    timed_fn()
   ev1.record()
   barrier()
-  launches = lib.lewi_launch_count() - launches0
-  layer.set_profile_hook(None)
-  clocks = sampler.stop() if rank == 0 else None
   ms_total = ev0.elapsed_time(ev1)
   tms = torch.tensor([ms_total], dtype=torch.float64, device=device)
   if world > 1:
     dist.all_reduce(tms, op=dist.ReduceOp.MAX)
   ms_step = float(tms.item()) / args.steps
+
+  # ---- per-kernel durations: a CUDA event after every kernel.  The events are recorded into a second graph
+  # (external event nodes) and read back after every replay, so that the gaps a slow host leaves between eager
+  # launches do not count as kernel time; if that cannot be captured the step is queued eagerly instead.
+  marks = []
+  external = [True]
+  def hook(name):
+    ev = torch.cuda.Event(enable_timing=True, external=True) if external[0] else torch.cuda.Event(enable_timing=True)
+    ev.record()
+    marks.append((name, ev, torch.cuda.current_stream().cuda_stream))
+  n_prof = max(3, min(args.steps, 10))
+  per, overlapped = {}, set()
+  def account(step_marks):
+    last = {}   # previous mark on the same stream (the shared expert / the exchange run on a side stream)
+    main_sid = step_marks[0][2]
+    total = {}  # a name that occurs several times in a step (one launch per range of experts) is summed
+    for name, ev, sid in step_marks:
+      prev = last.get(sid)
+      last[sid] = ev
+      if name in ("bench_step", "step_begin", "side_begin") or prev is None:
+        continue
+      total[name] = total.get(name, 0.0) + prev.elapsed_time(ev)
+      if sid != main_sid:
+        overlapped.add(name)   # elapsed time on a side stream includes waiting for SMs: not a kernel duration
+    for name, ms in total.items():
+      per.setdefault(name, []).append(ms)
+  def profiled_step():
+    hook("bench_step")
+    return step_fn()
+  kernel_events = "events in a replayed cuda graph"
+  layer.set_profile_hook(hook)
+  # A kernel's duration is taken with nothing else on the GPU: in this pass the shared expert runs in line instead
+  # of on its side stream (the timed region above keeps the overlap).  The exchange of the expert-parallel layer
+  # cannot be taken out, so at N > 1 GEMM durations include what the exchange kernels take from them.
+  overlap_shared, layer.OVERLAP_SHARED = layer.OVERLAP_SHARED, False
+  try:
+    if not capturable or args.no_graph:
+      raise RuntimeError("eager")
+    prof = layer.CapturedStep(profiled_step, keep_profile_hook=True)
+    step_marks = list(marks)
+    for _ in range(n_prof):
+      barrier()
+      prof()
+      torch.cuda.synchronize()
+      account(step_marks)
+  except Exception:
+    kernel_events = "events between eager launches"
+    external[0] = False
+    del marks[:]
+    per.clear()
+    barrier()
+    for _ in range(n_prof):
+      profiled_step()
+    barrier()
+    starts = [i for i, mk in enumerate(marks) if mk[0] == "bench_step"] + [len(marks)]
+    for a, b in zip(starts[:-1], starts[1:]):
+      account(marks[a:b])
+    step_marks = marks[starts[-2]:]
+  layer.set_profile_hook(None)
+  layer.OVERLAP_SHARED = overlap_shared
+  kernels = {n: sum(v) / len(v) for n, v in per.items()}
+
+  # ---- the same step queued eagerly: launch count, and how long the host needs to queue a step
+  n_eager = max(3, min(args.steps, 10))
+  launches0 = lib.lewi_launch_count()
+  barrier()
+  ev0.record()
+  host0 = time.perf_counter()
+  for _ in range(n_eager):
+    step_fn()
+  host_ms = (time.perf_counter() - host0) * 1e3 / n_eager
+  ev1.record()
+  barrier()
+  launches_per_step = (lib.lewi_launch_count() - launches0) // n_eager
+  launches = launches_per_step * args.steps
+  clocks = sampler.stop() if rank == 0 else None
+  tms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=device)
+  if world > 1:
+    dist.all_reduce(tms, op=dist.ReduceOp.MAX)
+  eager_ms_step = float(tms.item()) / n_eager
   status = _lib.last_status()
   if status != 0:
     raise SystemExit(f"device status {status} after the timed region (a bounded wait ran out or an index was bad)")
 
-  # per-kernel durations (averaged over steps)
-  per = {}
-  last = {}   # previous mark on the same stream (the shared expert runs on a side stream)
-  main_sid = marks[0][2] if marks else None
-  overlapped = set()
-  for name, ev, sid in marks:
-    prev = last.get(sid)
-    last[sid] = ev
-    if name in ("bench_step", "step_begin", "side_begin") or prev is None:
-      continue
-    per.setdefault(name, []).append(prev.elapsed_time(ev))
-    if sid != main_sid:
-      overlapped.add(name)   # elapsed time on the side stream includes waiting for SMs: not a kernel duration
-  kernels = {n: sum(v) / len(v) for n, v in per.items()}
   if args.timeline and rank == 0:
     # every mark of the last timed step: milliseconds since the step began, stream, name (a mark follows its kernel)
-    start = max(i for i, mk in enumerate(marks) if mk[0] == "bench_step")
     sids = {}
     with open(args.timeline, "w") as fh:
-      for name, ev, sid in marks[start:]:
-        fh.write(f"{marks[start][1].elapsed_time(ev):9.3f}  s{sids.setdefault(sid, len(sids))}  {name}\n")
+      for name, ev, sid in step_marks:
+        fh.write(f"{step_marks[0][1].elapsed_time(ev):9.3f}  s{sids.setdefault(sid, len(sids))}  {name}\n")
 
   # ---- end-to-end through the public API with host buffers (pinned), copies inside the timed region
   e2e = None
@@ -362,7 +438,7 @@ def main():
     return
 
   peaks, peak_kind = load_peaks()
-  work = kernel_work(c)
+  work = kernel_work(c, world)
   table = {}
   for n, ms in kernels.items():
     if n not in work:
@@ -372,15 +448,15 @@ def main():
       ach = amount / (ms * 1e-3) / 1e12
       table[n] = dict(ms=round(ms, 4), bound=bound, achieved=round(ach, 1), unit="TFLOP/s",
                       frac=round(ach / peaks["bf16_tflops_sustained"], 4))
-    else:
+    elif amount > 0:
       ach = amount / (ms * 1e-3) / 1e9
       table[n] = dict(ms=round(ms, 4), bound=bound, achieved=round(ach, 1), unit="GB/s",
-                      frac=round(ach / peaks["hbm_gbs"], 4))
+                      frac=round(ach / (NVLINK_GBS if bound == "nvlink" else peaks["hbm_gbs"]), 4))
   for n in overlapped:
     if n in table:
       table[n]["overlapped"] = True
   roofline = None
-  solo = [n for n in table if n not in overlapped]
+  solo = [n for n in table if n not in overlapped and table[n]["bound"] != "nvlink"]
   dominant = max(solo, key=lambda n: kernels[n]) if solo else None
   dk = table.get(dominant)
   if dk is not None:
@@ -393,7 +469,7 @@ def main():
   gemm_ms = sum(ms for n, ms in kernels.items() if work.get(n, ("", 0))[0] == "tensor" and n not in overlapped)
   gemm_flops = sum(work[n][1] for n in kernels if work.get(n, ("", 0))[0] == "tensor" and n not in overlapped)
   mem_names = ("dispatch_gather", "combine_gather_reduce", "combine_bwd_gather_dot", "combine_bwd_scaled_gather",
-               "combine_bwd_gather", "dispatch_bwd_gather_reduce")
+               "combine_bwd_gather", "dispatch_bwd_gather_reduce", "combine_reduce", "combine_bwd_reduce")
   mem_ms = sum(ms for n, ms in kernels.items() if n in mem_names)
   mem_bytes = sum(work[n][1] for n in mem_names if n in kernels)
   summary = {
@@ -418,7 +494,8 @@ def main():
       "metric": METRIC, "value": c["T"] * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
       "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
       "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, c, world),
-      "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "host_enqueue_ms_per_step": round(host_ms, 3),
+      "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "timed_with": timed_with, "kernel_events": kernel_events, "eager_ms_per_step": round(eager_ms_step, 4),
+      "host_enqueue_ms_per_step": round(host_ms, 3),
       "roofline": roofline, "cpu_baseline": cpu_baseline,
       "summary": summary, "kernels": table,
   }

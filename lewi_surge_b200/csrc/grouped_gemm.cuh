@@ -25,29 +25,32 @@ namespace gg {
 constexpr int BM = 128;       // rows per CTA tile (= routing block)
 constexpr int BN = 256;       // accumulator columns per tile (MMA N)
 constexpr int BK = 64;        // contraction elements per stage (128 bytes of bf16)
-constexpr int RING_BYTES = 192 * 1024;         // shared-memory operand ring of one CTA
+constexpr int DATA_BYTES = 224 * 1024;         // operand ring + epilogue staging of one CTA
+constexpr int EPI_WARPS = 8;      // two warps per TMEM lane quarter, each takes half of the columns
+// The dSwiGLU epilogue moves its g|u and dg|du blocks with TMA and needs 8 KB of staging per warp (two 32-row x
+// 128-byte swizzled tiles); the others transpose 32x32 blocks through 4 KB.  The ring gets the rest.
+__host__ __device__ constexpr int staging_per_warp(int epi) { return epi == 2 /* DSWIGLU */ ? 8192 : 4096; }
+__host__ __device__ constexpr int ring_bytes(int epi) { return DATA_BYTES - EPI_WARPS * staging_per_warp(epi); }
 constexpr int A_BYTES = BM * BK * 2;           // 16 KB
 constexpr int CHUNK_BYTES = 64 * BK * 2;       // 8 KB: one [64 k][64 mn] box of an MN-major operand
-// One CTA per tile (cta_group::1): B is 256 x 64 = 32 KB, 4 stages of 48 KB.
+// One CTA per tile (cta_group::1): B is 256 x 64 = 32 KB, 4 stages of 48 KB (3 under the dSwiGLU epilogue).
 // A CTA pair per 256-row tile (cta_group::2): each CTA holds its own 128 rows of A and HALF of B
-// (128 x 64 = 16 KB), 6 stages of 32 KB; the tensor cores of both SMs read both halves.
-template <bool PAIR> struct Cfg {
+// (128 x 64 = 16 KB), 6 stages of 32 KB (5 under dSwiGLU); the tensor cores of both SMs read both halves.
+template <bool PAIR, int EPI = 0> struct Cfg {
   static constexpr int B_BYTES = PAIR ? BN * BK : BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
-  static constexpr int STAGES = RING_BYTES / STAGE_BYTES;
+  static constexpr int STAGES = ring_bytes(EPI) / STAGE_BYTES;
 };
 constexpr int MAX_STAGES = 6;
 constexpr int PAIR_PREFIX_BYTES = 1040;        // uint16 prefix of row-block pairs per expert (E <= 512)
 constexpr int GATHER_ROWS_BYTES = 512;         // source-row numbers of the tile being gathered
-constexpr int EPI_WARPS = 8;      // two warps per TMEM lane quarter, each takes half of the columns
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
-constexpr int STAGING_PER_WARP = 4096;  // epilogue transposition buffer of one warp
-// 231,184 bytes.  An SM has 233,472 and every resident CTA reserves 1,024 of them, so exactly one more CTA that
+constexpr int EPI_BAR_BYTES = 64;        // one mbarrier per epilogue warp (TMA loads of the dSwiGLU epilogue)
+// 231,248 bytes.  An SM has 233,472 and every resident CTA reserves 1,024 of them, so exactly one more CTA that
 // uses no shared memory (a gather or exchange kernel from another stream) fits beside a GEMM CTA.  That is why
 // there is no slack for aligning the ring: the kernel asks for a 1024-byte aligned base and checks it.
-constexpr size_t SMEM_BYTES = (size_t)RING_BYTES + 256 /*barriers*/ + PAIR_PREFIX_BYTES + GATHER_ROWS_BYTES +
-                              (size_t)EPI_WARPS * STAGING_PER_WARP;
+constexpr size_t SMEM_BYTES = (size_t)DATA_BYTES + 256 /*barriers*/ + PAIR_PREFIX_BYTES + GATHER_ROWS_BYTES + EPI_BAR_BYTES;
 
 enum Major { NN = 0, NT = 1, TN = 2 };
 enum Epi { PLAIN = 0, SWIGLU = 1, DSWIGLU = 2, TNOUT = 3 };
@@ -264,9 +267,11 @@ constexpr int max_regs(int epi) { return epi == 2 /* DSWIGLU */ ? 168 : LEWI_GEM
 template <int MAJOR, int EPI, bool PAIR>
 __global__ void __maxnreg__(max_regs(EPI))
 grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_constant__ CUtensorMap tm_b,
-                    const __grid_constant__ CUtensorMap tm_b2, const Args a) {
-  constexpr int STAGES = Cfg<PAIR>::STAGES;
-  constexpr int STAGE_BYTES = Cfg<PAIR>::STAGE_BYTES;
+                    const __grid_constant__ CUtensorMap tm_b2, const __grid_constant__ CUtensorMap tm_c,
+                    const __grid_constant__ CUtensorMap tm_d, const Args a) {
+  constexpr int STAGES = Cfg<PAIR, EPI>::STAGES;
+  constexpr int STAGE_BYTES = Cfg<PAIR, EPI>::STAGE_BYTES;
+  constexpr int RING_BYTES = ring_bytes(EPI);
   constexpr int B_CHUNKS = PAIR ? 2 : 4;   // 64-column boxes of an MN-major B operand held by one CTA
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const uint32_t smem_base = ptx::smem_u32(smem_raw);
@@ -274,7 +279,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     if (threadIdx.x == 0) raise_status(LEWI_STATUS_SMEM_LAYOUT);
     return;
   }
-  const uint32_t bar_base = smem_base + RING_BYTES;
+  const uint32_t bar_base = smem_base + DATA_BYTES;
   // barrier layout (8 bytes each): full[MAX_STAGES], empty[MAX_STAGES], tmem_full[2], tmem_empty[2], drain
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
   auto empty_bar = [&](int s) { return bar_base + 8u * (MAX_STAGES + s); };
@@ -283,10 +288,11 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   const uint32_t drain_bar = bar_base + 8u * (2 * MAX_STAGES + 4);
   auto gfull_bar = [&](int s) { return bar_base + 176u + 8u * s; };   // peer CTA: its own gathered rows of stage s
   uint8_t* generic_base = smem_raw;
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(generic_base + RING_BYTES + 160);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + RING_BYTES + 168);
-  uint16_t* pair_prefix = reinterpret_cast<uint16_t*>(generic_base + RING_BYTES + 256);
-  int* gather_rows = reinterpret_cast<int*>(generic_base + RING_BYTES + 256 + PAIR_PREFIX_BYTES);   // [128] source rows
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(generic_base + DATA_BYTES + 160);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + DATA_BYTES + 168);
+  uint16_t* pair_prefix = reinterpret_cast<uint16_t*>(generic_base + DATA_BYTES + 256);
+  int* gather_rows = reinterpret_cast<int*>(generic_base + DATA_BYTES + 256 + PAIR_PREFIX_BYTES);   // [128] source rows
+  auto epi_bar = [&](int w) { return bar_base + 256u + PAIR_PREFIX_BYTES + GATHER_ROWS_BYTES + 8u * w; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;   // 0 = leader of the pair
@@ -306,12 +312,17 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       ptx::mbar_init(tempty_bar(b), PAIR ? 2 * EPI_WARPS : EPI_WARPS);
     }
     ptx::mbar_init(drain_bar, 1);
+    for (int w = 0; w < EPI_WARPS; ++w) ptx::mbar_init(epi_bar(w), 1);
     *abort_flag = 0;
     ptx::mbar_fence_init();
     ptx::fence_proxy_async();
     ptx::prefetch_tensormap(&tm_a);
     ptx::prefetch_tensormap(&tm_b);
     if constexpr (EPI == SWIGLU || MAJOR == NT) ptx::prefetch_tensormap(&tm_b2);
+    if constexpr (EPI == DSWIGLU) {
+      ptx::prefetch_tensormap(&tm_c);
+      ptx::prefetch_tensormap(&tm_d);
+    }
   }
   int n_units = 0;  // NN/NT: row blocks (or pairs of row blocks) to process
   if constexpr (MAJOR != TN) {
@@ -436,7 +447,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const bool skip_b = (a.dbg & 4) != 0;
         const int nb0 = t.n0 + (PAIR ? (int)cta_rank * (BN / 2) : 0);   // first B column/row held by this CTA
         if (lane == 0) {
-          const uint32_t cta_bytes = (gather_a ? 0 : A_BYTES) + ((skip_b || gather_b) ? 0 : Cfg<PAIR>::B_BYTES);
+          const uint32_t cta_bytes = (gather_a ? 0 : A_BYTES) + ((skip_b || gather_b) ? 0 : Cfg<PAIR, EPI>::B_BYTES);
           // in pair mode the peer gathers the same operands, so both CTAs bring the same TMA byte count
           if (leader) ptx::mbar_expect_tx(full_bar(s), PAIR ? 2 * cta_bytes : cta_bytes);
           const uint32_t fb = full_target(s);
@@ -606,8 +617,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     // ------------------------------------------------------------------ epilogue (warps 2..9)
     const int lane_grp = warp & 3;           // TMEM lanes 32*lane_grp .. +31 are readable by this warp
     const int col_half = (warp - 2) >> 2;    // which half of the tile's columns this warp stores
-    uint8_t* stage = generic_base + RING_BYTES + 256 + PAIR_PREFIX_BYTES + GATHER_ROWS_BYTES + (warp - 2) * STAGING_PER_WARP;
+    uint8_t* stage = generic_base + RING_BYTES + (warp - 2) * staging_per_warp(EPI);
     uint32_t acc_it = 0;
+    [[maybe_unused]] uint32_t epi_phase = 0;
     bool ok = true;
     for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
       const Tile t = decode_tile<MAJOR, EPI, PAIR>(a, tile, n_tiles_n, pair_prefix);
@@ -620,15 +632,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if (a.dbg & 3) rows_valid = 0;
       const int n_end = (a.dbg & 2) ? 0 : t.nlim;
 
-      // DSWIGLU: the first block of g/u is fetched before the accumulator is waited for
-      [[maybe_unused]] uint4 pg[4], pu[4];
-      [[maybe_unused]] const __nv_bfloat16* gu_base = nullptr;
+      // DSWIGLU: this warp's 32 rows x 128 columns of g and u arrive, and dg and du leave, as TMA tiles of 32 rows x
+      // 64 columns (128-byte swizzle) in the warp's 8 KB of staging: [g tile | u tile], results written in place.
+      // Lane 0 issues the copies; the first pair of loads is in flight before the accumulator is waited for.
+      [[maybe_unused]] const uint32_t tile_g = ptx::smem_u32(stage), tile_u = tile_g + 4096;
+      [[maybe_unused]] auto dsw_load = [&](int n) {
+        if (lane == 0) {
+          ptx::bulk_wait_read();   // the stores of the previous half have finished reading the staging tiles
+          ptx::mbar_expect_tx(epi_bar(warp - 2), 8192);
+          ptx::tma_load_3d(tile_g, &tm_c, epi_bar(warp - 2), n, 0, (int)wrow0);
+          ptx::tma_load_3d(tile_u, &tm_c, epi_bar(warp - 2), n, 1, (int)wrow0);
+        }
+      };
       if constexpr (EPI == DSWIGLU) {
-        gu_base = a.gu + wrow0 * (2LL * a.N);
-        const int n = t.n0 + col_half * 128;
-        const int cv = max(0, min(32, a.N - n));
-        warp_fetch32_bf16(lane, gu_base + n, 2LL * a.N, rows_valid, cv, pg);
-        warp_fetch32_bf16(lane, gu_base + a.N + n, 2LL * a.N, rows_valid, cv, pu);
+        if (rows_valid > 0 && t.n0 + col_half * 128 < n_end) dsw_load(t.n0 + col_half * 128);
       }
 
       uint32_t acc = 0;
@@ -703,7 +720,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       } else if constexpr (EPI == DSWIGLU) {
         const int f = a.N;
-        __nv_bfloat16* dgu = reinterpret_cast<__nv_bfloat16*>(a.out) + wrow0 * (2LL * f);
         float dsc = 1.0f, dw_acc = 0.f;
         if (a.scale_src != nullptr) {
           dsc = 0.f;
@@ -712,19 +728,29 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (gi >= 0) dsc = a.scale_src[gi];
           }
         }
-#pragma unroll
-        for (int ci = 0; ci < 4; ++ci) {
-          const int c = col_half * 4 + ci;
-          const int n = t.n0 + c * 32;
-          if (n < n_end) {  // uniform across the warp
-            const int cv = min(32, f - n);
+        uint8_t* my_g = stage + lane * 128;   // this lane's row of the swizzled g tile; the u tile is 4 KB further
+#pragma unroll 1
+        for (int hf = 0; hf < 2 && ok; ++hf) {
+          const int nh = t.n0 + col_half * 128 + hf * 64;
+          if (rows_valid == 0 || nh >= n_end) break;   // uniform across the warp
+          if (hf == 1) dsw_load(nh);
+          const bool got = ptx::mbar_wait(epi_bar(warp - 2), epi_phase, abort_flag);
+          epi_phase ^= 1u;
+          __syncwarp();
+          if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+#pragma unroll 1
+          for (int b = 0; b < 2; ++b) {
+            const int c = col_half * 4 + hf * 2 + b;
             float g[32], u[32];
-            warp_own_row32_bf16(stage, lane, pg, g);
-            warp_own_row32_bf16(stage + 2048, lane, pu, u);
-            if (ci < 3 && n + 32 < f) {  // next block's g/u are in flight while this one is processed
-              const int cvn = min(32, f - n - 32);
-              warp_fetch32_bf16(lane, gu_base + n + 32, 2LL * f, rows_valid, cvn, pg);
-              warp_fetch32_bf16(lane, gu_base + f + n + 32, 2LL * f, rows_valid, cvn, pu);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int off = ((b * 4 + q) ^ (lane & 7)) << 4;
+              const uint4 pg = *reinterpret_cast<const uint4*>(my_g + off);
+              const uint4 pu = *reinterpret_cast<const uint4*>(my_g + 4096 + off);
+              g[q * 8 + 0] = bf16_lo(pg.x); g[q * 8 + 1] = bf16_hi(pg.x); g[q * 8 + 2] = bf16_lo(pg.y); g[q * 8 + 3] = bf16_hi(pg.y);
+              g[q * 8 + 4] = bf16_lo(pg.z); g[q * 8 + 5] = bf16_hi(pg.z); g[q * 8 + 6] = bf16_lo(pg.w); g[q * 8 + 7] = bf16_hi(pg.w);
+              u[q * 8 + 0] = bf16_lo(pu.x); u[q * 8 + 1] = bf16_hi(pu.x); u[q * 8 + 2] = bf16_lo(pu.y); u[q * 8 + 3] = bf16_hi(pu.y);
+              u[q * 8 + 4] = bf16_lo(pu.z); u[q * 8 + 5] = bf16_hi(pu.z); u[q * 8 + 6] = bf16_lo(pu.w); u[q * 8 + 7] = bf16_hi(pu.w);
             }
             uint32_t r[32];
             if (has_acc) {
@@ -741,8 +767,23 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               g[q] = dh * u[q] * sg * (1.0f + g[q] * (1.0f - sg));
               u[q] = du;
             }
-            warp_store32_bf16(stage, lane, g, dgu + n, 2LL * f, rows_valid, cv);
-            warp_store32_bf16(stage + 2048, lane, u, dgu + f + n, 2LL * f, rows_valid, cv);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const int off = ((b * 4 + q) ^ (lane & 7)) << 4;
+              *reinterpret_cast<uint4*>(my_g + off) =
+                  make_uint4(pack_bf16(g[q * 8 + 0], g[q * 8 + 1]), pack_bf16(g[q * 8 + 2], g[q * 8 + 3]),
+                             pack_bf16(g[q * 8 + 4], g[q * 8 + 5]), pack_bf16(g[q * 8 + 6], g[q * 8 + 7]));
+              *reinterpret_cast<uint4*>(my_g + 4096 + off) =
+                  make_uint4(pack_bf16(u[q * 8 + 0], u[q * 8 + 1]), pack_bf16(u[q * 8 + 2], u[q * 8 + 3]),
+                             pack_bf16(u[q * 8 + 4], u[q * 8 + 5]), pack_bf16(u[q * 8 + 6], u[q * 8 + 7]));
+            }
+          }
+          ptx::fence_proxy_async();   // the tiles were written through the generic proxy, the store reads them through the async one
+          __syncwarp();
+          if (lane == 0) {
+            ptx::tma_store_3d(&tm_d, tile_g, nh, 0, (int)wrow0);
+            ptx::tma_store_3d(&tm_d, tile_u, nh, 1, (int)wrow0);
+            ptx::bulk_commit();
           }
         }
         if (a.dw_partial != nullptr && lane < rows_valid) {
@@ -785,6 +826,9 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
         ++acc_it;
       }
+    }
+    if constexpr (EPI == DSWIGLU) {
+      if (lane == 0) ptx::bulk_wait_all();   // this warp's last tile stores are complete before the CTA can exit
     }
   }
 
@@ -847,12 +891,12 @@ inline EncodeTiledFn encode_fn() {
 
 // bf16 tensor [d2][d1][d0] (d0 contiguous); box [b2][b1][b0]; rank 2 when d2 == 0.
 inline bool make_map(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0,
-                     uint32_t b1) {
+                     uint32_t b1, uint32_t b2 = 1) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr || d0 == 0 || d1 == 0) return false;
   cuuint64_t dims[3] = {d0, d1, d2 ? d2 : 1};
   cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
-  cuuint32_t box[3] = {b0, b1, 1};
+  cuuint32_t box[3] = {b0, b1, b2};
   cuuint32_t estr[3] = {1, 1, 1};
   const cuuint32_t rank = d2 ? 3 : 2;
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
@@ -887,7 +931,7 @@ constexpr size_t SMEM_EXCLUSIVE_PAD = 1024;
 
 template <int MAJOR, int EPI, bool PAIR>
 inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, Args a,
-                  long long max_tiles) {
+                  long long max_tiles, const CUtensorMap& tc, const CUtensorMap& td) {
   static bool attr_set[64] = {false};
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess) return LEWI_ERR_CUDA;
@@ -925,13 +969,13 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
     attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
-    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, tb2, a) != cudaSuccess) {
+    if (cudaLaunchKernelEx(&cfg, kern, ta, tb, tb2, tc, td, a) != cudaSuccess) {
       (void)cudaGetLastError();
       return LEWI_ERR_CUDA;
     }
   } else {
     if (grid > max_tiles) grid = max_tiles;
-    kern<<<(int)grid, THREADS, smem, st>>>(ta, tb, tb2, a);
+    kern<<<(int)grid, THREADS, smem, st>>>(ta, tb, tb2, tc, td, a);
   }
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
@@ -939,10 +983,14 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
 
 // Picks the CTA-pair kernel when enabled, else the single-CTA one.
 template <int MAJOR, int EPI>
+// tc / td: tensor maps of the epilogue's own tiled input and output (dSwiGLU: g|u and dg|du); unused otherwise.
 inline int launch_auto(bool pair, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2,
-                       const Args& a, long long max_tiles) {
-  if (pair) return launch<MAJOR, EPI, true>(st, ta, tb, tb2, a, max_tiles);
-  return launch<MAJOR, EPI, false>(st, ta, tb, tb2, a, max_tiles);
+                       const Args& a, long long max_tiles, const CUtensorMap* tc = nullptr,
+                       const CUtensorMap* td = nullptr) {
+  const CUtensorMap& c = tc != nullptr ? *tc : ta;
+  const CUtensorMap& d = td != nullptr ? *td : ta;
+  if (pair) return launch<MAJOR, EPI, true>(st, ta, tb, tb2, a, max_tiles, c, d);
+  return launch<MAJOR, EPI, false>(st, ta, tb, tb2, a, max_tiles, c, d);
 }
 
 }  // namespace gg

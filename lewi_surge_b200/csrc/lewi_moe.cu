@@ -610,8 +610,12 @@ int lewi_grouped_gemm_dh_dswiglu_gather(void* stream, const void* dys, const int
   a.K = d;
   a.kb_total = (d + gg::BK - 1) / gg::BK;
   a.N = f;
+  // the epilogue reads g|u and writes dg|du as tiles of 32 rows x 64 columns of the [rows][2][f] tensors
+  CUtensorMap tgu, tdgu;
+  if (!gg::make_map(&tgu, gu, (uint64_t)f, 2, (uint64_t)rows, 64, 1, 32)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&tdgu, dgu, (uint64_t)f, 2, (uint64_t)rows, 64, 1, 32)) return LEWI_ERR_CUDA;
   const long long tiles = (long long)a.n_blocks_host * ((f + gg::BN - 1) / gg::BN);
-  return gg::launch_auto<gg::NT, gg::DSWIGLU>(pair, as_stream(stream), ta, tb, tb, a, tiles);
+  return gg::launch_auto<gg::NT, gg::DSWIGLU>(pair, as_stream(stream), ta, tb, tb, a, tiles, &tgu, &tdgu);
 }
 
 int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, const void* w_up, void* dxs,
