@@ -462,7 +462,8 @@ def main():
   if dk is not None:
     roofline = {"kernel": dominant, "bound": dk["bound"], "achieved": dk["achieved"],
                 "peak": peaks["bf16_tflops_sustained"] if dk["bound"] == "tensor" else peaks["hbm_gbs"],
-                "unit": dk["unit"], "frac": dk["frac"], "traffic": KNOWN_TRAFFIC.get((args.config, dominant)),
+                "unit": dk["unit"], "frac": dk["frac"], "traffic": KNOWN_TRAFFIC.get((args.config, dominant)) if not args.tokens else None,
+                "algorithmic": work[dominant][1],
                 "peak_source": f"{peak_kind} ({'sustained bf16 GEMM' if dk['bound'] == 'tensor' else 'copy bandwidth'}; "
                                "kernel timed inside the step)",
                 "ms_per_launch": dk["ms"]}
@@ -504,9 +505,17 @@ def main():
     dist.destroy_process_group()
 
 
-# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) taken from ncu captures
-# summarised under profiles/; keyed by (config, kernel).
-KNOWN_TRAFFIC = {}
+# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised in
+# profiles/grouped_gemm_config2_t8k.md: measured at T=4096 and T=8192 tokens of config 2 and extended linearly in T
+# (expert weights are constant, row traffic is proportional) to the T=32768 launch the bench times.  Bytes.
+KNOWN_TRAFFIC = {
+    ("config2", "gemm_gateup_swiglu"): 1305e6,
+    ("config2", "gemm_down"): 741e6,
+    ("config2", "gemm_dh_dswiglu"): 1417e6,
+    ("config2", "gemm_dw_down"): 834e6,
+    ("config2", "gemm_dx"): 1096e6,
+    ("config2", "gemm_dw_gateup"): 1150e6,
+}
 
 
 if __name__ == "__main__":

@@ -138,3 +138,35 @@ def test_full_size_config2_properties(cuda):
     hs = torch.nn.functional.silu(xv @ w.ws_gate.double()) * (xv @ w.ws_up.double())
     acc += hs @ w.ws_down.double()
     assert float((out[tok].double() - acc).abs().max() / (acc.abs().max() + 1e-6)) <= 2e-2
+
+
+def test_captured_step_replays_the_eager_step(cuda):
+  """A step recorded into a CUDA graph gives the eager step's bits, also after its input buffers were rewritten."""
+  from lewi_surge_b200 import layer, _lib
+  t, d, e, f, fs, k = 1000, 256, 16, 128, 192, 6
+  a, b = O.make_inputs(t, d, e, f, fs, 3), O.make_inputs(t, d, e, f, fs, 4)
+  dev = {n: to_dev(a[n], torch.float32 if n == "w_router" else torch.bfloat16, cuda) for n in NAMES}
+  dev["w_router"] *= 5
+  w = layer.MoEWeights(dev["w_router"], dev["w_gate"], dev["w_up"], dev["w_down"], dev["ws_gate"], dev["ws_up"], dev["ws_down"])
+  x, dout = dev["x"], to_dev(a["dout"], torch.bfloat16, cuda)
+
+  def step():
+    out, cache = layer.moe_layer_fwd(x, w, k)
+    g = layer.moe_layer_bwd(dout, w, cache)
+    return out, g["dx"], g["dw_gate"], g["dw_down"], g["dw_router"], cache.tables.order
+
+  eager_a = [v.clone() for v in step()]
+  captured = layer.CapturedStep(step)
+  got = captured()
+  torch.cuda.synchronize()
+  for u, v in zip(got, eager_a):
+    assert torch.equal(u, v)
+  x.copy_(to_dev(b["x"], torch.bfloat16, cuda))          # different tokens, hence different routing and block counts
+  dout.copy_(to_dev(b["dout"], torch.bfloat16, cuda))
+  got = [v.clone() for v in captured()]
+  eager_b = step()
+  torch.cuda.synchronize()
+  assert not torch.equal(eager_a[5], eager_b[5])
+  for u, v in zip(got, eager_b):
+    assert torch.equal(u, v)
+  assert _lib.last_status() == 0
