@@ -235,6 +235,7 @@ def main():
   ap.add_argument("--no-graph", action="store_true", help="queue every timed step eagerly instead of replaying a CUDA graph")
   ap.add_argument("--timeline", default=None, help="write the last timed step's event marks (rank 0) to this file")
   ap.add_argument("--ep-sync", choices=["flags", "nccl"], default="flags", help="how the exchange orders the ranks")
+  ap.add_argument("--ep-threads", default="256,256", help="CTA size of the exchange kernels: forward,backward")
   ap.add_argument("--ep-phases", type=int, default=None, help="ranges of local experts the exchange is pipelined over")
   ap.add_argument("--dbg-flags", type=int, default=0, help="timing experiments only: results become wrong")
   ap.add_argument("--single-cta", action="store_true", help="A/B switch: force the cta_group::1 GEMM kernels")
@@ -275,7 +276,8 @@ def main():
     from lewi_surge_b200 import ep
     if args.ep_impl == "p2p":
       runner = ep.ExpertParallelP2P(w, c["k"], c["E"], c["T"], c["d"], dist.group.WORLD, capacity=args.ep_capacity,
-                                    phases=args.ep_phases, sync=args.ep_sync)
+                                    phases=args.ep_phases, sync=args.ep_sync,
+                                    exchange_threads=tuple(int(v) for v in args.ep_threads.split(",")))
     else:
       runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
     step_fn = lambda: runner.step(x, dout)

@@ -298,20 +298,25 @@ int lewi_ep_plan(void* stream, const int32_t* counts_all, int G, int E, int me, 
  * (me << 28 | slot, i32) to peers_ret[owner][row] (optional).  Only the rows of local experts (e mod E/G) in
  * [el_lo, el_hi) are moved: launching once per range of local experts lets the owners start on the first
  * range while the next one is still in flight.  M = T*k < 2^28.  The kernel is one small CTA per SM that
- * fits beside a resident grouped-GEMM CTA, so it overlaps GEMMs running on another stream. */
+ * fits beside a resident grouped-GEMM CTA, so it overlaps GEMMs running on another stream.  threads = CTA size
+ * (a multiple of 32 up to 256; 0 = 256): fewer warps keep fewer remote stores in flight per SM, which slows the
+ * transfer and disturbs a GEMM on the same SM less. */
 int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const int32_t* flat_expert,
                       const int32_t* offsets, const int32_t* dst_base, const float* slot_w,
                       void* const* peers_rows_host, void* const* peers_w_host, void* const* peers_ret_host, int me,
-                      int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T, int el_lo, int el_hi);
+                      int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T, int el_lo, int el_hi,
+                      int threads);
 
 /* Owner side of the way back: rows [pad_offsets[el_lo], pad_offsets[el_hi]) of `rows` [rmax_pad,d] bf16 are
  * stored to row `slot` of peers_slot_rows[source] ([M,d] bf16 on every rank), slot and source taken from the
  * return addresses ret i32 [rmax_pad] (-1 = padding row, skipped).  `pieces` f32 [rmax_pad,parts] (optional)
  * go to peers_slot_pieces[source][slot, :parts].  Either of rows / pieces may be null.  On the source rank
- * the combine is then a sum over k consecutive rows (lewi_gather_reduce with the identity index). */
+ * the combine is then a sum over k consecutive rows (lewi_gather_reduce with the identity index).  threads as in
+ * lewi_ep_push_rows. */
 int lewi_ep_return_rows(void* stream, const void* rows, const float* pieces, const int32_t* ret,
                         const int32_t* pad_offsets, int el_lo, int el_hi, void* const* peers_slot_rows_host,
-                        void* const* peers_slot_pieces_host, int d, int parts, int G, int64_t M, int64_t rmax_pad);
+                        void* const* peers_slot_pieces_host, int d, int parts, int G, int64_t M, int64_t rmax_pad,
+                        int threads);
 
 /* Zero rows [valid_end[el], pad_offsets[el+1]) of buf [rmax_pad,d] bf16 for every local expert and, with
  * ret (i32 [rmax_pad], optional), mark them as having no return address. */

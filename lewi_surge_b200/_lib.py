@@ -55,8 +55,8 @@ SIGNATURES = {
     "lewi_ep_ipc_release": (c_int, [P]),
     "lewi_ep_plan": (c_int, [P, P, c_int, c_int, c_int, c_int, c_int64, P, P, P, P, P, P]),
     "lewi_ep_push_rows": (c_int, [P, P, P, P, P, P, P, P, P, P, c_int, c_int64, c_int, c_int, c_int, c_int, c_int64, c_int64,
-                                  c_int, c_int]),
-    "lewi_ep_return_rows": (c_int, [P, P, P, P, P, c_int, c_int, P, P, c_int, c_int, c_int, c_int64, c_int64]),
+                                  c_int, c_int, c_int]),
+    "lewi_ep_return_rows": (c_int, [P, P, P, P, P, c_int, c_int, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int]),
     "lewi_ep_zero_pad": (c_int, [P, P, P, P, P, c_int, c_int, c_int64]),
     "lewi_set_sm_sharing": (c_int, [c_int]),
     "lewi_ep_put_i32": (c_int, [P, P, P, c_int64, c_int, c_int]),

@@ -729,11 +729,14 @@ int lewi_ep_plan(void* stream, const int32_t* counts_all, int G, int E, int me, 
 int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const int32_t* flat_expert,
                       const int32_t* offsets, const int32_t* dst_base, const float* slot_w,
                       void* const* peers_rows_host, void* const* peers_w_host, void* const* peers_ret_host, int me,
-                      int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T, int el_lo, int el_hi) {
+                      int64_t M, int k, int d, int E, int G, int64_t rmax_pad, int64_t T, int el_lo, int el_hi,
+                      int threads) {
   if (!x || !order || !flat_expert || !offsets || !dst_base || M < 0 || k <= 0 || d <= 0 || T < 0) return LEWI_ERR_ARG;
   if (G <= 0 || G > kMaxPeers || E <= 0 || E % G != 0 || me < 0 || me >= G || d % 8 != 0) return LEWI_ERR_ARG;
   if (el_lo < 0 || el_hi > E / G || el_lo > el_hi) return LEWI_ERR_ARG;
   if (M >= (1ll << kEpSlotBits)) return LEWI_ERR_LIMIT;
+  if (threads == 0) threads = kEpThreads;
+  if (threads < 32 || threads > kEpThreads || threads % 32 != 0) return LEWI_ERR_ARG;
   PeerPtrs rows, w, ret;
   if (!fill_peers(rows, peers_rows_host, G, true)) return LEWI_ERR_ARG;
   if (!fill_peers(w, peers_w_host, G, slot_w != nullptr)) return LEWI_ERR_ARG;
@@ -741,7 +744,7 @@ int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const i
   if (M == 0 || el_lo == el_hi) return LEWI_OK;
   static bool carve[64] = {false};
   prefer_shared_carveout(reinterpret_cast<const void*>(ep_push_rows_kernel), carve);
-  ep_push_rows_kernel<<<num_sms(), kEpThreads, 0, as_stream(stream)>>>(
+  ep_push_rows_kernel<<<num_sms(), threads, 0, as_stream(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(x), order, flat_expert, offsets, dst_base, slot_w, rows, w, ret, M, k, d, E / G,
       G, rmax_pad, T, el_lo, el_hi, me);
   LEWI_CHECK_LAUNCH();
@@ -750,17 +753,20 @@ int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const i
 
 int lewi_ep_return_rows(void* stream, const void* rows, const float* pieces, const int32_t* ret,
                         const int32_t* pad_offsets, int el_lo, int el_hi, void* const* peers_slot_rows_host,
-                        void* const* peers_slot_pieces_host, int d, int parts, int G, int64_t M, int64_t rmax_pad) {
+                        void* const* peers_slot_pieces_host, int d, int parts, int G, int64_t M, int64_t rmax_pad,
+                        int threads) {
   if (!ret || !pad_offsets || (!rows && !pieces) || d <= 0 || d % 8 != 0 || G <= 0 || G > kMaxPeers || M < 0)
     return LEWI_ERR_ARG;
   if (el_lo < 0 || el_lo > el_hi || (pieces && parts <= 0)) return LEWI_ERR_ARG;
+  if (threads == 0) threads = kEpThreads;
+  if (threads < 32 || threads > kEpThreads || threads % 32 != 0) return LEWI_ERR_ARG;
   PeerPtrs pr, pp;
   if (!fill_peers(pr, peers_slot_rows_host, G, rows != nullptr)) return LEWI_ERR_ARG;
   if (!fill_peers(pp, peers_slot_pieces_host, G, pieces != nullptr)) return LEWI_ERR_ARG;
   if (el_lo == el_hi) return LEWI_OK;
   static bool carve[64] = {false};
   prefer_shared_carveout(reinterpret_cast<const void*>(ep_return_rows_kernel), carve);
-  ep_return_rows_kernel<<<num_sms(), kEpThreads, 0, as_stream(stream)>>>(
+  ep_return_rows_kernel<<<num_sms(), threads, 0, as_stream(stream)>>>(
       reinterpret_cast<const __nv_bfloat16*>(rows), pieces, ret, pad_offsets, el_lo, el_hi, pr, pp, d, parts, G, M,
       rmax_pad);
   LEWI_CHECK_LAUNCH();

@@ -293,7 +293,8 @@ class ExpertParallelP2P:
 
   BARRIER_TIMEOUT_MS = 4000
 
-  def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None, phases=None, sync="flags"):
+  def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None, phases=None, sync="flags",
+               exchange_threads=(256, 256)):
     from . import _lib, layer, ops
     self.lib, self.layer, self.ops, self._lib = _lib.load(), layer, ops, _lib
     self.w, self.k, self.e, self.d, self.t = w, k, num_experts, d, tokens
@@ -306,6 +307,7 @@ class ExpertParallelP2P:
     if sync not in ("flags", "nccl"):
       raise ValueError("sync must be 'flags' or 'nccl'")
     self.sync = sync
+    self.fwd_threads, self.bwd_threads = (int(v) for v in exchange_threads)   # CTA size of the exchange kernels
     self.el = num_experts // self.world
     self.f = w.w_gate.shape[2]
     self.dev = w.w_gate.device
@@ -457,7 +459,8 @@ class ExpertParallelP2P:
     def push(p):
       check(lib.lewi_ep_push_rows(st(), ptr(x), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
                                   ptr(tb.topk_w), self.s_x.c_ptrs, self.s_w.c_ptrs, self.s_ret.c_ptrs, self.rank, self.m,
-                                  k, d, self.e, G, self.rmax, t, self.bounds[p], self.bounds[p + 1]), "lewi_ep_push_rows")
+                                  k, d, self.e, G, self.rmax, t, self.bounds[p], self.bounds[p + 1], self.fwd_threads),
+            "lewi_ep_push_rows")
       L._mark("ep_push_x")
 
     def gemms(p, mark_done):
@@ -473,8 +476,8 @@ class ExpertParallelP2P:
 
     def give_back(p):
       check(lib.lewi_ep_return_rows(st(), ptr(self.ys), None, ptr(self.ret), ptr(self.pad_offsets), self.bounds[p],
-                                    self.bounds[p + 1], self.s_yslot.c_ptrs, None, d, self.parts, G, self.m, self.rmax),
-            "lewi_ep_return_rows")
+                                    self.bounds[p + 1], self.s_yslot.c_ptrs, None, d, self.parts, G, self.m, self.rmax,
+                                    self.fwd_threads), "lewi_ep_return_rows")
       L._mark("ep_return_y")
 
     def shared_expert():   # needs nothing from other ranks: it fills the time the first rows are in flight
@@ -536,7 +539,7 @@ class ExpertParallelP2P:
     def push(p):
       check(lib.lewi_ep_push_rows(st(), ptr(dout), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
                                   None, self.s_dy.c_ptrs, None, None, self.rank, self.m, k, d, self.e, G, self.rmax, t,
-                                  self.bounds[p], self.bounds[p + 1]), "lewi_ep_push_rows")
+                                  self.bounds[p], self.bounds[p + 1], self.bwd_threads), "lewi_ep_push_rows")
       L._mark("ep_push_dout")
 
     def gemms(p, mark_done):
@@ -559,7 +562,7 @@ class ExpertParallelP2P:
     def give_back(p):
       check(lib.lewi_ep_return_rows(st(), ptr(self.dxs), ptr(self.dwp), ptr(self.ret), ptr(self.pad_offsets),
                                     self.bounds[p], self.bounds[p + 1], self.s_dxslot.c_ptrs, self.s_dwslot.c_ptrs, d,
-                                    self.parts, G, self.m, self.rmax), "lewi_ep_return_rows")
+                                    self.parts, G, self.m, self.rmax, self.bwd_threads), "lewi_ep_return_rows")
       L._mark("ep_return_dx")
 
     self._pipeline(push, gemms, give_back, first=shared_expert)

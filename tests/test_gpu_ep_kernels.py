@@ -74,7 +74,7 @@ def test_plan_push_return_emulated_ranks(cuda, g, e, k, t, d, phases):
     for lo, hi in zip(bounds[:-1], bounds[1:]):
       check(lib.lewi_ep_push_rows(st(), ptr(xs[r]), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets),
                                   ptr(plans[r]["dst_base"]), ptr(tb.topk_w), p_x, p_w, p_ret, r, m, k, d, e, g, rmax, t,
-                                  lo, hi), "push")
+                                  lo, hi, 0 if r % 2 == 0 else 128), "push")
   torch.cuda.synchronize()
   assert _lib.last_status() == 0
 
@@ -102,7 +102,7 @@ def test_plan_push_return_emulated_ranks(cuda, g, e, k, t, d, phases):
     pieces = torch.stack([recv_w[o], recv_w[o] * 3], 1).contiguous()
     for lo, hi in zip(bounds[:-1], bounds[1:]):
       check(lib.lewi_ep_return_rows(st(), ptr(ys), ptr(pieces), ptr(ret[o]), ptr(plans[o]["pad_offsets"]), lo, hi, p_y,
-                                    p_pc, d, 2, g, m, rmax), "return")
+                                    p_pc, d, 2, g, m, rmax, 0 if o % 2 == 0 else 64), "return")
   torch.cuda.synchronize()
   assert _lib.last_status() == 0
   for s in range(g):
