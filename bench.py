@@ -188,8 +188,8 @@ def run_reference(args, c, rank, world):
   sample = min(c["T"], 4096)
   step = cpu_oracle_step(c, sample)
   t1 = step()                       # warm-up, also sizes the sample: the whole run should stay within ~2.5 minutes
-  budget = 150.0
-  while sample > 256 and t1 * args.steps > budget:
+  limit_s = 150.0
+  while sample > 256 and t1 * args.steps > limit_s:
     sample //= 2
     step = cpu_oracle_step(c, sample)
     t1 = step()
@@ -235,6 +235,7 @@ def main():
   ap.add_argument("--no-graph", action="store_true", help="queue every timed step eagerly instead of replaying a CUDA graph")
   ap.add_argument("--timeline", default=None, help="write the last timed step's event marks (rank 0) to this file")
   ap.add_argument("--ep-sync", choices=["flags", "nccl"], default="flags", help="how the exchange orders the ranks")
+  ap.add_argument("--ep-dw-down-first", action="store_true", help="A/B switch: order of the two weight-gradient GEMMs")
   ap.add_argument("--ep-threads", default="256,256", help="CTA size of the exchange kernels: forward,backward")
   ap.add_argument("--ep-phases", type=int, default=None, help="ranges of local experts the exchange is pipelined over")
   ap.add_argument("--dbg-flags", type=int, default=0, help="timing experiments only: results become wrong")
@@ -277,7 +278,8 @@ def main():
     if args.ep_impl == "p2p":
       runner = ep.ExpertParallelP2P(w, c["k"], c["E"], c["T"], c["d"], dist.group.WORLD, capacity=args.ep_capacity,
                                     phases=args.ep_phases, sync=args.ep_sync,
-                                    exchange_threads=tuple(int(v) for v in args.ep_threads.split(",")))
+                                    exchange_threads=tuple(int(v) for v in args.ep_threads.split(",")),
+                                    dw_down_last=not args.ep_dw_down_first)
     else:
       runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
     step_fn = lambda: runner.step(x, dout)

@@ -294,7 +294,7 @@ class ExpertParallelP2P:
   BARRIER_TIMEOUT_MS = 4000
 
   def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None, phases=None, sync="flags",
-               exchange_threads=(256, 256)):
+               exchange_threads=(256, 256), dw_down_last=True):
     from . import _lib, layer, ops
     self.lib, self.layer, self.ops, self._lib = _lib.load(), layer, ops, _lib
     self.w, self.k, self.e, self.d, self.t = w, k, num_experts, d, tokens
@@ -308,6 +308,7 @@ class ExpertParallelP2P:
       raise ValueError("sync must be 'flags' or 'nccl'")
     self.sync = sync
     self.fwd_threads, self.bwd_threads = (int(v) for v in exchange_threads)   # CTA size of the exchange kernels
+    self.dw_down_last = bool(dw_down_last)
     self.el = num_experts // self.world
     self.f = w.w_gate.shape[2]
     self.dev = w.w_gate.device
@@ -553,11 +554,20 @@ class ExpertParallelP2P:
                                      ptr(nb), ptr(po), self.rmax, d, f, hi - lo), "lewi_grouped_gemm_dx")
       L._mark("gemm_dx")
       mark_done()   # the weight gradients below are of no interest to the other ranks
-      ops.grouped_gemm_tn(c["h"], self.recv_dy, po, hi - lo, out=grads["dw_down"][lo:hi])
-      L._mark("gemm_dw_down")
-      ops.grouped_gemm_tn(self.recv_x, dgu, po, hi - lo, out=grads["dw_gate"][lo:hi], out2=grads["dw_up"][lo:hi],
-                          split=True)
-      L._mark("gemm_dw_gateup")
+
+      def dw_down():
+        ops.grouped_gemm_tn(c["h"], self.recv_dy, po, hi - lo, out=grads["dw_down"][lo:hi])
+        L._mark("gemm_dw_down")
+
+      def dw_gateup():
+        ops.grouped_gemm_tn(self.recv_x, dgu, po, hi - lo, out=grads["dw_gate"][lo:hi], out2=grads["dw_up"][lo:hi],
+                            split=True)
+        L._mark("gemm_dw_gateup")
+
+      # The return of this range's dx starts now and shares the SMs with whatever comes next.  dW_down (few tiles,
+      # long contraction) was measured 3x slower beside it, dW_gate|up 1.1x: the robust one goes first.
+      for gemm in ((dw_gateup, dw_down) if self.dw_down_last else (dw_down, dw_gateup)):
+        gemm()
 
     def give_back(p):
       check(lib.lewi_ep_return_rows(st(), ptr(self.dxs), ptr(self.dwp), ptr(self.ret), ptr(self.pad_offsets),
