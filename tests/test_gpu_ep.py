@@ -1,5 +1,7 @@
-"""Expert-parallel layer on real GPUs (needs >= 2): NCCL all-to-all + the CUDA kernels, against the
-single-GPU layer on the concatenated batch (which the other tests pin to the oracle)."""
+"""Expert-parallel layer on real GPUs, one process per GPU: the NCCL all-to-all version and the peer-memory version
+(one exchange per pass, pipelined over ranges of experts, with either way of ordering the ranks), against the
+single-GPU layer on the concatenated batch (which the other tests pin to the oracle).  World size 1 runs on one
+GPU; the rest needs at least 2."""
 import os
 import socket
 import sys
@@ -65,7 +67,7 @@ def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
 
 @pytest.mark.parametrize("impl", ["p2p", "p2p-phased"])
 def test_peer_memory_layer_on_one_gpu(cuda, tmp_path, impl):
-  """World size 1: the push / pull kernels and the plan run against this GPU's own buffers."""
+  """World size 1: the push / return kernels, the plan and the barrier run against this GPU's own buffers."""
   _check(cuda, tmp_path, (512, 256, 16, 128, 128, 4), 1, impl)
 
 

@@ -126,3 +126,36 @@ def test_barrier_alone_on_one_gpu(cuda):
   assert int(flags.item()) == 3 and int(epoch.item()) == 3 and _lib.last_status() == 0
   assert lib.lewi_ep_barrier(st(), peers, ptr(flags), ptr(epoch), 0, 1, 0) != 0        # timeout must be positive
   assert lib.lewi_ep_barrier(st(), peers, ptr(flags), None, 0, 1, 1000) != 0           # epoch counter is required
+
+
+def test_receive_buffer_too_small_is_reported_not_overrun(cuda):
+  """A plan that needs more rows than the buffers hold raises LEWI_STATUS_EP_OVERFLOW; rows past the end are dropped."""
+  from lewi_surge_b200 import _lib, layer
+  lib, ptr, st, check = _lib.load(), _lib.ptr, _lib.stream, _lib.check
+  g, e, k, t, d = 2, 4, 2, 400, 256
+  el, m = e // g, t * k
+  gen = torch.Generator(device="cpu").manual_seed(3)
+  x = torch.randn(t, d, generator=gen).to(cuda, torch.bfloat16)
+  tb = layer.router_topk((torch.randn(t, e, generator=gen) * 3).to(cuda), k)
+  counts_all = torch.cat([tb.counts, tb.counts]).contiguous()          # both emulated ranks route the same way
+  need = int(owner_layout(counts_all.cpu().numpy().reshape(g, e), g, e)[0][:, -1].max())
+  rmax = need // 2 // BLOCK * BLOCK                                       # half of what rank 0 will receive
+  i32 = dict(dtype=torch.int32, device=cuda)
+  plan = dict(dst_base=torch.zeros(e, **i32), pad_offsets=torch.zeros(el + 1, **i32), valid_end=torch.zeros(el, **i32),
+              n_blocks=torch.zeros(1, **i32), recv_rows=torch.zeros(1, **i32))
+  _lib.last_status()
+  check(lib.lewi_ep_plan(st(), ptr(counts_all), g, e, 0, BLOCK, rmax, ptr(plan["dst_base"]), ptr(plan["pad_offsets"]),
+                         ptr(plan["valid_end"]), ptr(plan["n_blocks"]), None, ptr(plan["recv_rows"])), "plan")
+  assert _lib.last_status() & 4                                            # LEWI_STATUS_EP_OVERFLOW
+  assert int(plan["n_blocks"].item()) == rmax // BLOCK                     # clamped to the buffer
+  guard = 64
+  bufs = [torch.full((rmax + guard, d), 7.0, dtype=torch.bfloat16, device=cuda) for _ in range(g)]
+  rets = [torch.full((rmax + guard,), -5, **i32) for _ in range(g)]
+  table = lambda ts: (ctypes.c_void_p * g)(*[v.data_ptr() for v in ts])
+  check(lib.lewi_ep_push_rows(st(), ptr(x), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(plan["dst_base"]), None,
+                              table(bufs), None, table(rets), 0, m, k, d, e, g, rmax, t, 0, el, 0), "push")
+  torch.cuda.synchronize()
+  for b, r in zip(bufs, rets):
+    assert torch.all(b[rmax:] == 7.0) and torch.all(r[rmax:] == -5)         # nothing was written past the end
+  assert torch.any(bufs[0][:rmax] != 7.0)
+  _lib.last_status()
