@@ -434,7 +434,8 @@ def main():
     dt = (time.perf_counter() - t0) / n_e2e
     e2e = {"value": c["T"] / dt, "unit": "tokens/s", "h2d_bytes_per_step": xh.numel() * 2 + gh.numel() * 2,
            "d2h_bytes_per_step": oh.numel() * 2 + dxh.numel() * 2, "ms_per_step": dt * 1e3,
-           "note": "x and upstream gradient copied in from pinned host memory, output and dx copied back, every step"}
+           "note": "x and upstream gradient copied in from pinned host memory, output and dx copied back, every step; "
+                   "two of the four copies overlap the compute"}
 
   if rank != 0:
     if world > 1:

@@ -388,22 +388,68 @@ def moe_layer_bwd(dout, w: MoEWeights, c: LayerCache):
 def moe_layer_step_host(x_host, dout_host, w: MoEWeights, k, out_host, dx_host, bufs=None):
   """One forward+backward with HOST activations: copies x and the upstream gradient in from (pinned)
   host memory, runs the layer, copies the output and dx back.  Weight gradients stay on the device
-  (they feed the optimizer there).  Returns the gradient dict; the copies are asynchronous on the
-  current stream, so synchronise before reading the host buffers."""
+  (they feed the optimizer there).  Returns the gradient dict; everything is asynchronous with respect to the
+  host and ordered on the current stream, so synchronise it before reading the host buffers.
+
+  With a `bufs` dict that is passed again on later calls the device buffers are kept, the forward and the
+  backward pass are each recorded into a CUDA graph on the second call (the first one runs eagerly and sets
+  kernel attributes), the upstream gradient is copied in on a second stream while the forward pass runs and the
+  output is copied out while the backward pass runs: of the four PCIe transfers only x (before) and dx (after)
+  are exposed."""
   dev = w.w_gate.device
   if bufs is None:
     bufs = {}
   xd = bufs.get("x")
-  if xd is None or xd.shape != x_host.shape:
+  if xd is None or xd.shape != x_host.shape or bufs.get("k") != k:
+    bufs.clear()
     xd = bufs["x"] = torch.empty(x_host.shape, dtype=x_host.dtype, device=dev)
     bufs["dout"] = torch.empty(dout_host.shape, dtype=dout_host.dtype, device=dev)
-  gd = bufs["dout"]
+    bufs["k"] = k
+    bufs["copy_stream"] = torch.cuda.Stream(dev)
+    bufs["calls"] = 0
+  gd, cp = bufs["dout"], bufs["copy_stream"]
+  main = torch.cuda.current_stream(dev)
+  bufs["calls"] += 1
+
+  if bufs["calls"] == 2 and "graphs" not in bufs:
+    hook = _HOOK
+    set_profile_hook(None)
+    try:
+      fwd, bwd = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
+      with torch.cuda.graph(fwd):
+        out, cache = moe_layer_fwd(xd, w, k)
+      with torch.cuda.graph(bwd, pool=fwd.pool()):
+        grads = moe_layer_bwd(gd, w, cache)
+      bufs["graphs"] = (fwd, bwd, out, grads)
+    except Exception:   # a step that cannot be captured keeps running eagerly
+      bufs["graphs"] = None
+    finally:
+      set_profile_hook(hook)
+
+  graphs = bufs.get("graphs")
   xd.copy_(x_host, non_blocking=True)
-  gd.copy_(dout_host, non_blocking=True)
-  out, cache = moe_layer_fwd(xd, w, k)
-  grads = moe_layer_bwd(gd, w, cache)
-  out_host.copy_(out, non_blocking=True)
+  start = main.record_event()
+  with torch.cuda.stream(cp):
+    cp.wait_event(start)   # the previous step no longer reads the upstream-gradient buffer
+    gd.copy_(dout_host, non_blocking=True)
+    dout_in = cp.record_event()
+  if graphs:
+    fwd, bwd, out, grads = graphs
+    fwd.replay()
+  else:
+    out, cache = moe_layer_fwd(xd, w, k)
+  fwd_done = main.record_event()
+  with torch.cuda.stream(cp):
+    cp.wait_event(fwd_done)
+    out_host.copy_(out, non_blocking=True)
+    out_back = cp.record_event()
+  main.wait_event(dout_in)
+  if graphs:
+    bwd.replay()
+  else:
+    grads = moe_layer_bwd(gd, w, cache)
   dx_host.copy_(grads["dx"], non_blocking=True)
+  main.wait_event(out_back)
   return grads
 
 
