@@ -20,7 +20,8 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
   sys.path.insert(0, ROOT)
 
-# Workloads named by BASELINE.json's configs (per-GPU shapes).
+# The five benchmark workloads (per-GPU shapes): stage-1 layer, stage-2 layer, skewed routing, the scaled-up
+# expert-parallel layer and the long-context share.
 CONFIGS = {
     "config1": dict(T=4096, d=1024, E=64, f=512, k=6, fs=512, bias=False),
     "config2": dict(T=32768, d=1024, E=128, f=512, k=6, fs=512, bias=False),
@@ -185,6 +186,11 @@ def run_reference(args, c, rank, world):
     return
   import numpy as np  # noqa: F401
   cores = os.cpu_count() or 1
+  try:   # torchrun exports OMP_NUM_THREADS=1 to its workers: give the BLAS behind NumPy every core back
+    from threadpoolctl import threadpool_limits
+    threadpool_limits(limits=cores)
+  except Exception:  # noqa: BLE001
+    pass
   sample = min(c["T"], 4096)
   step = cpu_oracle_step(c, sample)
   t1 = step()                       # warm-up, also sizes the sample: the whole run should stay within ~2.5 minutes
@@ -238,7 +244,8 @@ def main():
   ap.add_argument("--ep-dw-down-first", action="store_true", help="A/B switch: order of the two weight-gradient GEMMs")
   ap.add_argument("--ep-threads", default="256,256", help="CTA size of the exchange kernels: forward,backward")
   ap.add_argument("--ep-phases", type=int, default=None, help="ranges of local experts the exchange is pipelined over")
-  ap.add_argument("--dbg-flags", type=int, default=0, help="timing experiments only: results become wrong")
+  ap.add_argument("--preload-s", type=float, default=2.0,
+                  help="seconds of untimed replays right before the timed window (clocks and power settle)")
   ap.add_argument("--single-cta", action="store_true", help="A/B switch: force the cta_group::1 GEMM kernels")
   args = ap.parse_args()
   rank = int(os.environ.get("RANK", "0"))
@@ -267,15 +274,15 @@ def main():
     dist.init_process_group("nccl", device_id=device)
   lib = _lib.load()
   if args.single_cta:
-    lib.lewi_debug_set_cta_pair(0)
-  if args.dbg_flags:
-    lib.lewi_debug_set_flags(args.dbg_flags)
+    lib.lewi_set_cta_pair(0)
 
   x, dout, wd, bias = make_device_inputs(c, device, seed=rank, torch=torch, world=world)
   w = layer.MoEWeights(router_bias=bias, **wd)
+  ep_parity = None
   if world > 1:
     from lewi_surge_b200 import ep
     if args.ep_impl == "p2p":
+      ep_parity = ep_parity_check(args, c, rank, world, device, torch, dist)
       runner = ep.ExpertParallelP2P(w, c["k"], c["E"], c["T"], c["d"], dist.group.WORLD, capacity=args.ep_capacity,
                                     phases=args.ep_phases, sync=args.ep_sync,
                                     exchange_threads=tuple(int(v) for v in args.ep_threads.split(",")),
@@ -286,7 +293,7 @@ def main():
   else:
     def step_fn():
       out, cache = layer.moe_layer_fwd(x, w, c["k"])
-      return layer.moe_layer_bwd(dout, w, cache)
+      return out, layer.moe_layer_bwd(dout, w, cache)
 
   def barrier():
     if world > 1:
@@ -311,31 +318,53 @@ def main():
     except Exception as exc:   # keep going eagerly; the line says so
       timed_fn, timed_with = step_fn, f"eager launches (capture failed: {type(exc).__name__})"
     barrier()
+  # Untimed load right before the timed window: the GPU reaches the clocks and the power state it keeps under this
+  # work, which is the regime the sustained GEMM peak was measured in.  Every rank runs the same number of steps.
+  preload_steps = 0
+  if args.preload_s > 0:
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(3):
+      timed_fn()
+    ev1.record()
+    barrier()
+    est = torch.tensor([ev0.elapsed_time(ev1) / 3], dtype=torch.float64, device=device)
+    if world > 1:
+      dist.all_reduce(est, op=dist.ReduceOp.MAX)
+    preload_steps = int(min(max(args.preload_s * 1e3 / max(float(est.item()), 1e-3), 1), 5000))
+    for _ in range(preload_steps):
+      timed_fn()
   sampler = ClockSampler(local_rank)
+  barrier()
   if rank == 0:
     sampler.start()
   ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-  barrier()
   ev0.record()
   for _ in range(args.steps):
     timed_fn()
   ev1.record()
   barrier()
+  clocks = sampler.stop() if rank == 0 else None
   ms_total = ev0.elapsed_time(ev1)
   tms = torch.tensor([ms_total], dtype=torch.float64, device=device)
   if world > 1:
     dist.all_reduce(tms, op=dist.ReduceOp.MAX)
   ms_step = float(tms.item()) / args.steps
 
-  # ---- per-kernel durations: a CUDA event after every kernel.  The events are recorded into a second graph
-  # (external event nodes) and read back after every replay, so that the gaps a slow host leaves between eager
-  # launches do not count as kernel time; if that cannot be captured the step is queued eagerly instead.
+  # ---- per-kernel durations: a CUDA event after every kernel, on the stream the kernel went to.  The events are
+  # recorded into a second graph (external event nodes) and read back after every replay, so that the gaps a slow
+  # host leaves between eager launches do not count as kernel time; if that cannot be captured the step is queued
+  # eagerly instead.
   marks = []
   external = [True]
-  def hook(name):
+  ext_streams = {}
+  def hook(name, stream_ptr):
+    st = ext_streams.get(stream_ptr)
+    if st is None:
+      st = ext_streams[stream_ptr] = torch.cuda.ExternalStream(stream_ptr, device=device)
     ev = torch.cuda.Event(enable_timing=True, external=True) if external[0] else torch.cuda.Event(enable_timing=True)
-    ev.record()
-    marks.append((name, ev, torch.cuda.current_stream().cuda_stream))
+    ev.record(st)
+    marks.append((name, ev, stream_ptr))
   n_prof = max(3, min(args.steps, 10))
   per, overlapped = {}, set()
   def account(step_marks):
@@ -353,7 +382,7 @@ def main():
     for name, ms in total.items():
       per.setdefault(name, []).append(ms)
   def profiled_step():
-    hook("bench_step")
+    hook("bench_step", torch.cuda.current_stream().cuda_stream)
     return step_fn()
   kernel_events = "events in a replayed cuda graph"
   layer.set_profile_hook(hook)
@@ -361,11 +390,14 @@ def main():
   # of on its side stream (the timed region above keeps the overlap).  The exchange of the expert-parallel layer
   # cannot be taken out, so at N > 1 GEMM durations include what the exchange kernels take from them.
   overlap_shared, layer.OVERLAP_SHARED = layer.OVERLAP_SHARED, False
+  prof_sampler = ClockSampler(local_rank)
   try:
     if not capturable or args.no_graph:
       raise RuntimeError("eager")
     prof = layer.CapturedStep(profiled_step, keep_profile_hook=True)
     step_marks = list(marks)
+    if rank == 0:
+      prof_sampler.start()
     for _ in range(n_prof):
       barrier()
       prof()
@@ -384,6 +416,7 @@ def main():
     for a, b in zip(starts[:-1], starts[1:]):
       account(marks[a:b])
     step_marks = marks[starts[-2]:]
+  prof_clocks = prof_sampler.stop() if rank == 0 else None
   layer.set_profile_hook(None)
   layer.OVERLAP_SHARED = overlap_shared
   kernels = {n: sum(v) / len(v) for n, v in per.items()}
@@ -401,7 +434,6 @@ def main():
   barrier()
   launches_per_step = (lib.lewi_launch_count() - launches0) // n_eager
   launches = launches_per_step * args.steps
-  clocks = sampler.stop() if rank == 0 else None
   tms = torch.tensor([ev0.elapsed_time(ev1)], dtype=torch.float64, device=device)
   if world > 1:
     dist.all_reduce(tms, op=dist.ReduceOp.MAX)
@@ -417,25 +449,44 @@ def main():
       for name, ev, sid in step_marks:
         fh.write(f"{step_marks[0][1].elapsed_time(ev):9.3f}  s{sids.setdefault(sid, len(sids))}  {name}\n")
 
-  # ---- end-to-end through the public API with host buffers (pinned), copies inside the timed region
+  # ---- end-to-end through the public API with host buffers (pinned): every step's x and upstream gradient come in
+  # from host memory and its output and dx go back, all inside the timed region (wall clock, final drain included)
   e2e = None
-  if world == 1 and not args.no_e2e:
+  if not args.no_e2e:
     xh, gh = x.cpu().pin_memory(), dout.cpu().pin_memory()
     oh, dxh = torch.empty_like(xh).pin_memory(), torch.empty_like(xh).pin_memory()
-    bufs = {}
+    if world == 1:
+      pipe = layer.host_pipeline(w, c["k"], c["T"], graph=not args.no_graph)
+    else:
+      def make_step(xd, gd):
+        def one():
+          out, grads = runner.step(xd, gd)
+          return out, grads["dx"]
+        one()
+        return layer.CapturedStep(one) if (capturable and not args.no_graph) else one
+      pipe = layer.HostPipeline(make_step, c["T"], c["d"], device)
     for _ in range(3):
-      layer.moe_layer_step_host(xh, gh, w, c["k"], oh, dxh, bufs)
-    torch.cuda.synchronize()
-    n_e2e = max(3, min(args.steps, 10))
+      pipe.step(xh, gh, oh, dxh)
+    pipe.drain()
+    barrier()
+    n_e2e = max(3, min(args.steps, 20))
     t0 = time.perf_counter()
     for _ in range(n_e2e):
-      layer.moe_layer_step_host(xh, gh, w, c["k"], oh, dxh, bufs)
-      torch.cuda.synchronize()
-    dt = (time.perf_counter() - t0) / n_e2e
-    e2e = {"value": c["T"] / dt, "unit": "tokens/s", "h2d_bytes_per_step": xh.numel() * 2 + gh.numel() * 2,
-           "d2h_bytes_per_step": oh.numel() * 2 + dxh.numel() * 2, "ms_per_step": dt * 1e3,
-           "note": "x and upstream gradient copied in from pinned host memory, output and dx copied back, every step; "
-                   "two of the four copies overlap the compute"}
+      pipe.step(xh, gh, oh, dxh)
+    pipe.drain()
+    dt_local = time.perf_counter() - t0
+    tdt = torch.tensor([dt_local], dtype=torch.float64, device=device)
+    if world > 1:
+      dist.all_reduce(tdt, op=dist.ReduceOp.MAX)
+    dt = float(tdt.item()) / n_e2e
+    e2e = {"value": c["T"] * world / dt, "unit": "tokens/s", "h2d_bytes_per_step": (xh.numel() + gh.numel()) * 2 * world,
+           "d2h_bytes_per_step": (oh.numel() + dxh.numel()) * 2 * world, "ms_per_step": dt * 1e3, "steps": n_e2e,
+           "note": "x and upstream gradient copied in from pinned host memory, output and dx copied back, every step, "
+                   "inside the timed region (wall clock over the steps and the final drain; max over ranks); the copies "
+                   "of a step overlap the compute of its neighbours (double-buffered staging, PCIe in both directions)"}
+    status = _lib.last_status()
+    if status != 0:
+      raise SystemExit(f"device status {status} after the end-to-end steps")
 
   if rank != 0:
     if world > 1:
@@ -444,6 +495,13 @@ def main():
 
   peaks, peak_kind = load_peaks()
   work = kernel_work(c, world)
+  # which bf16 peak a kernel's duration is compared with: the clocks decide.  After the untimed load the GPU is in the
+  # regime of the sustained figure when its SM clock sits well below the maximum; a run that stayed at full clock is
+  # a burst and belongs against the burst figure.
+  pc = prof_clocks or {}
+  mhz, mhz_max = pc.get("sm_mhz"), pc.get("sm_max_mhz")
+  regime = "sustained" if (mhz and mhz_max and mhz < 0.85 * mhz_max) else "burst"
+  tensor_peak = peaks["bf16_tflops_sustained"] if regime == "sustained" else peaks["bf16_tflops"]
   table = {}
   for n, ms in kernels.items():
     if n not in work:
@@ -452,7 +510,8 @@ def main():
     if bound == "tensor":
       ach = amount / (ms * 1e-3) / 1e12
       table[n] = dict(ms=round(ms, 4), bound=bound, achieved=round(ach, 1), unit="TFLOP/s",
-                      frac=round(ach / peaks["bf16_tflops_sustained"], 4))
+                      frac=round(ach / tensor_peak, 4), frac_burst=round(ach / peaks["bf16_tflops"], 4),
+                      frac_sustained=round(ach / peaks["bf16_tflops_sustained"], 4))
     elif amount > 0:
       ach = amount / (ms * 1e-3) / 1e9
       table[n] = dict(ms=round(ms, 4), bound=bound, achieved=round(ach, 1), unit="GB/s",
@@ -466,23 +525,33 @@ def main():
   dk = table.get(dominant)
   if dk is not None:
     roofline = {"kernel": dominant, "bound": dk["bound"], "achieved": dk["achieved"],
-                "peak": peaks["bf16_tflops_sustained"] if dk["bound"] == "tensor" else peaks["hbm_gbs"],
-                "unit": dk["unit"], "frac": dk["frac"], "traffic": KNOWN_TRAFFIC.get((args.config, dominant)) if not args.tokens else None,
+                "peak": tensor_peak if dk["bound"] == "tensor" else peaks["hbm_gbs"],
+                "unit": dk["unit"], "frac": dk["frac"], "traffic": measured_traffic(args.config, dominant, c["T"]),
                 "algorithmic": work[dominant][1],
-                "peak_source": f"{peak_kind} ({'sustained bf16 GEMM' if dk['bound'] == 'tensor' else 'copy bandwidth'}; "
-                               "kernel timed inside the step)",
-                "ms_per_launch": dk["ms"]}
+                "peak_source": f"{peak_kind}: " + (f"{regime} bf16 GEMM (median SM clock {mhz} of {mhz_max} MHz while the kernels "
+                                                   "were timed)" if dk["bound"] == "tensor" else "copy bandwidth"),
+                "ms_per_launch": dk["ms"], "ms_x_mhz": round(dk["ms"] * mhz, 1) if mhz else None}
+    if dk["bound"] == "tensor":
+      roofline.update(frac_burst=dk["frac_burst"], frac_sustained=dk["frac_sustained"])
   gemm_ms = sum(ms for n, ms in kernels.items() if work.get(n, ("", 0))[0] == "tensor" and n not in overlapped)
   gemm_flops = sum(work[n][1] for n in kernels if work.get(n, ("", 0))[0] == "tensor" and n not in overlapped)
-  mem_names = ("dispatch_gather", "combine_gather_reduce", "combine_bwd_gather_dot", "combine_bwd_scaled_gather",
-               "combine_bwd_gather", "dispatch_bwd_gather_reduce", "combine_reduce", "combine_bwd_reduce")
+  routed = ("gemm_gateup_swiglu", "gemm_down", "gemm_dh_dswiglu", "gemm_dw_down", "gemm_dx", "gemm_dw_gateup")
+  routed_ms = sum(kernels[n] for n in routed if n in kernels)
+  routed_flops = sum(work[n][1] for n in routed if n in kernels)
+  mem_names = ("dispatch_gather", "combine_gather_reduce", "combine_bwd_gather", "dispatch_bwd_gather_reduce",
+               "combine_reduce", "combine_bwd_reduce")
   mem_ms = sum(ms for n, ms in kernels.items() if n in mem_names)
   mem_bytes = sum(work[n][1] for n in mem_names if n in kernels)
+  tf = lambda flops, ms: flops / (ms * 1e-3) / 1e12
   summary = {
-      "layer_tflops": round(layer_flops(c) / (ms_step * 1e-3) / 1e12, 1),
-      "layer_frac_of_bf16_peak": round(layer_flops(c) / (ms_step * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], 4),
-      "grouped_gemm_tflops": round(gemm_flops / (gemm_ms * 1e-3) / 1e12, 1) if gemm_ms else None,
-      "grouped_gemm_frac_of_bf16_peak": round(gemm_flops / (gemm_ms * 1e-3) / 1e12 / peaks["bf16_tflops_sustained"], 4) if gemm_ms else None,
+      "tensor_regime": regime, "sm_mhz_while_kernels_timed": mhz,
+      "layer_tflops": round(tf(layer_flops(c), ms_step), 1),
+      "layer_frac_of_bf16_burst": round(tf(layer_flops(c), ms_step) / peaks["bf16_tflops"], 4),
+      "layer_frac_of_bf16_sustained": round(tf(layer_flops(c), ms_step) / peaks["bf16_tflops_sustained"], 4),
+      "grouped_gemm_tflops": round(tf(routed_flops, routed_ms), 1) if routed_ms else None,
+      "grouped_gemm_frac_of_bf16_burst": round(tf(routed_flops, routed_ms) / peaks["bf16_tflops"], 4) if routed_ms else None,
+      "grouped_gemm_frac_of_bf16_sustained": round(tf(routed_flops, routed_ms) / peaks["bf16_tflops_sustained"], 4) if routed_ms else None,
+      "all_gemm_tflops": round(tf(gemm_flops, gemm_ms), 1) if gemm_ms else None,
       "permute_combine_gbs": round(mem_bytes / (mem_ms * 1e-3) / 1e9, 1) if mem_ms else None,
       "permute_combine_frac_of_hbm": round(mem_bytes / (mem_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4) if mem_ms else None,
   }
@@ -500,9 +569,10 @@ def main():
       "metric": METRIC, "value": c["T"] * world / (ms_step * 1e-3), "unit": "tokens/s", "n_gpus": world,
       "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
       "vs_baseline": None, "dtype": "bf16", "data": "synthetic", "config": workload_config(args, c, world),
-      "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "timed_with": timed_with, "kernel_events": kernel_events, "eager_ms_per_step": round(eager_ms_step, 4),
+      "clocks": clocks, "e2e": e2e, "gpu_launches": int(launches), "timed_with": timed_with,
+      "preload_steps": preload_steps, "kernel_events": kernel_events, "eager_ms_per_step": round(eager_ms_step, 4),
       "host_enqueue_ms_per_step": round(host_ms, 3),
-      "roofline": roofline, "cpu_baseline": cpu_baseline,
+      "roofline": roofline, "cpu_baseline": cpu_baseline, "ep_parity": ep_parity,
       "summary": summary, "kernels": table,
   }
   print(json.dumps(line), flush=True)
@@ -510,17 +580,72 @@ def main():
     dist.destroy_process_group()
 
 
-# DRAM traffic per launch (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu captures summarised in
-# profiles/grouped_gemm_config2_t8k.md: measured at T=4096 and T=8192 tokens of config 2 and extended linearly in T
-# (expert weights are constant, row traffic is proportional) to the T=32768 launch the bench times.  Bytes.
-KNOWN_TRAFFIC = {
-    ("config2", "gemm_gateup_swiglu"): 1305e6,
-    ("config2", "gemm_down"): 741e6,
-    ("config2", "gemm_dh_dswiglu"): 1417e6,
-    ("config2", "gemm_dw_down"): 834e6,
-    ("config2", "gemm_dx"): 1096e6,
-    ("config2", "gemm_dw_gateup"): 1150e6,
-}
+def measured_traffic(config, kernel, tokens):
+  """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of `kernel`, from the ncu captures recorded
+  in the traffic table next to the profile summaries: measured at reduced token counts of the same workload and
+  extended linearly in the token count (expert weights are constant, row traffic is proportional)."""
+  path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+  try:
+    with open(path) as fh:
+      rec = json.load(fh)[config][kernel]
+    (t0, b0), (t1, b1) = sorted(zip(rec["tokens"], rec["bytes"]))[:2]
+    return b0 + (b1 - b0) * (tokens - t0) / (t1 - t0)
+  except Exception:  # noqa: BLE001  (no capture on record for this kernel / workload)
+    return None
+
+
+def ep_parity_check(args, c, rank, world, device, torch, dist, tokens=1024):
+  """One small expert-parallel step (`tokens` per rank, the workload's widths) checked against the CPU oracle on the
+  concatenated batch: out and dx of every rank, the owners' expert weight gradients.  Runs before the timed region;
+  a mismatch ends the run with a non-zero exit code."""
+  import numpy as np
+  import oracle as O
+  from lewi_surge_b200 import ep, layer, _lib
+  d, E, f, k, fs = c["d"], c["E"], c["f"], c["k"], c["fs"]
+  el = E // world
+  full = O.make_inputs(tokens * world, d, E, f, fs, seed=4242)      # every rank builds the same global problem
+  bias = O.zipf_bias(E, 4242) if c["bias"] else None
+  bf = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device=device, dtype=torch.bfloat16)
+  lo, hi = rank * el, (rank + 1) * el
+  w = layer.MoEWeights(torch.from_numpy(full["w_router"]).to(device), bf(full["w_gate"][lo:hi]), bf(full["w_up"][lo:hi]),
+                       bf(full["w_down"][lo:hi]), bf(full["ws_gate"]), bf(full["ws_up"]), bf(full["ws_down"]),
+                       torch.from_numpy(bias).to(device) if bias is not None else None)
+  runner = ep.ExpertParallelP2P(w, k, E, tokens, d, dist.group.WORLD, phases=args.ep_phases, sync=args.ep_sync)
+  sl = slice(rank * tokens, (rank + 1) * tokens)
+  out, g = runner.step(bf(full["x"][sl]), bf(full["dout"][sl]))
+  status = _lib.last_status()
+  mine = dict(out=out, dx=g["dx"], logits=runner.last_logits, dw_gate=g["dw_gate"], dw_up=g["dw_up"], dw_down=g["dw_down"])
+  gathered = {}
+  for name, ten in mine.items():
+    ten = ten.float().contiguous()
+    parts = [torch.empty_like(ten) for _ in range(world)] if rank == 0 else None
+    dist.gather(ten, parts, dst=0)
+    if rank == 0:
+      gathered[name] = torch.cat(parts, 0).cpu().numpy()
+  st = torch.tensor([status], dtype=torch.int32, device=device)
+  dist.all_reduce(st, op=dist.ReduceOp.MAX)
+  runner.close()
+  res = None
+  if rank == 0:
+    names = ("x", "w_router", "w_gate", "w_up", "w_down", "ws_gate", "ws_up", "ws_down")
+    a = [full[n] for n in names]
+    want, cache = O.moe_layer_fwd(*a, k, logits=gathered["logits"])    # the devices' own logits: routing is comparable
+    gw = O.moe_layer_bwd(full["dout"], *a, k, cache)
+    errs = {"out": O.rel_err(gathered["out"], want), "dx": O.rel_err(gathered["dx"], gw["dx"])}
+    for n in ("dw_gate", "dw_up", "dw_down"):
+      errs[n] = O.rel_err(gathered[n], gw[n])
+    worst = max(errs.values())
+    res = {"tokens_per_rank": tokens, "max_rel_err": worst, "errors": {n: round(v, 6) for n, v in errs.items()},
+           "device_status": int(st.item()), "ok": bool(worst <= 1e-2 and int(st.item()) == 0),
+           "checked": "out, dx of every rank and the owners' dW_gate/dW_up/dW_down against the float32 CPU oracle on the "
+                      "concatenated batch"}
+  flag = torch.tensor([1 if (res is None or res["ok"]) else 0], dtype=torch.int32, device=device)
+  dist.broadcast(flag, src=0)
+  if int(flag.item()) == 0:
+    if rank == 0:
+      print(json.dumps({"ep_parity": res}), flush=True)
+    raise SystemExit("expert-parallel parity check failed")
+  return res
 
 
 if __name__ == "__main__":

@@ -56,7 +56,9 @@ int lewi_last_status(void* stream);
 /* Static bound on padded rows: floor((m + num_experts*(block-1)) / block) * block. */
 int64_t lewi_padded_rows_bound(int64_t m, int num_experts, int block);
 
-/* Bytes of scratch that lewi_router_topk / lewi_sort_indices need for T tokens (M = T*k slots). */
+/* Bytes of scratch that lewi_router_topk / lewi_sort_indices need for M = T*k slots.  The bound is deliberately
+ * conservative (it assumes the smallest chunk the kernels ever use, 128 slots); lewi_router_topk actually works in
+ * chunks of 128*k slots and touches about 1/k of it. */
 int64_t lewi_route_workspace_bytes(int64_t num_slots, int num_experts);
 
 /* ------------------------------------------------------------------------------------------------
@@ -84,12 +86,14 @@ int lewi_router_logits(void* stream, const void* x, const float* w_router, const
  *   order i32 [M], pos i32 [M]      exactly sort_indices() of the reference (pos = inverse of order)
  *   pad_pos i32 [M]                 padded row of slot i
  *   row_slot i32 [Mpad]             slot held by padded row r, -1 for a padding row
- *   probs_mean f32 [E] or null      column sums of the soft-max probabilities (for the load-balance loss)
+ *   probs_sum f32 [E] or null       column sums of the soft-max probabilities (for the load-balance loss)
+ *   aux_loss f32 [1] or null        load-balance loss E * sum_e (counts[e] / (T*k)) * (probs_sum[e] / T), unweighted
+ *                                   (configs/stage1.yml:41 weights it by load_balance_loss_weight; needs probs_sum)
  */
 int lewi_router_topk(void* stream, const float* logits, int64_t T, int E, int k, int block,
                      int32_t* topk_idx, float* topk_w, int32_t* counts, int32_t* offsets,
                      int32_t* pad_offsets, int32_t* block_expert, int32_t* n_blocks, int32_t* order,
-                     int32_t* pos, int32_t* pad_pos, int32_t* row_slot, float* probs_sum,
+                     int32_t* pos, int32_t* pad_pos, int32_t* row_slot, float* probs_sum, float* aux_loss,
                      void* workspace, int64_t workspace_bytes);
 
 /* lewi_router_topk without a workspace argument.  It has no counterpart in the reference: it exists
@@ -130,11 +134,24 @@ int lewi_router_topk_bwd(void* stream, const float* logits, const int32_t* topk_
                          float* dlogits, void* dlogits_bf16, int64_t T, int E, int k);
 
 /* Same, with the routing-weight gradient given as pieces: dw[t,j] = sum_p dw_partial[pad_pos[t*k+j], p]
- * (the pieces are written by lewi_grouped_gemm_dh_dswiglu_gather).  dw may then be null; dw_out [T,k]
+ * (the pieces are written by lewi_grouped_gemm_dh_dswiglu_scaled).  dw may then be null; dw_out [T,k]
  * (optional) receives the summed gradient. */
 int lewi_router_topk_bwd_partial(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
                                  const float* dw_partial, int dw_parts, const int32_t* pad_pos, float* dw_out,
                                  float* dlogits, void* dlogits_bf16, int64_t T, int E, int k);
+
+/* The complete router backward.  On top of lewi_router_topk_bwd_partial:
+ *   counts i32 [E] + aux_grad    adds the gradient of aux_grad * (the load-balance loss lewi_router_topk reports) to
+ *                                dlogits; the token fractions counts/(T*k) are constants of that loss (counts null or
+ *                                aux_grad 0: no such term);
+ *   d_bias f32 [E] (optional)    column sums of dlogits = gradient of a router logit bias; needs a workspace of
+ *                                lewi_router_bias_grad_workspace_bytes(T, E) bytes; summed in a fixed order. */
+int64_t lewi_router_bias_grad_workspace_bytes(int64_t T, int E);
+int lewi_router_topk_bwd_full(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
+                              const float* dw_partial, int dw_parts, const int32_t* pad_pos, float* dw_out,
+                              float* dlogits, void* dlogits_bf16, int64_t T, int E, int k,
+                              const int32_t* counts, float aux_grad, float* d_bias, void* workspace,
+                              int64_t workspace_bytes);
 
 /* dst (bf16) = round-to-nearest-even(src (f32)), n elements.  Used for the bf16 copy of the f32 router
  * weight (the reference casts rhs to the lhs dtype before its GEMMs: modal/padded_gmm.py:67). */
@@ -183,7 +200,9 @@ int lewi_gather_dot(void* stream, const void* y, const int32_t* pos, const void*
  * pad_offsets i32 [E+1] (the padded row range of every expert, as the router call produces it) lets
  * the library run CTA pairs (tcgen05 cta_group::2: two SMs share one 256-row tile and each loads half
  * of the weight tile); when it is null but block_expert is given, single-CTA kernels are used.
- * K and N extents must be multiples of 8; all operands bf16.
+ * K and N extents must be multiples of 8; all operands bf16.  With several groups (E > 1) a call needs
+ * block_expert, or pad_offsets with CTA pairs enabled; otherwise it is rejected with LEWI_ERR_SHAPE.
+ * E <= 512 when pad_offsets is given (LEWI_ERR_LIMIT beyond).
  * ---------------------------------------------------------------------------------------------- */
 
 /* out[r, :] = a[r, :] . b[e]      a [rows,K], b [E,K,N], out [rows,N] (out_dtype), optional f32 row_scale[rows]. */
@@ -218,21 +237,16 @@ int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_
                                     const int32_t* block_expert, const int32_t* n_blocks,
                                     const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
 
-/* lewi_grouped_gemm_gateup_swiglu with the dispatch gather fused into the operand load: xs is the
- * UNPERMUTED source [src_rows,d]; padded row r reads xs[row_idx[r] / idx_div] (row_idx[r] < 0: zero row),
- * i.e. row_idx = row_slot and idx_div = k replace `_route_activations` (modal/moe_permute.py:399-404)
- * without materialising the permuted rows (row_idx null: xs is already in padded order).
- * h_scale_src (optional, f32 indexed by scale_idx[r]; scale_idx defaults to row_idx, and to r itself when
- * both are null) multiplies h: with
- * the router weights there, the down projection yields already-weighted expert outputs and the combine
- * needs no weights.  Measured note: the in-kernel row gather is correct but slower than gathering first
- * on B200; the scale is free. */
-int lewi_grouped_gemm_gateup_swiglu_gather(void* stream, const void* xs, const int32_t* row_idx, int idx_div,
-                                           int64_t src_rows, const int32_t* scale_idx,
-                                           const float* h_scale_src, const void* w_gate,
-                                           const void* w_up, void* gu, void* h,
-                                           const int32_t* block_expert, const int32_t* n_blocks,
-                                           const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
+/* lewi_grouped_gemm_gateup_swiglu whose epilogue also multiplies h by a per-row factor:
+ * h[r] *= h_scale_src[scale_idx[r]] (scale_idx[r] < 0: factor 0; scale_idx null: h_scale_src[r]).
+ * With the router weights there (scale_idx = row_slot, h_scale_src = topk_w flattened) the down projection yields
+ * already-weighted expert outputs and the combine (`unpermute`, modal/moe_permute.py:417-433) needs no weights.
+ * gu keeps the unscaled pre-activations. */
+int lewi_grouped_gemm_gateup_swiglu_scaled(void* stream, const void* xs, const int32_t* scale_idx,
+                                           const float* h_scale_src, const void* w_gate, const void* w_up,
+                                           void* gu, void* h, const int32_t* block_expert,
+                                           const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows,
+                                           int d, int f, int E);
 
 /* Backward of the down projection fused with the SwiGLU derivative:
  * dh = dys.Wd[e]^T; dg = dh*u*silu'(g); du = dh*silu(g).  dys [rows,d], w_down [E,f,d],
@@ -241,32 +255,103 @@ int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_do
                                  void* dgu, const int32_t* block_expert, const int32_t* n_blocks,
                                  const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
 
-/* Same with the upstream-gradient gather fused in (dys [src_rows,d] unpermuted, picked through row_idx /
- * idx_div; null: dys is in padded order), dh multiplied by scale_src[scale_idx[r]] (the router weight;
- * scale_idx defaults to row_idx), and, if dw_partial is not null,
+/* Same with dh multiplied by scale_src[scale_idx[r]] (the router weight of the row's slot; indexing as in
+ * lewi_grouped_gemm_gateup_swiglu_scaled) and, if dw_partial is not null,
  * dw_partial[r, p] = sum over a column range of dh_unscaled * silu(g) * u: the pieces of the routing-weight
  * gradient <dout[t], y[row]> (reference: gather_dot in `_combine_bwd`, modal/moe_permute.py:303-309).
  * dw_partial is [rows, lewi_dw_partial_parts(f)] f32. */
 int lewi_dw_partial_parts(int f);
-int lewi_grouped_gemm_dh_dswiglu_gather(void* stream, const void* dys, const int32_t* row_idx, int idx_div,
-                                        int64_t src_rows, const int32_t* scale_idx,
-                                        const float* scale_src, float* dw_partial,
-                                        const void* w_down, const void* gu, void* dgu,
-                                        const int32_t* block_expert, const int32_t* n_blocks,
-                                        const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
-
-/* lewi_grouped_gemm_tn where the contraction rows of a and/or b are picked through row_idx / idx_div
- * from an unpermuted source of src_rows rows (gather_a / gather_b non-zero). */
-int lewi_grouped_gemm_tn_gather(void* stream, const void* a, const void* b, void* out, void* out2,
-                                const int32_t* pad_offsets, int64_t rows, int Ma, int Nb, int E,
-                                int out_dtype, void* workspace, int64_t workspace_bytes,
-                                const int32_t* row_idx, int idx_div, int64_t src_rows, int gather_a,
-                                int gather_b);
+int lewi_grouped_gemm_dh_dswiglu_scaled(void* stream, const void* dys, const int32_t* scale_idx,
+                                        const float* scale_src, float* dw_partial, const void* w_down,
+                                        const void* gu, void* dgu, const int32_t* block_expert,
+                                        const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows,
+                                        int d, int f, int E);
 
 /* dxs = dg.Wg[e]^T + du.Wu[e]^T.  dgu [rows,2f], w_gate/w_up [E,d,f], dxs [rows,d] bf16. */
 int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, const void* w_up,
                          void* dxs, const int32_t* block_expert, const int32_t* n_blocks,
                          const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
+
+/* ------------------------------------------------------------------------------------------------
+ * The whole layer in two calls.  lewi_moe_fwd / lewi_moe_bwd queue the complete launch sequence of the MoE layer of
+ * the MaxText `qwen3_5` block as the reference patches it: router (softmax -> top-k -> renormalise,
+ * configs/stage1.yml:33-41) -> `_route_activations` (modal/moe_permute.py:399-404) -> the three `ragged_dot`s of the
+ * SwiGLU experts (modal/padded_gmm.py:45-69) -> `unpermute` (modal/moe_permute.py:417-433), plus the always-on shared
+ * expert (configs/stage1.yml:32,35), and the gradient of all of it with the gather-only structure of
+ * `_combine_bwd` / `_dispatch_bwd` (modal/moe_permute.py:282-309).
+ *
+ * Shapes: x, out, dout, dx bf16 [T,d]; w_router f32 [d,E], router_bias f32 [E] or null; w_gate, w_up bf16 [E,d,f],
+ * w_down bf16 [E,f,d] (wi_0, wi_1, wo: modal/stage2.py:338-341); shared expert ws_gate, ws_up bf16 [d,fs],
+ * ws_down bf16 [fs,d] (fs = 0: no shared expert, pointers null); w_sg f32 [d] or null: optional gate of the shared
+ * expert, out = routed + sigmoid(x . w_sg) * shared (the Hugging Face twin has it, tools/grow_7b.py:85; null = gate 1).
+ *
+ * Buffers the caller owns:
+ *   residual   lewi_moe_residual_layout(...) bytes; written by fwd, read by bwd (logits, routing tables, the permuted
+ *              rows xs, pre-activations g|u, h, the shared expert's g|u and h, the gate).  Item i of the
+ *              LEWI_MOE_RES_* list starts at byte offsets_host[i]; offsets_host has LEWI_MOE_RES_COUNT + 1 entries,
+ *              the last is the total.  The routing tables are those of lewi_router_topk.
+ *   workspace  lewi_moe_workspace_bytes(...) bytes of scratch; contents are undefined after a call, and one
+ *              workspace can serve fwd and bwd of any number of layers on the same stream.
+ * Both buffers must be 16-byte aligned.  `has_gate` (layout functions) = whether w_sg will be passed.
+ *
+ * side_stream (may be null or equal to stream): the shared expert, which needs only x / dout, is queued there
+ * between two events so that it overlaps the memory-bound routing, dispatch and gather kernels; the call
+ * returns with `stream` waiting for it.  The four events per device are created on first use and kept.
+ *
+ * router_prepared (may be null): the bf16 pieces of w_router that the router GEMMs read, as written by
+ * lewi_moe_prepare_router (lewi_moe_router_prepared_bytes(d,E) bytes); pass it to skip that conversion in
+ * every call while the router weight is unchanged.
+ *
+ * aux_loss f32 [1] (may be null) receives the load-balance loss of lewi_router_topk; bwd adds aux_grad times its
+ * gradient to the router gradient (aux_grad = load_balance_loss_weight x the upstream gradient of the loss; 0: none).
+ * dw_topk f32 [T,k] (may be null) receives the gradient of the routing weights; d_router_bias f32 [E] (may be null);
+ * dw_sg f32 [d] (given exactly when w_sg is); weight gradients of the experts and the shared expert have
+ * wgrad_dtype (LEWI_BF16 or LEWI_F32), dw_router is f32 [d,E].  Experts without rows get exactly-zero gradients.
+ * ---------------------------------------------------------------------------------------------- */
+#define LEWI_MOE_RES_LOGITS 0       /* f32 [T,E]        */
+#define LEWI_MOE_RES_TOPK_IDX 1     /* i32 [T,k]        */
+#define LEWI_MOE_RES_TOPK_W 2       /* f32 [T,k]        */
+#define LEWI_MOE_RES_COUNTS 3       /* i32 [E]          */
+#define LEWI_MOE_RES_OFFSETS 4      /* i32 [E+1]        */
+#define LEWI_MOE_RES_PAD_OFFSETS 5  /* i32 [E+1]        */
+#define LEWI_MOE_RES_N_BLOCKS 6     /* i32 [1]          */
+#define LEWI_MOE_RES_PROBS_SUM 7    /* f32 [E]          */
+#define LEWI_MOE_RES_BLOCK_EXPERT 8 /* i32 [Mpad/128]   */
+#define LEWI_MOE_RES_ORDER 9        /* i32 [T*k]        */
+#define LEWI_MOE_RES_POS 10         /* i32 [T*k]        */
+#define LEWI_MOE_RES_PAD_POS 11     /* i32 [T*k]        */
+#define LEWI_MOE_RES_ROW_SLOT 12    /* i32 [Mpad]       */
+#define LEWI_MOE_RES_XS 13          /* bf16 [Mpad,d]    */
+#define LEWI_MOE_RES_GU 14          /* bf16 [Mpad,2f]   */
+#define LEWI_MOE_RES_H 15           /* bf16 [Mpad,f] (times the router weight of the row) */
+#define LEWI_MOE_RES_GUS 16         /* bf16 [T,2fs]     */
+#define LEWI_MOE_RES_HS 17          /* bf16 [T,fs] (times the gate, if any) */
+#define LEWI_MOE_RES_GATE 18        /* f32 [T] (only with w_sg) */
+#define LEWI_MOE_RES_COUNT 19
+
+int64_t lewi_moe_residual_layout(int64_t T, int d, int E, int f, int k, int fs, int has_gate,
+                                 int64_t* offsets_host);
+int64_t lewi_moe_workspace_bytes(int64_t T, int d, int E, int f, int k, int fs, int has_gate);
+int64_t lewi_moe_router_prepared_bytes(int d, int E);
+int lewi_moe_prepare_router(void* stream, const float* w_router, void* prepared, int d, int E);
+
+int lewi_moe_fwd(void* stream, void* side_stream, const void* x, const float* w_router,
+                 const float* router_bias, const void* router_prepared, const void* w_gate, const void* w_up,
+                 const void* w_down, const void* ws_gate, const void* ws_up, const void* ws_down,
+                 const float* w_sg, void* out, float* aux_loss, void* residual, int64_t residual_bytes,
+                 void* workspace, int64_t workspace_bytes, int64_t T, int d, int E, int f, int k, int fs);
+
+int lewi_moe_bwd(void* stream, void* side_stream, const void* dout, const void* x, const float* w_router,
+                 const void* router_prepared, const void* w_gate, const void* w_up, const void* w_down,
+                 const void* ws_gate, const void* ws_up, const void* ws_down, const float* w_sg,
+                 const void* residual, int64_t residual_bytes, void* workspace, int64_t workspace_bytes,
+                 void* dx, float* dw_router, float* d_router_bias, void* dw_gate, void* dw_up, void* dw_down,
+                 void* dws_gate, void* dws_up, void* dws_down, float* dw_sg, float* dw_topk, float aux_grad,
+                 int wgrad_dtype, int64_t T, int d, int E, int f, int k, int fs);
+
+/* Profiling hook: fn(name, stream) is called on the host after each kernel (or kernel group) that lewi_moe_fwd /
+ * lewi_moe_bwd queue, with the stream it went to; a timing harness records events there.  null disables (default). */
+int lewi_moe_set_mark_callback(void (*fn)(const char*, void*));
 
 /* ------------------------------------------------------------------------------------------------
  * Expert parallelism over peer memory (one process per GPU on an NVSwitch node).  The reference never ran
@@ -342,16 +427,9 @@ int lewi_ep_put_i32(void* stream, const int32_t* src, void* const* peers_dst_hos
 int lewi_ep_barrier(void* stream, void* const* peers_flags_host, int32_t* my_flags, int32_t* epoch_counter, int me,
                     int G, int64_t timeout_ms);
 
-/* Bring-up hook (not part of the drop-in surface): overrides the shared-memory matrix-descriptor
- * geometry in bytes for K-major and MN-major operands; 0 keeps a value. */
-int lewi_debug_set_desc(int k_lbo, int k_sbo, int k_step, int mn_lbo, int mn_sbo, int mn_step);
-
-/* Bring-up hook: 0 forces the single-CTA GEMM kernels everywhere, 1 (default) allows CTA pairs. */
-int lewi_debug_set_cta_pair(int on);
-
-/* Bring-up hook for timing experiments: bit 0 epilogue without global I/O, bit 1 epilogue only returns the
- * accumulator, bit 2 producer skips the B operand.  Any non-zero value makes results wrong; default 0. */
-int lewi_debug_set_flags(int flags);
+/* A/B switch: 0 forces the single-CTA (cta_group::1) GEMM kernels everywhere, 1 (default) allows CTA pairs
+ * (cta_group::2) where pad_offsets is given.  Host-side, read at launch time. */
+int lewi_set_cta_pair(int on);
 
 #ifdef __cplusplus
 }

@@ -26,17 +26,18 @@ SIGNATURES = {
     "lewi_route_workspace_bytes": (c_int64, [c_int64, c_int]),
     "lewi_router_logits_workspace_bytes": (c_int64, [c_int, c_int]),
     "lewi_router_logits": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, P, c_int64]),
-    "lewi_router_topk": (c_int, [P, P, c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P, P, P, c_int64]),
+    "lewi_router_topk": (c_int, [P, P, c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P, P, P, P, c_int64]),
     "lewi_router_topk_static_max_bytes": (c_int64, []),
     "lewi_router_topk_static": (c_int, [P, P, c_int64, c_int, c_int, c_int, P, P, P, P, P, P, P, P, P, P, P, P]),
     "lewi_sort_indices": (c_int, [P, P, c_int64, c_int, c_int, P, P, P, P, P, P, P, P, P, P, c_int64]),
     "lewi_router_topk_bwd": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int]),
     "lewi_cast_f32_to_bf16": (c_int, [P, P, P, c_int64]),
     "lewi_router_topk_bwd_partial": (c_int, [P, P, P, P, P, c_int, P, P, P, P, c_int64, c_int, c_int]),
-    "lewi_grouped_gemm_gateup_swiglu_gather": (c_int, [P, P, P, c_int, c_int64, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_router_bias_grad_workspace_bytes": (c_int64, [c_int64, c_int]),
+    "lewi_router_topk_bwd_full": (c_int, [P, P, P, P, P, c_int, P, P, P, P, c_int64, c_int, c_int, P, c_float, P, P, c_int64]),
+    "lewi_grouped_gemm_gateup_swiglu_scaled": (c_int, [P, P, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_dw_partial_parts": (c_int, [c_int]),
-    "lewi_grouped_gemm_dh_dswiglu_gather": (c_int, [P, P, P, c_int, c_int64, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
-    "lewi_grouped_gemm_tn_gather": (c_int, [P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, P, c_int64, P, c_int, c_int64, c_int, c_int]),
+    "lewi_grouped_gemm_dh_dswiglu_scaled": (c_int, [P, P, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_group_tables": (c_int, [P, P, c_int64, c_int, c_int, P, P, P, P, P]),
     "lewi_gather_rows": (c_int, [P, P, P, P, P, c_int64, c_int64, c_int, c_int, c_int, c_int, P, c_int]),
     "lewi_gather_reduce": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64]),
@@ -48,6 +49,13 @@ SIGNATURES = {
     "lewi_grouped_gemm_gateup_swiglu": (c_int, [P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dh_dswiglu": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dx": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_moe_residual_layout": (c_int64, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, P]),
+    "lewi_moe_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int]),
+    "lewi_moe_router_prepared_bytes": (c_int64, [c_int, c_int]),
+    "lewi_moe_prepare_router": (c_int, [P, P, P, c_int, c_int]),
+    "lewi_moe_fwd": (c_int, [P] * 16 + [c_int64, P, c_int64, c_int64, c_int, c_int, c_int, c_int, c_int]),
+    "lewi_moe_bwd": (c_int, [P] * 14 + [c_int64, P, c_int64] + [P] * 11 + [c_float, c_int, c_int64, c_int, c_int, c_int, c_int, c_int]),
+    "lewi_moe_set_mark_callback": (c_int, [P]),
     "lewi_ep_alloc": (c_int, [c_int64, P]),
     "lewi_ep_free": (c_int, [P]),
     "lewi_ep_ipc_export": (c_int, [P, P]),
@@ -61,9 +69,7 @@ SIGNATURES = {
     "lewi_set_sm_sharing": (c_int, [c_int]),
     "lewi_ep_put_i32": (c_int, [P, P, P, c_int64, c_int, c_int]),
     "lewi_ep_barrier": (c_int, [P, P, P, P, c_int, c_int, c_int64]),
-    "lewi_debug_set_cta_pair": (c_int, [c_int]),
-    "lewi_debug_set_flags": (c_int, [c_int]),
-    "lewi_debug_set_desc": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int]),
+    "lewi_set_cta_pair": (c_int, [c_int]),
 }
 
 _lib = None

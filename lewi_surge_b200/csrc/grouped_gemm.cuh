@@ -2,7 +2,7 @@
 //
 // One persistent, warp-specialised kernel per (operand-major, epilogue) combination:
 //   warp 0      TMA producer: tiled cp.async.bulk.tensor loads (128-byte swizzle, no multicast)
-//               into a 4-stage shared-memory ring;
+//               into a shared-memory ring (4 stages of 48 KB per CTA, or 6 of 32 KB per CTA of a pair);
 //   warp 1      allocates TMEM and issues tcgen05.mma (128 x 256 x 16, bf16 in, f32 accumulate)
 //               from one thread; accumulators are double-buffered in TMEM (2 x 256 columns);
 //   warps 2-9   epilogue: tcgen05.ld the accumulator (thread = row; two warps share a TMEM lane
@@ -27,30 +27,31 @@ constexpr int BN = 256;       // accumulator columns per tile (MMA N)
 constexpr int BK = 64;        // contraction elements per stage (128 bytes of bf16)
 constexpr int DATA_BYTES = 224 * 1024;         // operand ring + epilogue staging of one CTA
 constexpr int EPI_WARPS = 8;      // two warps per TMEM lane quarter, each takes half of the columns
-// The dSwiGLU epilogue moves its g|u and dg|du blocks with TMA and needs 8 KB of staging per warp (two 32-row x
-// 128-byte swizzled tiles); the others transpose 32x32 blocks through 4 KB.  The ring gets the rest.
-__host__ __device__ constexpr int staging_per_warp(int epi) { return epi == 2 /* DSWIGLU */ ? 8192 : 4096; }
+// Every epilogue warp moves its output (and the dSwiGLU epilogue also its g|u input) as TMA tiles of 32 rows x
+// 128 bytes (128-byte swizzle, 4 KB).  It owns two such tiles of staging, three under the SwiGLU epilogue, which
+// stores g, u and h of the same columns.  The operand ring gets the rest.
+constexpr int TILE_BYTES = 4096;
+__host__ __device__ constexpr int staging_per_warp(int epi) { return epi == 1 /* SWIGLU */ ? 3 * TILE_BYTES : 2 * TILE_BYTES; }
 __host__ __device__ constexpr int ring_bytes(int epi) { return DATA_BYTES - EPI_WARPS * staging_per_warp(epi); }
 constexpr int A_BYTES = BM * BK * 2;           // 16 KB
 constexpr int CHUNK_BYTES = 64 * BK * 2;       // 8 KB: one [64 k][64 mn] box of an MN-major operand
-// One CTA per tile (cta_group::1): B is 256 x 64 = 32 KB, 4 stages of 48 KB (3 under the dSwiGLU epilogue).
+// One CTA per tile (cta_group::1): B is 256 x 64 = 32 KB, 3 stages of 48 KB (2 under the SwiGLU epilogue).
 // A CTA pair per 256-row tile (cta_group::2): each CTA holds its own 128 rows of A and HALF of B
-// (128 x 64 = 16 KB), 6 stages of 32 KB (5 under dSwiGLU); the tensor cores of both SMs read both halves.
+// (128 x 64 = 16 KB), 5 stages of 32 KB (4 under SwiGLU); the tensor cores of both SMs read both halves.
 template <bool PAIR, int EPI = 0> struct Cfg {
   static constexpr int B_BYTES = PAIR ? BN * BK : BN * BK * 2;
   static constexpr int STAGE_BYTES = A_BYTES + B_BYTES;
   static constexpr int STAGES = ring_bytes(EPI) / STAGE_BYTES;
 };
-constexpr int MAX_STAGES = 6;
-constexpr int PAIR_PREFIX_BYTES = 1040;        // uint16 prefix of row-block pairs per expert (E <= 512)
-constexpr int GATHER_ROWS_BYTES = 512;         // source-row numbers of the tile being gathered
+constexpr int MAX_STAGES = 5;
+constexpr int PAIR_PREFIX_BYTES = 1040;        // uint16 prefix per expert (E <= 512): row-block pairs (NN/NT) or contraction parts (TN)
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr int TMEM_COLS = 512;
 constexpr int EPI_BAR_BYTES = 64;        // one mbarrier per epilogue warp (TMA loads of the dSwiGLU epilogue)
-// 231,248 bytes.  An SM has 233,472 and every resident CTA reserves 1,024 of them, so exactly one more CTA that
+// 230,736 bytes.  An SM has 233,472 and every resident CTA reserves 1,024 of them, so exactly one more CTA that
 // uses no shared memory (a gather or exchange kernel from another stream) fits beside a GEMM CTA.  That is why
 // there is no slack for aligning the ring: the kernel asks for a 1024-byte aligned base and checks it.
-constexpr size_t SMEM_BYTES = (size_t)DATA_BYTES + 256 /*barriers*/ + PAIR_PREFIX_BYTES + GATHER_ROWS_BYTES + EPI_BAR_BYTES;
+constexpr size_t SMEM_BYTES = (size_t)DATA_BYTES + 256 /*barriers*/ + PAIR_PREFIX_BYTES + EPI_BAR_BYTES;
 
 enum Major { NN = 0, NT = 1, TN = 2 };
 enum Epi { PLAIN = 0, SWIGLU = 1, DSWIGLU = 2, TNOUT = 3 };
@@ -77,19 +78,15 @@ struct Args {
   int k_splits;                 // TN: the contraction of every output tile is cut into this many parts
   float* partial;               // TN with k_splits > 1: f32 partial products [k_splits, E, Ma, N]
   const float* col_bias;        // PLAIN: optional f32 per output column
+  const float* r1_row;          // PLAIN: optional rank-one term added to the product: out[r,n] += r1_row[r] * r1_col[n]
+  const float* r1_col;
+  int tn_part_rows;             // TN over several experts: > 0 cuts an expert's contraction into parts of this many rows
+                                // (a multiple of 64); experts with more than one part go through `partial`
   const int32_t* scale_idx;     // SWIGLU / DSWIGLU: padded row -> index into scale_src (negative: scale 0; null: the row itself)
   const float* scale_src;       // SWIGLU / DSWIGLU: optional f32 table indexed by scale_idx[row] (router weight of the
                                 // row's slot); SWIGLU stores h * scale, DSWIGLU multiplies dh by it
   float* dw_partial;            // DSWIGLU: optional [rows, dw_parts] f32, sum over this warp's columns of
   int dw_parts;                 //   dh_unscaled * silu(g) * u  (= pieces of the routing-weight gradient)
-  const void* ga_ptr;           // gathered A operand (bf16 rows picked through g_idx) or null: A comes through tm_a
-  const void* gb_ptr;           // TN only: gathered B operand or null
-  long long ga_ld, gb_ld;       // row strides (elements) of the gathered sources
-  const int32_t* g_idx;         // padded row -> source index (negative = zero row)
-  int g_div;                    // source row = index / g_div (slot -> token)
-  int g_src_rows;               // rows of the gathered source (indices beyond it give zero rows)
-  int dbg;                      // bring-up experiments only (0 in production): 1 no global I/O in the epilogue,
-                                // 2 epilogue only hands the accumulator back, 4 the producer skips the B operand
   uint64_t desc_hi_a, desc_hi_b;
   uint32_t kstep_a, kstep_b;    // bytes to advance the descriptor start per 16-wide k step
   uint32_t idesc;
@@ -97,78 +94,60 @@ struct Args {
 
 __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.0f, 1.0f + __expf(-x)); }
 
-// ---- epilogue I/O.  A thread owns one row of the accumulator (TMEM lane = row), but a warp-wide
-// store of "my row's 16 bytes" would touch 32 different lines.  Blocks of 32 rows x 32 columns are
-// therefore transposed through a small swizzled staging buffer in shared memory so that every
-// global load/store instruction covers whole 64- or 128-byte row segments.
-
-// 32 x 32 f32 (one row per lane) -> bf16 rows of 64 bytes.  `base` points at (first row of the warp,
-// first column of the block); rows >= rows_valid and 8-column groups >= cols_valid are skipped.
-__device__ __forceinline__ void warp_store32_bf16(uint8_t* stage, int lane, const float* v, __nv_bfloat16* base,
-                                                  long long ld, int rows_valid, int cols_valid) {
+// ---- epilogue output.  A thread owns one row of the accumulator (TMEM lane = row).  Rows are written into a
+// staging tile of 32 rows x 128 bytes in the layout a 128-byte-swizzled TMA box has in shared memory (16-byte piece
+// q of row r sits at r*128 + ((q ^ (r & 7)) << 4)); one lane then stores the tile with cp.async.bulk.tensor, which
+// writes whole 128-byte lines and clips rows and columns that lie outside the tensor.
+__device__ __forceinline__ void tile_put16(uint8_t* tile, int lane, int piece, uint4 v) {
+  *reinterpret_cast<uint4*>(tile + lane * 128 + ((piece ^ (lane & 7)) << 4)) = v;
+}
+// 32 floats of this lane's row -> bf16 pieces [piece0, piece0 + 4) of the tile
+__device__ __forceinline__ void tile_put_bf16x32(uint8_t* tile, int lane, int piece0, const float* v) {
 #pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    uint4 pk = make_uint4(pack_bf16(v[q * 8 + 0], v[q * 8 + 1]), pack_bf16(v[q * 8 + 2], v[q * 8 + 3]),
-                          pack_bf16(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16(v[q * 8 + 6], v[q * 8 + 7]));
-    *reinterpret_cast<uint4*>(stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4)) = pk;
-  }
-  __syncwarp();
+  for (int q = 0; q < 4; ++q)
+    tile_put16(tile, lane, piece0 + q,
+               make_uint4(pack_bf16(v[q * 8 + 0], v[q * 8 + 1]), pack_bf16(v[q * 8 + 2], v[q * 8 + 3]),
+                          pack_bf16(v[q * 8 + 4], v[q * 8 + 5]), pack_bf16(v[q * 8 + 6], v[q * 8 + 7])));
+}
+// 32 floats of this lane's row -> the whole tile as f32
+__device__ __forceinline__ void tile_put_f32x32(uint8_t* tile, int lane, const float* v) {
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = i * 8 + (lane >> 2), seg = lane & 3;
-    const uint4 pk = *reinterpret_cast<const uint4*>(stage + r * 64 + ((seg ^ ((r >> 1) & 3)) << 4));
-    if (r < rows_valid && seg * 8 < cols_valid) st_v4(base + r * ld + seg * 8, pk);
-  }
-  __syncwarp();
+  for (int q = 0; q < 8; ++q)
+    tile_put16(tile, lane, q,
+               make_uint4(__float_as_uint(v[q * 4]), __float_as_uint(v[q * 4 + 1]), __float_as_uint(v[q * 4 + 2]),
+                          __float_as_uint(v[q * 4 + 3])));
 }
 
-// 32 x 32 f32 (one row per lane) -> f32 rows of 128 bytes.
-__device__ __forceinline__ void warp_store32_f32(uint8_t* stage, int lane, const float* v, float* base, long long ld,
-                                                 int rows_valid, int cols_valid) {
-#pragma unroll
-  for (int q = 0; q < 8; ++q) {
-    uint4 pk = make_uint4(__float_as_uint(v[q * 4]), __float_as_uint(v[q * 4 + 1]), __float_as_uint(v[q * 4 + 2]),
-                          __float_as_uint(v[q * 4 + 3]));
-    *reinterpret_cast<uint4*>(stage + lane * 128 + ((q ^ (lane & 7)) << 4)) = pk;
+// One warp's staging tiles, used round-robin.  acquire() hands out the next tile once the TMA store that last
+// read it has finished reading; commit(...) is called after the warp has filled the tile.
+template <int NBUF>
+struct TileStager {
+  uint8_t* base;
+  uint32_t n;
+  __device__ __forceinline__ uint8_t* acquire(int lane) {
+    if (lane == 0 && n >= NBUF) ptx::bulk_wait_read_n<NBUF - 1>();
+    __syncwarp();
+    return base + (n % NBUF) * TILE_BYTES;
   }
-  __syncwarp();
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const int r = i * 4 + (lane >> 3), seg = lane & 7;
-    const uint4 pk = *reinterpret_cast<const uint4*>(stage + r * 128 + ((seg ^ (r & 7)) << 4));
-    if (r < rows_valid && seg * 4 < cols_valid) st_v4(base + r * ld + seg * 4, pk);
+  __device__ __forceinline__ void store2d(int lane, const void* tmap, uint8_t* tile, int c0, int c1) {
+    ptx::fence_proxy_async();   // the tile was written through the generic proxy, the store reads it through the async one
+    __syncwarp();
+    if (lane == 0) {
+      ptx::tma_store_2d(tmap, ptx::smem_u32(tile), c0, c1);
+      ptx::bulk_commit();
+    }
+    ++n;
   }
-  __syncwarp();
-}
-
-// Coalesced read of a 32 x 32 bf16 block into registers (4 x 16 bytes per lane, not yet transposed).
-__device__ __forceinline__ void warp_fetch32_bf16(int lane, const __nv_bfloat16* base, long long ld, int rows_valid,
-                                                  int cols_valid, uint4 (&t)[4]) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = i * 8 + (lane >> 2), seg = lane & 3;
-    t[i] = make_uint4(0, 0, 0, 0);
-    if (r < rows_valid && seg * 8 < cols_valid) t[i] = ld_nc_v4(base + r * ld + seg * 8);
+  __device__ __forceinline__ void store3d(int lane, const void* tmap, uint8_t* tile, int c0, int c1, int c2) {
+    ptx::fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      ptx::tma_store_3d(tmap, ptx::smem_u32(tile), c0, c1, c2);
+      ptx::bulk_commit();
+    }
+    ++n;
   }
-}
-// Registers of warp_fetch32_bf16 -> staging -> this lane's own row as 32 floats.
-__device__ __forceinline__ void warp_own_row32_bf16(uint8_t* stage, int lane, const uint4 (&t)[4], float* v) {
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const int r = i * 8 + (lane >> 2), seg = lane & 3;
-    *reinterpret_cast<uint4*>(stage + r * 64 + ((seg ^ ((r >> 1) & 3)) << 4)) = t[i];
-  }
-  __syncwarp();
-#pragma unroll
-  for (int q = 0; q < 4; ++q) {
-    const uint4 pk = *reinterpret_cast<const uint4*>(stage + lane * 64 + ((q ^ ((lane >> 1) & 3)) << 4));
-    v[q * 8 + 0] = bf16_lo(pk.x); v[q * 8 + 1] = bf16_hi(pk.x);
-    v[q * 8 + 2] = bf16_lo(pk.y); v[q * 8 + 3] = bf16_hi(pk.y);
-    v[q * 8 + 4] = bf16_lo(pk.z); v[q * 8 + 5] = bf16_hi(pk.z);
-    v[q * 8 + 6] = bf16_lo(pk.w); v[q * 8 + 7] = bf16_hi(pk.w);
-  }
-  __syncwarp();
-}
+};
 
 struct Tile {
   int e;        // expert
@@ -179,7 +158,7 @@ struct Tile {
   int nlim;     // columns >= nlim are not stored by this tile
   int kb0;      // first 64-wide contraction step of this tile
   int kb;       // number of 64-wide contraction steps
-  int split;    // TN: index of the contraction part
+  int split;    // TN: slot of this part in `partial`, or -1 when the tile is stored straight to the output
 };
 
 // Row-block pairs (pair mode, NN/NT): expert e owns ceil(blocks_e / 2) pairs; pp[e] is the exclusive
@@ -192,10 +171,33 @@ __device__ __forceinline__ Tile decode_tile(const Args& a, int tile, int n_tiles
     constexpr int TM = PAIR ? 2 * BM : BM;
     const int m_tiles = (a.Ma + TM - 1) / TM;
     const int per_e = m_tiles * n_tiles_n;
-    t.split = tile % a.k_splits;
-    tile /= a.k_splits;
-    t.e = tile / per_e;
-    const int rem = tile - t.e * per_e;
+    int part, n_parts, part_kb;   // this tile's contraction part, the parts of its expert, 64-row steps per part
+    if (a.tn_part_rows > 0) {
+      // ragged split: pp[e] = exclusive prefix of the experts' part counts (every expert has at least one part)
+      const int unit = tile / per_e;
+      tile -= unit * per_e;
+      int lo = 0, hi = a.E;
+      while (hi - lo > 1) {
+        const int mid = (lo + hi) >> 1;
+        if ((int)pp[mid] <= unit) lo = mid; else hi = mid;
+      }
+      t.e = lo;
+      part = unit - (int)pp[lo];
+      n_parts = (int)pp[lo + 1] - (int)pp[lo];
+      part_kb = a.tn_part_rows / BK;
+      // parts of multi-part experts live in `partial`; expert e's run of slots starts at 2 * (pp[e] - e), which is
+      // twice the number of extra parts before it and therefore never overlaps the next run
+      t.split = n_parts > 1 ? 2 * ((int)pp[lo] - lo) + part : -1;
+    } else {
+      part = tile % a.k_splits;
+      tile /= a.k_splits;
+      t.e = tile / per_e;
+      tile -= t.e * per_e;
+      n_parts = a.k_splits;
+      part_kb = 0;
+      t.split = a.k_splits > 1 ? part * a.E + t.e : -1;
+    }
+    const int rem = tile;
     t.m0 = (rem / n_tiles_n) * TM;
     const int nt = rem % n_tiles_n;
     if (a.out2 != nullptr) {  // two column halves, tiled separately so that no tile straddles them
@@ -215,9 +217,9 @@ __device__ __forceinline__ Tile decode_tile(const Args& a, int tile, int n_tiles
     }
     t.row0 = r0;
     const int kb_total = (int)((r1 - r0 + BK - 1) / BK);
-    const int per = (kb_total + a.k_splits - 1) / a.k_splits;
-    t.kb0 = t.split * per;
-    t.kb = max(0, min(per, kb_total - t.kb0));
+    if (part_kb == 0) part_kb = (kb_total + n_parts - 1) / n_parts;
+    t.kb0 = part * part_kb;
+    t.kb = max(0, min(part_kb, kb_total - t.kb0));
   } else {
     const int unit = tile / n_tiles_n;   // row block (one CTA) or pair of row blocks (CTA pair)
     const int nt = tile - unit * n_tiles_n;
@@ -286,26 +288,20 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + b); };
   auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * MAX_STAGES + 2 + b); };
   const uint32_t drain_bar = bar_base + 8u * (2 * MAX_STAGES + 4);
-  auto gfull_bar = [&](int s) { return bar_base + 176u + 8u * s; };   // peer CTA: its own gathered rows of stage s
   uint8_t* generic_base = smem_raw;
   volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(generic_base + DATA_BYTES + 160);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(generic_base + DATA_BYTES + 168);
   uint16_t* pair_prefix = reinterpret_cast<uint16_t*>(generic_base + DATA_BYTES + 256);
-  int* gather_rows = reinterpret_cast<int*>(generic_base + DATA_BYTES + 256 + PAIR_PREFIX_BYTES);   // [128] source rows
-  auto epi_bar = [&](int w) { return bar_base + 256u + PAIR_PREFIX_BYTES + GATHER_ROWS_BYTES + 8u * w; };
+  auto epi_bar = [&](int w) { return bar_base + 256u + PAIR_PREFIX_BYTES + 8u * w; };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t cta_rank = PAIR ? ptx::cluster_ctarank() : 0u;   // 0 = leader of the pair
   const bool leader = cta_rank == 0;
 
   if (threadIdx.x == 0) {
-    const bool gathering = a.ga_ptr != nullptr || a.gb_ptr != nullptr;
     for (int s = 0; s < STAGES; ++s) {
-      // one arrival posts the TMA byte count; gathering adds this CTA's 32 lanes and, in pair mode, one
-      // forwarded arrival for the peer's lanes
-      ptx::mbar_init(full_bar(s), 1 + (gathering ? 32 + (PAIR ? 1 : 0) : 0));
+      ptx::mbar_init(full_bar(s), 1);    // one arrival posts the TMA byte count
       ptx::mbar_init(empty_bar(s), 1);
-      ptx::mbar_init(gfull_bar(s), 32);
     }
     for (int b = 0; b < 2; ++b) {
       ptx::mbar_init(tfull_bar(b), 1);
@@ -319,13 +315,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     ptx::prefetch_tensormap(&tm_a);
     ptx::prefetch_tensormap(&tm_b);
     if constexpr (EPI == SWIGLU || MAJOR == NT) ptx::prefetch_tensormap(&tm_b2);
-    if constexpr (EPI == DSWIGLU) {
-      ptx::prefetch_tensormap(&tm_c);
-      ptx::prefetch_tensormap(&tm_d);
-    }
+    ptx::prefetch_tensormap(&tm_c);
+    ptx::prefetch_tensormap(&tm_d);
   }
   int n_units = 0;  // NN/NT: row blocks (or pairs of row blocks) to process
-  if constexpr (MAJOR != TN) {
+  if constexpr (MAJOR == TN) {
+    if (a.tn_part_rows > 0 && threadIdx.x == 32) {  // exclusive prefix of the experts' contraction-part counts
+      int run = 0;
+      for (int e = 0; e < a.E; ++e) {
+        pair_prefix[e] = (uint16_t)run;
+        const int rows_e = a.pad_offsets[e + 1] - a.pad_offsets[e];
+        run += max(1, (rows_e + a.tn_part_rows - 1) / a.tn_part_rows);
+      }
+      pair_prefix[a.E] = (uint16_t)min(run, 65535);
+    }
+  } else {
     if constexpr (PAIR) {
       if (a.pad_offsets != nullptr) {
         if (threadIdx.x == 32) {  // exclusive prefix of ceil(blocks_e / 2); a few hundred adds at most
@@ -360,7 +364,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
   if constexpr (MAJOR == TN) {
     constexpr int TM = PAIR ? 2 * BM : BM;
     n_tiles_n = a.out2 != nullptr ? 2 * ((a.N / 2 + BN - 1) / BN) : (a.N + BN - 1) / BN;
-    total_tiles = a.E * ((a.Ma + TM - 1) / TM) * n_tiles_n * a.k_splits;
+    const int per_e = ((a.Ma + TM - 1) / TM) * n_tiles_n;
+    total_tiles = a.tn_part_rows > 0 ? min((int)pair_prefix[a.E], a.n_blocks_host) * per_e : a.E * per_e * a.k_splits;
   } else {
     const int bn_out = (EPI == SWIGLU) ? BN / 2 : BN;
     n_tiles_n = (a.N + bn_out - 1) / bn_out;
@@ -381,94 +386,35 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
 
   if (warp == 0) {
     // ------------------------------------------------------------------ producer warp
-    // Lane 0 posts the byte count and issues the tiled TMA loads.  A gathered operand (its rows are picked
-    // through an index table instead of being materialised first) is copied by all 32 lanes with 16-byte
-    // cp.async into the same 128-byte-swizzled layout a tiled TMA load would have written: row j of a tile
-    // sits at j*128 bytes and its 16-byte piece c at ((c ^ (j & 7)) << 4).  Rows that do not exist
-    // (padding, rows past the group) are zero-filled.  Each lane then lets the hardware arrive on the
-    // stage's barrier when its copies have landed (cp.async.mbarrier.arrive.noinc), so nothing waits here.
-    const bool gather_a = a.ga_ptr != nullptr, gather_b = a.gb_ptr != nullptr;
-    const bool gathering = gather_a || gather_b;
-    const int src_rows = a.g_src_rows;
+    // Lane 0 posts the byte count of a stage and issues its tiled TMA loads.
     uint32_t it = 0;
     bool ok = true;
-    auto src_of = [&](int v) {
-      if (v < 0) return -1;
-      v /= a.g_div;
-      return v < src_rows ? v : -1;
-    };
-    const int piece = lane & 7, rsub = lane >> 3;
-    for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
-      const Tile t = decode_tile<MAJOR, EPI, PAIR>(a, tile, n_tiles_n, pair_prefix);
-      // TN: queue of the next stages' row indices (lanes 0-15 hold four consecutive k-rows each)
-      [[maybe_unused]] int4 q0 = make_int4(-1, -1, -1, -1), q1 = q0, q2 = q0, q3 = q0;
-      [[maybe_unused]] long long tn_r_end = 0;
-      auto tn_idx = [&](int kb) {
-        const long long r = (long long)t.row0 + (long long)(t.kb0 + kb) * BK + 4 * (lane & 15);
-        int4 v = make_int4(-1, -1, -1, -1);
-        if (lane < 16 && kb < t.kb) {
-          if (r + 3 < tn_r_end) {
-            v = *reinterpret_cast<const int4*>(a.g_idx + r);
-          } else {
-            if (r < tn_r_end) v.x = a.g_idx[r];
-            if (r + 1 < tn_r_end) v.y = a.g_idx[r + 1];
-            if (r + 2 < tn_r_end) v.z = a.g_idx[r + 2];
-          }
-        }
-        return v;
-      };
-      if (gathering) {
-        if constexpr (MAJOR != TN) {
-          // source rows of this CTA's 128 tile rows -> shared memory (lane writes rows 4*lane .. +3)
-          const long long r = (long long)t.row0 + (long long)cta_rank * BM + 4 * lane;
-          int4 v = make_int4(-1, -1, -1, -1);
-          if (r + 3 < a.rows) {
-            v = *reinterpret_cast<const int4*>(a.g_idx + r);
-          } else {
-            if (r < a.rows) v.x = a.g_idx[r];
-            if (r + 1 < a.rows) v.y = a.g_idx[r + 1];
-            if (r + 2 < a.rows) v.z = a.g_idx[r + 2];
-          }
-          __syncwarp();
-          *reinterpret_cast<int4*>(gather_rows + 4 * lane) = make_int4(src_of(v.x), src_of(v.y), src_of(v.z), src_of(v.w));
-          __syncwarp();
-        } else {
-          tn_r_end = a.pad_offsets != nullptr ? (long long)a.pad_offsets[t.e + 1] : a.rows;
-          q0 = tn_idx(0); q1 = tn_idx(1); q2 = tn_idx(2); q3 = tn_idx(3);
-        }
-      }
-      for (int kb = 0; kb < t.kb; ++kb, ++it) {
-        const int s = it % STAGES;
-        const uint32_t ph = (it / STAGES) & 1u;
-        bool got = true;
-        if (lane == 0 || gathering) got = ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
-        if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
-        const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
-        const bool skip_b = (a.dbg & 4) != 0;
-        const int nb0 = t.n0 + (PAIR ? (int)cta_rank * (BN / 2) : 0);   // first B column/row held by this CTA
-        if (lane == 0) {
-          const uint32_t cta_bytes = (gather_a ? 0 : A_BYTES) + ((skip_b || gather_b) ? 0 : Cfg<PAIR, EPI>::B_BYTES);
-          // in pair mode the peer gathers the same operands, so both CTAs bring the same TMA byte count
+    if (lane == 0) {
+      for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
+        const Tile t = decode_tile<MAJOR, EPI, PAIR>(a, tile, n_tiles_n, pair_prefix);
+        for (int kb = 0; kb < t.kb; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1u;
+          if (!ptx::mbar_wait(empty_bar(s), ph ^ 1u, abort_flag)) { ok = false; break; }
+          const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
+          const int nb0 = t.n0 + (PAIR ? (int)cta_rank * (BN / 2) : 0);   // first B column/row held by this CTA
+          constexpr uint32_t cta_bytes = A_BYTES + Cfg<PAIR, EPI>::B_BYTES;
+          // in pair mode both CTAs bring the same TMA byte count to the leader's barrier
           if (leader) ptx::mbar_expect_tx(full_bar(s), PAIR ? 2 * cta_bytes : cta_bytes);
           const uint32_t fb = full_target(s);
           auto load2 = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1) {
             if constexpr (PAIR) ptx::tma_load_2d_pair(dst, tm, fb, c0, c1); else ptx::tma_load_2d(dst, tm, fb, c0, c1);
           };
           auto load3 = [&](uint32_t dst, const CUtensorMap* tm, int c0, int c1, int c2) {
-            if (skip_b) return;   // every 3-D load is a B-operand load
             if constexpr (PAIR) ptx::tma_load_3d_pair(dst, tm, fb, c0, c1, c2); else ptx::tma_load_3d(dst, tm, fb, c0, c1, c2);
           };
           if constexpr (MAJOR == TN) {
             const int r = t.row0 + (t.kb0 + kb) * BK;
             const int ma0 = t.m0 + (int)cta_rank * BM;
-            if (!gather_a) {
 #pragma unroll
-              for (int c = 0; c < 2; ++c) load2(sa + c * CHUNK_BYTES, &tm_a, ma0 + 64 * c, r);
-            }
-            if (!gather_b && !skip_b) {
+            for (int c = 0; c < 2; ++c) load2(sa + c * CHUNK_BYTES, &tm_a, ma0 + 64 * c, r);
 #pragma unroll
-              for (int c = 0; c < B_CHUNKS; ++c) load2(sb + c * CHUNK_BYTES, &tm_b, nb0 + 64 * c, r);
-            }
+            for (int c = 0; c < B_CHUNKS; ++c) load2(sb + c * CHUNK_BYTES, &tm_b, nb0 + 64 * c, r);
           } else {
             int ka = kb * BK;
             if constexpr (MAJOR == NN) {
@@ -476,7 +422,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             } else {
               if (kb >= a.kb_split) ka = a.k2_offset + (kb - a.kb_split) * BK;
             }
-            if (!gather_a) load2(sa, &tm_a, ka, t.row0 + (int)cta_rank * BM);
+            load2(sa, &tm_a, ka, t.row0 + (int)cta_rank * BM);
             if constexpr (MAJOR == NN) {
               if constexpr (EPI == SWIGLU) {
                 if constexpr (PAIR) {  // the leader's half of B is the gate tile, the peer's half the up tile
@@ -499,78 +445,21 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             }
           }
         }
-        if (gathering) {
-          if constexpr (MAJOR != TN) {
-            // A tile [128 rows][64 k]
-            const int col = kb * BK + piece * 8;
-            const bool col_ok = col < a.K;
-            const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(a.ga_ptr);
-#pragma unroll 8
-            for (int i = 0; i < 32; ++i) {
-              const int j = i * 4 + rsub;
-              const int sr = gather_rows[j];
-              const bool v = sr >= 0 && col_ok;
-              const __nv_bfloat16* src = v ? base + (long long)sr * a.ga_ld + col : base;
-              ptx::cp_async16(sa + j * 128 + ((piece ^ (j & 7)) << 4), src, v);
-            }
-          } else {
-            // MN-major chunks [64 k-rows][64 columns]: k-row j of the stage is padded row r0 + j
-            __syncwarp();
-            if (lane < 16) *reinterpret_cast<int4*>(gather_rows + 4 * lane) = make_int4(src_of(q0.x), src_of(q0.y), src_of(q0.z), src_of(q0.w));
-            q0 = q1; q1 = q2; q2 = q3; q3 = tn_idx(kb + 4);
-            __syncwarp();
-            auto gather_chunks = [&](uint32_t dst0, int n_chunks, const void* ptr, long long ld, int col0, int width) {
-              const __nv_bfloat16* base = reinterpret_cast<const __nv_bfloat16*>(ptr);
-              for (int c = 0; c < n_chunks; ++c) {
-                const int col = col0 + 64 * c + piece * 8;
-                const bool col_ok = col < width;
-#pragma unroll 8
-                for (int i = 0; i < 16; ++i) {
-                  const int j = i * 4 + rsub;
-                  const int sr = gather_rows[j];
-                  const bool v = sr >= 0 && col_ok;
-                  const __nv_bfloat16* src = v ? base + (long long)sr * ld + col : base;
-                  ptx::cp_async16(dst0 + c * CHUNK_BYTES + j * 128 + ((piece ^ (j & 7)) << 4), src, v);
-                }
-              }
-            };
-            if (gather_a) gather_chunks(sa, 2, a.ga_ptr, a.ga_ld, t.m0 + (int)cta_rank * BM, a.Ma);
-            if (gather_b && !skip_b) gather_chunks(sb, B_CHUNKS, a.gb_ptr, a.gb_ld, nb0, a.N);
+      }
+      if (*abort_flag && leader) {
+        // give the copies already issued a bounded chance to land before shared memory is released
+        const uint32_t first = it > STAGES ? it - STAGES : 0;
+        for (uint32_t j = first; j < it; ++j) {
+          const unsigned long long t0 = ptx::globaltimer_ns();
+          while (!ptx::mbar_try_wait(full_bar(j % STAGES), (j / STAGES) & 1u)) {
+            if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
           }
-          // the hardware arrives for this lane once its copies above have landed
-          ptx::cp_async_arrive_noinc((PAIR && !leader) ? gfull_bar(s) : full_bar(s));
         }
       }
     }
-    if (gathering) ptx::cp_async_wait<0>();   // nothing of this warp is in flight when shared memory is released
-    if (lane == 0 && *abort_flag && leader) {
-      // give the copies already issued a bounded chance to land before shared memory is released
-      const uint32_t first = it > STAGES ? it - STAGES : 0;
-      for (uint32_t j = first; j < it; ++j) {
-        const unsigned long long t0 = ptx::globaltimer_ns();
-        while (!ptx::mbar_try_wait(full_bar(j % STAGES), (j / STAGES) & 1u)) {
-          if (ptx::globaltimer_ns() - t0 > 2000000ull) break;
-        }
-      }
-    }
+    __syncwarp();
   } else if (warp == 1) {
     // ------------------------------------------------------------------ MMA issuer (leader CTA only in pair mode)
-    const bool gathering = a.ga_ptr != nullptr || a.gb_ptr != nullptr;
-    if (PAIR && lane == 0 && !leader && gathering) {
-      // Peer CTA: its gathered rows are announced on its own barrier (cp.async can only arrive locally);
-      // this otherwise idle thread forwards each completed stage to the leader's full barrier.
-      uint32_t it = 0;
-      bool ok = true;
-      for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
-        const Tile t = decode_tile<MAJOR, EPI, PAIR>(a, tile, n_tiles_n, pair_prefix);
-        for (int kb = 0; kb < t.kb; ++kb, ++it) {
-          const int s = it % STAGES;
-          if (!ptx::mbar_wait(gfull_bar(s), (it / STAGES) & 1u, abort_flag)) { ok = false; break; }
-          ptx::fence_proxy_async();
-          ptx::mbar_arrive_cluster(ptx::map_to_cta(full_bar(s), 0));
-        }
-      }
-    }
     if (lane == 0 && leader) {
       uint32_t it = 0, acc_it = 0;
       bool ok = true;
@@ -585,7 +474,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           const int s = it % STAGES;
           const uint32_t ph = (it / STAGES) & 1u;
           if (!ptx::mbar_wait(full_bar(s), ph, abort_flag)) { ok = false; break; }
-          if (gathering) ptx::fence_proxy_async();   // cp.async wrote through the generic proxy, the MMA reads through the async one
           ptx::tc_fence_after();
           const uint32_t sa = smem_base + s * STAGE_BYTES, sb = sa + A_BYTES;
 #pragma unroll
@@ -620,6 +508,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
     uint8_t* stage = generic_base + RING_BYTES + (warp - 2) * staging_per_warp(EPI);
     uint32_t acc_it = 0;
     [[maybe_unused]] uint32_t epi_phase = 0;
+    [[maybe_unused]] TileStager<2> out2buf{stage, 0};
     bool ok = true;
     for (int tile = tile_first; ok && tile < total_tiles; tile += tile_step) {
       const Tile t = decode_tile<MAJOR, EPI, PAIR>(a, tile, n_tiles_n, pair_prefix);
@@ -629,17 +518,16 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const long long row_lim = MAJOR == TN ? (long long)a.Ma : a.rows;
       int rows_valid = (int)max(0LL, min(32LL, row_lim - wrow0));
       if (MAJOR != TN && cta_rank == 1 && !t.second) rows_valid = 0;   // this CTA's block belongs to the next expert
-      if (a.dbg & 3) rows_valid = 0;
-      const int n_end = (a.dbg & 2) ? 0 : t.nlim;
+      const int n_end = t.nlim;
 
       // DSWIGLU: this warp's 32 rows x 128 columns of g and u arrive, and dg and du leave, as TMA tiles of 32 rows x
-      // 64 columns (128-byte swizzle) in the warp's 8 KB of staging: [g tile | u tile], results written in place.
+      // 64 columns in the warp's two staging tiles: [g tile | u tile], results written in place.
       // Lane 0 issues the copies; the first pair of loads is in flight before the accumulator is waited for.
-      [[maybe_unused]] const uint32_t tile_g = ptx::smem_u32(stage), tile_u = tile_g + 4096;
+      [[maybe_unused]] const uint32_t tile_g = ptx::smem_u32(stage), tile_u = tile_g + TILE_BYTES;
       [[maybe_unused]] auto dsw_load = [&](int n) {
         if (lane == 0) {
           ptx::bulk_wait_read();   // the stores of the previous half have finished reading the staging tiles
-          ptx::mbar_expect_tx(epi_bar(warp - 2), 8192);
+          ptx::mbar_expect_tx(epi_bar(warp - 2), 2 * TILE_BYTES);
           ptx::tma_load_3d(tile_g, &tm_c, epi_bar(warp - 2), n, 0, (int)wrow0);
           ptx::tma_load_3d(tile_u, &tm_c, epi_bar(warp - 2), n, 1, (int)wrow0);
         }
@@ -660,63 +548,98 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       const uint32_t t_addr = tmem_base + acc * BN + ((uint32_t)(lane_grp * 32) << 16);
 
       if constexpr (EPI == PLAIN) {
-        const long long grow = wrow0 + lane;
-        const float sc = (a.row_scale != nullptr && lane < rows_valid) ? a.row_scale[grow] : 1.0f;
+        // out [rows, N] through tm_c: bf16 tiles of 64 columns or f32 tiles of 32 columns
+        if (rows_valid > 0) {
+          const long long grow = wrow0 + lane;
+          const bool live = lane < rows_valid;
+          const float sc = (a.row_scale != nullptr && live) ? a.row_scale[grow] : 1.0f;
+          const float r1 = (a.r1_row != nullptr && live) ? a.r1_row[grow] : 0.f;
+          uint8_t* buf = nullptr;
 #pragma unroll 1
-        for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
-          const int n = t.n0 + c * 32;
-          if (n >= n_end) break;  // uniform across the warp
-          const int cv = min(32, a.N - n);
-          uint32_t r[32];
-          float v[32];
-          if (has_acc) {
-            ptx::tmem_ld_32x32(t_addr + c * 32, r);
-            ptx::tmem_ld_wait();
-          }
+          for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
+            const int n = t.n0 + c * 32;
+            if (n >= n_end) break;  // uniform across the warp
+            const int cv = min(32, a.N - n);
+            uint32_t r[32];
+            float v[32];
+            if (has_acc) {
+              ptx::tmem_ld_32x32(t_addr + c * 32, r);
+              ptx::tmem_ld_wait();
+            }
 #pragma unroll
-          for (int q = 0; q < 32; ++q) v[q] = has_acc ? __uint_as_float(r[q]) * sc : 0.f;
-          if (a.col_bias != nullptr) {
+            for (int q = 0; q < 32; ++q) v[q] = has_acc ? __uint_as_float(r[q]) * sc : 0.f;
+            if (a.col_bias != nullptr) {
 #pragma unroll
-            for (int q = 0; q < 32; ++q) v[q] += (q < cv) ? a.col_bias[n + q] : 0.f;
+              for (int q = 0; q < 32; ++q) v[q] += (q < cv) ? a.col_bias[n + q] : 0.f;
+            }
+            if (a.r1_row != nullptr) {
+#pragma unroll
+              for (int q = 0; q < 32; ++q) v[q] += (q < cv) ? r1 * a.r1_col[n + q] : 0.f;
+            }
+            if (a.out_f32) {
+              buf = out2buf.acquire(lane);
+              tile_put_f32x32(buf, lane, v);
+              out2buf.store2d(lane, &tm_c, buf, n, (int)wrow0);
+            } else {
+              if ((c & 1) == 0) buf = out2buf.acquire(lane);
+              tile_put_bf16x32(buf, lane, (c & 1) * 4, v);
+              // a 64-column tile is complete after its odd 32-column block, or when the row ends inside it
+              if ((c & 1) == 1 || n + 32 >= n_end) out2buf.store2d(lane, &tm_c, buf, n - (c & 1) * 32, (int)wrow0);
+            }
           }
-          if (a.out_f32) warp_store32_f32(stage, lane, v, reinterpret_cast<float*>(a.out) + wrow0 * a.N + n, a.N, rows_valid, cv);
-          else warp_store32_bf16(stage, lane, v, reinterpret_cast<__nv_bfloat16*>(a.out) + wrow0 * a.N + n, a.N, rows_valid, cv);
         }
       } else if constexpr (EPI == SWIGLU) {
+        // h [rows, f] through tm_c, gu [rows][2][f] through tm_d; this warp owns 64 h columns: three 4 KB tiles
         const int f = a.N;
-        float hsc = 1.0f;
-        if (a.scale_src != nullptr) {
-          hsc = 0.f;
-          if (lane < rows_valid) {
-            const long long gi = a.scale_idx != nullptr ? (long long)a.scale_idx[wrow0 + lane] : wrow0 + lane;
-            if (gi >= 0) hsc = a.scale_src[gi];
+        const int n64 = t.n0 + col_half * 64;
+        if (rows_valid > 0 && n64 < n_end) {
+          float hsc = 1.0f;
+          if (a.scale_src != nullptr) {
+            hsc = 0.f;
+            if (lane < rows_valid) {
+              const long long gi = a.scale_idx != nullptr ? (long long)a.scale_idx[wrow0 + lane] : wrow0 + lane;
+              if (gi >= 0) hsc = a.scale_src[gi];
+            }
           }
-        }
+          if (lane == 0) ptx::bulk_wait_read();   // the previous tile's three stores have read the staging tiles
+          __syncwarp();
+          uint8_t* buf_g = stage;
+          uint8_t* buf_u = stage + TILE_BYTES;
+          uint8_t* buf_h = stage + 2 * TILE_BYTES;
 #pragma unroll 1
-        for (int c = col_half * 2; c < col_half * 2 + 2; ++c) {
-          const int n = t.n0 + c * 32;
-          if (n >= n_end) break;
-          const int cv = min(32, f - n);
-          uint32_t rg[32], ru[32];
-          if (has_acc) {
-            ptx::tmem_ld_32x32(t_addr + c * 32, rg);
-            ptx::tmem_ld_32x32(t_addr + BN / 2 + c * 32, ru);
-            ptx::tmem_ld_wait();
-          }
-          float g[32], u[32];
+          for (int b = 0; b < 2; ++b) {
+            const int c = col_half * 2 + b;
+            if (t.n0 + c * 32 >= n_end) break;
+            uint32_t rg[32], ru[32];
+            if (has_acc) {
+              ptx::tmem_ld_32x32(t_addr + c * 32, rg);
+              ptx::tmem_ld_32x32(t_addr + BN / 2 + c * 32, ru);
+              ptx::tmem_ld_wait();
+            }
+            float g[32], u[32];
 #pragma unroll
-          for (int q = 0; q < 32; ++q) {
-            g[q] = has_acc ? __uint_as_float(rg[q]) : 0.f;
-            u[q] = has_acc ? __uint_as_float(ru[q]) : 0.f;
-          }
-          if (a.out2 != nullptr) {
-            __nv_bfloat16* gu = reinterpret_cast<__nv_bfloat16*>(a.out2) + wrow0 * (2LL * f);
-            warp_store32_bf16(stage, lane, g, gu + n, 2LL * f, rows_valid, cv);
-            warp_store32_bf16(stage, lane, u, gu + f + n, 2LL * f, rows_valid, cv);
-          }
+            for (int q = 0; q < 32; ++q) {
+              g[q] = has_acc ? __uint_as_float(rg[q]) : 0.f;
+              u[q] = has_acc ? __uint_as_float(ru[q]) : 0.f;
+            }
+            if (a.out2 != nullptr) {
+              tile_put_bf16x32(buf_g, lane, b * 4, g);
+              tile_put_bf16x32(buf_u, lane, b * 4, u);
+            }
 #pragma unroll
-          for (int q = 0; q < 32; ++q) g[q] = g[q] * fast_sigmoid(g[q]) * u[q] * hsc;
-          warp_store32_bf16(stage, lane, g, reinterpret_cast<__nv_bfloat16*>(a.out) + wrow0 * f + n, f, rows_valid, cv);
+            for (int q = 0; q < 32; ++q) g[q] = g[q] * fast_sigmoid(g[q]) * u[q] * hsc;
+            tile_put_bf16x32(buf_h, lane, b * 4, g);
+          }
+          ptx::fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) {
+            if (a.out2 != nullptr) {
+              ptx::tma_store_3d(&tm_d, ptx::smem_u32(buf_g), n64, 0, (int)wrow0);
+              ptx::tma_store_3d(&tm_d, ptx::smem_u32(buf_u), n64, 1, (int)wrow0);
+            }
+            ptx::tma_store_2d(&tm_c, ptx::smem_u32(buf_h), n64, (int)wrow0);
+            ptx::bulk_commit();
+          }
         }
       } else if constexpr (EPI == DSWIGLU) {
         const int f = a.N;
@@ -746,7 +669,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             for (int q = 0; q < 4; ++q) {
               const int off = ((b * 4 + q) ^ (lane & 7)) << 4;
               const uint4 pg = *reinterpret_cast<const uint4*>(my_g + off);
-              const uint4 pu = *reinterpret_cast<const uint4*>(my_g + 4096 + off);
+              const uint4 pu = *reinterpret_cast<const uint4*>(my_g + TILE_BYTES + off);
               g[q * 8 + 0] = bf16_lo(pg.x); g[q * 8 + 1] = bf16_hi(pg.x); g[q * 8 + 2] = bf16_lo(pg.y); g[q * 8 + 3] = bf16_hi(pg.y);
               g[q * 8 + 4] = bf16_lo(pg.z); g[q * 8 + 5] = bf16_hi(pg.z); g[q * 8 + 6] = bf16_lo(pg.w); g[q * 8 + 7] = bf16_hi(pg.w);
               u[q * 8 + 0] = bf16_lo(pu.x); u[q * 8 + 1] = bf16_hi(pu.x); u[q * 8 + 2] = bf16_lo(pu.y); u[q * 8 + 3] = bf16_hi(pu.y);
@@ -767,16 +690,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
               g[q] = dh * u[q] * sg * (1.0f + g[q] * (1.0f - sg));
               u[q] = du;
             }
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const int off = ((b * 4 + q) ^ (lane & 7)) << 4;
-              *reinterpret_cast<uint4*>(my_g + off) =
-                  make_uint4(pack_bf16(g[q * 8 + 0], g[q * 8 + 1]), pack_bf16(g[q * 8 + 2], g[q * 8 + 3]),
-                             pack_bf16(g[q * 8 + 4], g[q * 8 + 5]), pack_bf16(g[q * 8 + 6], g[q * 8 + 7]));
-              *reinterpret_cast<uint4*>(my_g + 4096 + off) =
-                  make_uint4(pack_bf16(u[q * 8 + 0], u[q * 8 + 1]), pack_bf16(u[q * 8 + 2], u[q * 8 + 3]),
-                             pack_bf16(u[q * 8 + 4], u[q * 8 + 5]), pack_bf16(u[q * 8 + 6], u[q * 8 + 7]));
-            }
+            tile_put_bf16x32(stage, lane, b * 4, g);
+            tile_put_bf16x32(stage + TILE_BYTES, lane, b * 4, u);
           }
           ptx::fence_proxy_async();   // the tiles were written through the generic proxy, the store reads them through the async one
           __syncwarp();
@@ -791,28 +706,37 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
           if (part < a.dw_parts) a.dw_partial[(wrow0 + lane) * a.dw_parts + part] = dw_acc;
         }
       } else {  // TNOUT
-        const int half = a.out2 != nullptr ? a.N / 2 : a.N;
+        // straight to the output ([E, Ma, N] through tm_c, or its two column halves through tm_c / tm_d), or one part
+        // of an expert's product as f32 into `partial` ([slots, Ma, N] through tm_b2)
+        if (rows_valid > 0) {
+          const int half = a.out2 != nullptr ? a.N / 2 : a.N;
+          const bool to_partial = t.split >= 0;
+          const bool f32_out = to_partial || a.out_f32;
+          uint8_t* buf = nullptr;
 #pragma unroll 1
-        for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
-          const int n = t.n0 + c * 32;
-          if (n >= n_end) break;
-          const int cv = min(32, t.nlim - n);
-          uint32_t r[32];
-          float v[32];
-          if (has_acc) {
-            ptx::tmem_ld_32x32(t_addr + c * 32, r);
-            ptx::tmem_ld_wait();
-          }
+          for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
+            const int n = t.n0 + c * 32;
+            if (n >= n_end) break;
+            uint32_t r[32];
+            float v[32];
+            if (has_acc) {
+              ptx::tmem_ld_32x32(t_addr + c * 32, r);
+              ptx::tmem_ld_wait();
+            }
 #pragma unroll
-          for (int q = 0; q < 32; ++q) v[q] = has_acc ? __uint_as_float(r[q]) : 0.f;
-          if (a.k_splits > 1) {
-            float* dst = a.partial + (((long long)t.split * a.E + t.e) * a.Ma + wrow0) * a.N + n;
-            warp_store32_f32(stage, lane, v, dst, a.N, rows_valid, cv);
-          } else {
-            void* base = (n < half) ? a.out : a.out2;
-            const long long off = ((long long)t.e * a.Ma + wrow0) * half + (n < half ? n : n - half);
-            if (a.out_f32) warp_store32_f32(stage, lane, v, reinterpret_cast<float*>(base) + off, half, rows_valid, cv);
-            else warp_store32_bf16(stage, lane, v, reinterpret_cast<__nv_bfloat16*>(base) + off, half, rows_valid, cv);
+            for (int q = 0; q < 32; ++q) v[q] = has_acc ? __uint_as_float(r[q]) : 0.f;
+            const CUtensorMap* tm = to_partial ? &tm_b2 : (n < half ? &tm_c : &tm_d);
+            const int z = to_partial ? t.split : t.e;
+            const int ncol = to_partial ? n : (n < half ? n : n - half);
+            if (f32_out) {
+              buf = out2buf.acquire(lane);
+              tile_put_f32x32(buf, lane, v);
+              out2buf.store3d(lane, tm, buf, ncol, (int)wrow0, z);
+            } else {
+              if ((c & 1) == 0) buf = out2buf.acquire(lane);
+              tile_put_bf16x32(buf, lane, (c & 1) * 4, v);
+              if ((c & 1) == 1 || n + 32 >= n_end) out2buf.store3d(lane, tm, buf, ncol - (c & 1) * 32, (int)wrow0, z);
+            }
           }
         }
       }
@@ -827,9 +751,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         ++acc_it;
       }
     }
-    if constexpr (EPI == DSWIGLU) {
-      if (lane == 0) ptx::bulk_wait_all();   // this warp's last tile stores are complete before the CTA can exit
-    }
+    if (lane == 0) ptx::bulk_wait_all();   // this warp's last tile stores are complete before the CTA can exit
   }
 
   ptx::tc_fence_before();
@@ -869,6 +791,50 @@ __global__ void __launch_bounds__(256) tn_reduce_kernel(const float* __restrict_
   }
 }
 
+// Ragged split (tn_part_rows > 0): sums the parts of every expert that has more than one, in part order, and writes
+// the expert's product in the output dtype.  grid = (column chunks, E); experts with one part were stored directly.
+__global__ void __launch_bounds__(256) tn_reduce_ragged_kernel(const float* __restrict__ partial,
+                                                               const int32_t* __restrict__ pad_offsets, int E,
+                                                               int part_rows, long long ma, int N, void* out, void* out2,
+                                                               int out_f32) {
+  __shared__ int s_base;
+  const int e = blockIdx.y;
+  const int rows_e = pad_offsets[e + 1] - pad_offsets[e];
+  const int n_parts = (rows_e + part_rows - 1) / part_rows;
+  if (n_parts <= 1) return;
+  if (threadIdx.x == 0) {
+    int extra = 0;   // parts beyond the first of all experts before e
+    for (int x = 0; x < e; ++x) {
+      const int r = pad_offsets[x + 1] - pad_offsets[x];
+      extra += max(1, (r + part_rows - 1) / part_rows) - 1;
+    }
+    s_base = 2 * extra;
+  }
+  __syncthreads();
+  const long long per = ma * N;               // elements of one expert's product
+  const long long total4 = per / 4;
+  const float4* src = reinterpret_cast<const float4*>(partial) + (long long)s_base * total4;
+  const int half = out2 != nullptr ? N / 2 : N;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4; i += (long long)gridDim.x * blockDim.x) {
+    float4 acc = src[i];
+    for (int p = 1; p < n_parts; ++p) {
+      const float4 v = src[i + (long long)p * total4];
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    const long long flat = i * 4;
+    const long long r = flat / N;
+    const int n = (int)(flat - r * N);
+    void* base = n < half ? out : out2;
+    const long long off = ((long long)e * ma + r) * half + (n < half ? n : n - half);
+    if (out_f32) {
+      *reinterpret_cast<float4*>(reinterpret_cast<float*>(base) + off) = acc;
+    } else {
+      *reinterpret_cast<uint2*>(reinterpret_cast<__nv_bfloat16*>(base) + off) =
+          make_uint2(pack_bf16(acc.x, acc.y), pack_bf16(acc.z, acc.w));
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -889,31 +855,34 @@ inline EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// bf16 tensor [d2][d1][d0] (d0 contiguous); box [b2][b1][b0]; rank 2 when d2 == 0.
+// bf16 (or f32) tensor [d2][d1][d0] (d0 contiguous); box [b2][b1][b0]; rank 2 when d2 == 0.
 inline bool make_map(CUtensorMap* m, const void* ptr, uint64_t d0, uint64_t d1, uint64_t d2, uint32_t b0,
-                     uint32_t b1, uint32_t b2 = 1) {
+                     uint32_t b1, uint32_t b2 = 1, bool f32 = false) {
   EncodeTiledFn fn = encode_fn();
   if (fn == nullptr || d0 == 0 || d1 == 0) return false;
+  const uint64_t esz = f32 ? 4 : 2;
   cuuint64_t dims[3] = {d0, d1, d2 ? d2 : 1};
-  cuuint64_t strides[2] = {d0 * 2, d0 * d1 * 2};
+  cuuint64_t strides[2] = {d0 * esz, d0 * d1 * esz};
   cuuint32_t box[3] = {b0, b1, b2};
   cuuint32_t estr[3] = {1, 1, 1};
   const cuuint32_t rank = d2 ? 3 : 2;
-  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank, const_cast<void*>(ptr), dims, strides, box, estr,
+  CUresult r = fn(m, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, rank,
+                  const_cast<void*>(ptr), dims, strides, box, estr,
                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
 
-// Descriptor geometry (bytes).  Overridable for bring-up through lewi_debug_set_desc().
-struct DescGeometry {
-  uint32_t k_lbo = 16, k_sbo = 1024, k_step = 32;          // K-major operand, 128-byte swizzle
-  uint32_t mn_lbo = CHUNK_BYTES, mn_sbo = 1024, mn_step = 2048;  // MN-major operand
-};
-inline DescGeometry& desc_geometry() {
-  static DescGeometry g;
-  return g;
+// Tensor map of an epilogue output [d2][rows][cols]: boxes of 32 rows x 128 bytes (64 bf16 or 32 f32 columns).
+inline bool make_out_map(CUtensorMap* m, const void* ptr, uint64_t cols, uint64_t rows, uint64_t d2, bool f32) {
+  return make_map(m, ptr, cols, rows, d2, f32 ? 32 : 64, 32, 1, f32);
 }
+
+// Shared-memory matrix-descriptor geometry (bytes) of the two operand layouts, both 128-byte swizzled.
+struct DescGeometry {
+  uint32_t k_lbo = 16, k_sbo = 1024, k_step = 32;          // K-major operand: rows of 128 bytes, 8-row groups 1 KB apart
+  uint32_t mn_lbo = CHUNK_BYTES, mn_sbo = 1024, mn_step = 2048;  // MN-major operand: [64 k][64 mn] boxes 8 KB apart
+};
 
 // Whether the CTA-pair (cta_group::2) kernels are used where the arguments allow it.
 inline bool& pair_mode() {
@@ -944,7 +913,7 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
     }
     attr_set[dev] = true;
   }
-  const DescGeometry& g = desc_geometry();
+  const DescGeometry g;
   const bool a_mn = MAJOR == TN, b_mn = MAJOR != NT;
   a.desc_hi_a = a_mn ? ptx::smem_desc_hi_sw128(g.mn_lbo, g.mn_sbo) : ptx::smem_desc_hi_sw128(g.k_lbo, g.k_sbo);
   a.desc_hi_b = b_mn ? ptx::smem_desc_hi_sw128(g.mn_lbo, g.mn_sbo) : ptx::smem_desc_hi_sw128(g.k_lbo, g.k_sbo);
@@ -983,7 +952,7 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
 
 // Picks the CTA-pair kernel when enabled, else the single-CTA one.
 template <int MAJOR, int EPI>
-// tc / td: tensor maps of the epilogue's own tiled input and output (dSwiGLU: g|u and dg|du); unused otherwise.
+// tc / td: tensor maps of the epilogue's tiled outputs (dSwiGLU: its g|u input and dg|du output).
 inline int launch_auto(bool pair, cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2,
                        const Args& a, long long max_tiles, const CUtensorMap* tc = nullptr,
                        const CUtensorMap* td = nullptr) {

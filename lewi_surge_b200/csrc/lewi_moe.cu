@@ -3,6 +3,7 @@
 #include "ep.cuh"
 #include "gather.cuh"
 #include "grouped_gemm.cuh"
+#include "moe_layer.cuh"
 #include "router_gemm.cuh"
 #include "routing.cuh"
 
@@ -71,13 +72,15 @@ int64_t lewi_route_workspace_bytes(int64_t num_slots, int num_experts) {
 int lewi_router_topk(void* stream, const float* logits, int64_t T, int E, int k, int block, int32_t* topk_idx,
                      float* topk_w, int32_t* counts, int32_t* offsets, int32_t* pad_offsets,
                      int32_t* block_expert, int32_t* n_blocks, int32_t* order, int32_t* pos, int32_t* pad_pos,
-                     int32_t* row_slot, float* probs_sum, void* workspace, int64_t workspace_bytes) {
+                     int32_t* row_slot, float* probs_sum, float* aux_loss, void* workspace,
+                     int64_t workspace_bytes) {
   if (!logits || !topk_idx || !topk_w || T < 0 || E <= 0 || k <= 0) return LEWI_ERR_ARG;
   if (k > E || k > kMaxTopK) return LEWI_ERR_LIMIT;
   if (block > 0 && (!pad_offsets || !block_expert || !n_blocks)) return LEWI_ERR_ARG;
+  if (aux_loss != nullptr && probs_sum == nullptr) return LEWI_ERR_ARG;
   return route_common(as_stream(stream), logits, nullptr, T, T * k, E, k, block, topk_idx, topk_w, counts, offsets,
                       pad_offsets, block_expert, n_blocks, order, pos, pad_pos, row_slot, probs_sum, workspace,
-                      workspace_bytes);
+                      workspace_bytes, aux_loss);
 }
 
 int64_t lewi_router_topk_static_max_bytes(void) { return LEWI_STATIC_SCRATCH_BYTES; }
@@ -128,26 +131,58 @@ int lewi_sort_indices(void* stream, const int32_t* flat_experts, int64_t M, int 
 
 int lewi_router_topk_bwd(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
                          float* dlogits, void* dlogits_bf16, int64_t T, int E, int k) {
-  return lewi_router_topk_bwd_partial(stream, logits, topk_idx, dw, nullptr, 0, nullptr, nullptr, dlogits, dlogits_bf16,
-                                      T, E, k);
+  return lewi_router_topk_bwd_full(stream, logits, topk_idx, dw, nullptr, 0, nullptr, nullptr, dlogits, dlogits_bf16, T, E,
+                                   k, nullptr, 0.f, nullptr, nullptr, 0);
 }
 
 int lewi_router_topk_bwd_partial(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
                                  const float* dw_partial, int dw_parts, const int32_t* pad_pos, float* dw_out,
                                  float* dlogits, void* dlogits_bf16, int64_t T, int E, int k) {
+  return lewi_router_topk_bwd_full(stream, logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits,
+                                   dlogits_bf16, T, E, k, nullptr, 0.f, nullptr, nullptr, 0);
+}
+
+int64_t lewi_router_bias_grad_workspace_bytes(int64_t T, int E) {
+  if (T < 0 || E <= 0) return LEWI_ERR_ARG;
+  return ((int64_t)gather_grid(T > 0 ? T : 1) * E * 4 + 255) / 256 * 256;
+}
+
+int lewi_router_topk_bwd_full(void* stream, const float* logits, const int32_t* topk_idx, const float* dw,
+                              const float* dw_partial, int dw_parts, const int32_t* pad_pos, float* dw_out,
+                              float* dlogits, void* dlogits_bf16, int64_t T, int E, int k, const int32_t* counts,
+                              float aux_grad, float* d_bias, void* workspace, int64_t workspace_bytes) {
   if (!logits || !topk_idx || (!dw && !dw_partial) || (!dlogits && !dlogits_bf16) || T < 0 || E <= 0 || k <= 0)
     return LEWI_ERR_ARG;
   if (dw_partial != nullptr && (dw_parts <= 0 || pad_pos == nullptr)) return LEWI_ERR_ARG;
   __nv_bfloat16* dlb = reinterpret_cast<__nv_bfloat16*>(dlogits_bf16);
   if (E > kMaxExperts || k > kMaxTopK || k > E) return LEWI_ERR_LIMIT;
-  if (T == 0) return LEWI_OK;
-  const int grid = gather_grid(T);
   cudaStream_t st = as_stream(stream);
-  if (E <= 64) router_topk_bwd_kernel<2><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, dlb, T, E, k);
-  else if (E <= 128) router_topk_bwd_kernel<4><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, dlb, T, E, k);
-  else if (E <= 256) router_topk_bwd_kernel<8><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, dlb, T, E, k);
-  else router_topk_bwd_kernel<16><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, dlb, T, E, k);
+  if (T == 0) {
+    if (d_bias != nullptr && cudaMemsetAsync(d_bias, 0, (size_t)E * 4, st) != cudaSuccess) return LEWI_ERR_CUDA;
+    return LEWI_OK;
+  }
+  const int grid = gather_grid(T);
+  float* bias_partial = nullptr;
+  if (d_bias != nullptr) {
+    if (workspace == nullptr || workspace_bytes < (int64_t)grid * E * 4) return LEWI_ERR_WORKSPACE;
+    bias_partial = reinterpret_cast<float*>(workspace);
+  }
+  // load-balance loss E * sum_e (counts_e / M)(probs_sum_e / T): d/dp[t,e] = E * counts_e / (M * T), times aux_grad
+  const float aux_coef = counts != nullptr ? aux_grad * (float)E / ((float)(T * k) * (float)T) : 0.f;
+  const int32_t* cnt = (counts != nullptr && aux_grad != 0.f) ? counts : nullptr;
+#define LEWI_RTB(ER)                                                                                                  \
+  router_topk_bwd_kernel<ER><<<grid, 256, 0, st>>>(logits, topk_idx, dw, dw_partial, dw_parts, pad_pos, dw_out, dlogits, \
+                                                   dlb, T, E, k, cnt, aux_coef, bias_partial)
+  if (E <= 64) LEWI_RTB(2);
+  else if (E <= 128) LEWI_RTB(4);
+  else if (E <= 256) LEWI_RTB(8);
+  else LEWI_RTB(16);
+#undef LEWI_RTB
   LEWI_CHECK_LAUNCH();
+  if (d_bias != nullptr) {
+    col_sum_reduce_kernel<<<E, 256, 0, st>>>(bias_partial, grid, E, d_bias);
+    LEWI_CHECK_LAUNCH();
+  }
   return LEWI_OK;
 }
 
@@ -260,8 +295,6 @@ int lewi_gather_dot(void* stream, const void* y, const int32_t* pos, const void*
 
 namespace {
 
-int g_debug_flags = 0;
-
 struct RowGroupArgs {
   const int32_t* block_expert;
   const int32_t* n_blocks;
@@ -282,6 +315,11 @@ inline bool use_pair(const RowGroupArgs& r) {
 inline int check_rows(const RowGroupArgs& r) {
   if (r.rows < 0 || r.E <= 0) return LEWI_ERR_ARG;
   if (r.rows > 0x7fffff00LL) return LEWI_ERR_LIMIT;
+  // the CTA-pair kernels keep a per-expert prefix table in shared memory that is sized for kMaxExperts
+  if (r.pad_offsets != nullptr && r.E > kMaxExperts) return LEWI_ERR_LIMIT;
+  // several groups need a way to find a row block's expert: block_expert (single-CTA kernels) or
+  // pad_offsets with the CTA-pair kernels; pad_offsets alone is not enough when pairs are unavailable
+  if (r.E > 1 && r.block_expert == nullptr && (r.pad_offsets == nullptr || !use_pair(r))) return LEWI_ERR_SHAPE;
   return LEWI_OK;
 }
 
@@ -308,18 +346,13 @@ inline void fill_common(gg::Args& a, const RowGroupArgs& r) {
   a.k_splits = 1;
   a.partial = nullptr;
   a.col_bias = nullptr;
+  a.r1_row = nullptr;
+  a.r1_col = nullptr;
+  a.tn_part_rows = 0;
   a.scale_src = nullptr;
   a.scale_idx = nullptr;
   a.dw_partial = nullptr;
   a.dw_parts = 0;
-  a.ga_ptr = nullptr;
-  a.gb_ptr = nullptr;
-  a.ga_ld = 0;
-  a.gb_ld = 0;
-  a.g_idx = nullptr;
-  a.g_div = 1;
-  a.g_src_rows = 0;
-  a.dbg = g_debug_flags;
 }
 
 // Number of contraction parts for a TN product with `tiles0` output tiles (1 = no split).
@@ -340,29 +373,10 @@ int64_t lewi_router_logits_workspace_bytes(int d, int E) {
   return ((int64_t)3 * d * E * 2 + 255) / 256 * 256;
 }
 
-int lewi_router_logits(void* stream, const void* x, const float* w_router, const float* bias, float* logits,
-                       int64_t T, int d, int E, void* workspace, int64_t workspace_bytes) {
-  if (!x || !w_router || !logits || T < 0 || d <= 0 || E <= 0) return LEWI_ERR_ARG;
-  if (T == 0) return LEWI_OK;
-  cudaStream_t st = as_stream(stream);
-  const bool tensor_path = workspace != nullptr && workspace_bytes >= (int64_t)3 * d * E * 2 && d % 64 == 0 &&
-                           E % 64 == 0 && aligned16(x) && aligned16(workspace) && aligned16(logits) &&
-                           T <= 0x7fffff00LL;
-  if (!tensor_path) {
-    dim3 grid((unsigned)((T + kRgTile - 1) / kRgTile), (unsigned)((E + kRgTile - 1) / kRgTile));
-    router_logits_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), w_router, bias, logits, T,
-                                               d, E);
-    LEWI_CHECK_LAUNCH();
-    return LEWI_OK;
-  }
-  // f32 weight = hi + mid + lo (three bf16 pieces, 24 mantissa bits); x is bf16, so every product is
-  // exact in f32 and the tensor cores accumulate in f32: logits = [x x x] . [hi; mid; lo].
-  __nv_bfloat16* w3 = reinterpret_cast<__nv_bfloat16*>(workspace);
-  const long long n = (long long)d * E;
-  long long sgrid = (n + 255) / 256;
-  if (sgrid > (long long)num_sms() * 8) sgrid = (long long)num_sms() * 8;
-  split3_bf16_kernel<<<(int)sgrid, 256, 0, st>>>(w_router, w3, n);
-  LEWI_CHECK_LAUNCH();
+namespace {
+// logits = [x x x] . [hi; mid; lo] on the tensor cores; w3 holds the three bf16 pieces of the f32 weight.
+int router_logits_tensor(cudaStream_t st, const void* x, const void* w3, const float* bias, float* logits, int64_t T,
+                         int d, int E) {
   CUtensorMap ta, tb;
   if (!gg::make_map(&ta, x, (uint64_t)d, (uint64_t)T, 0, 64, 128)) return LEWI_ERR_CUDA;
   if (!gg::make_map(&tb, w3, (uint64_t)E, (uint64_t)3 * d, 1, 64, 64)) return LEWI_ERR_CUDA;
@@ -377,8 +391,40 @@ int lewi_router_logits(void* stream, const void* x, const float* w_router, const
   a.out_f32 = 1;
   a.a_k_wrap = d;
   a.col_bias = bias;
+  CUtensorMap tc;
+  if (!gg::make_out_map(&tc, logits, (uint64_t)E, (uint64_t)T, 0, true)) return LEWI_ERR_CUDA;
   const long long tiles = (long long)a.n_blocks_host * ((E + gg::BN - 1) / gg::BN);
-  return gg::launch_auto<gg::NN, gg::PLAIN>(pair, st, ta, tb, tb, a, tiles);
+  return gg::launch_auto<gg::NN, gg::PLAIN>(pair, st, ta, tb, tb, a, tiles, &tc);
+}
+
+inline bool router_tensor_ok(const void* x, const float* logits, int64_t T, int d, int E) {
+  return d % 64 == 0 && E % 64 == 0 && aligned16(x) && aligned16(logits) && T <= 0x7fffff00LL;
+}
+}  // namespace
+
+int lewi_router_logits(void* stream, const void* x, const float* w_router, const float* bias, float* logits,
+                       int64_t T, int d, int E, void* workspace, int64_t workspace_bytes) {
+  if (!x || !w_router || !logits || T < 0 || d <= 0 || E <= 0) return LEWI_ERR_ARG;
+  if (T == 0) return LEWI_OK;
+  cudaStream_t st = as_stream(stream);
+  const bool tensor_path = workspace != nullptr && workspace_bytes >= (int64_t)3 * d * E * 2 && aligned16(workspace) &&
+                           router_tensor_ok(x, logits, T, d, E);
+  if (!tensor_path) {
+    dim3 grid((unsigned)((T + kRgTile - 1) / kRgTile), (unsigned)((E + kRgTile - 1) / kRgTile));
+    router_logits_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), w_router, bias, logits, T,
+                                               d, E);
+    LEWI_CHECK_LAUNCH();
+    return LEWI_OK;
+  }
+  // f32 weight = hi + mid + lo (three bf16 pieces, 24 mantissa bits); x is bf16, so every product is
+  // exact in f32 and the tensor cores accumulate in f32.
+  __nv_bfloat16* w3 = reinterpret_cast<__nv_bfloat16*>(workspace);
+  const long long n = (long long)d * E;
+  long long sgrid = (n + 255) / 256;
+  if (sgrid > (long long)num_sms() * 8) sgrid = (long long)num_sms() * 8;
+  split3_bf16_kernel<<<(int)sgrid, 256, 0, st>>>(w_router, w3, nullptr, n);
+  LEWI_CHECK_LAUNCH();
+  return router_logits_tensor(st, x, w3, bias, logits, T, d, E);
 }
 
 int lewi_grouped_gemm_nn(void* stream, const void* a_ptr, const void* b_ptr, void* out, const float* row_scale,
@@ -402,8 +448,10 @@ int lewi_grouped_gemm_nn(void* stream, const void* a_ptr, const void* b_ptr, voi
   a.kb_total = (K + gg::BK - 1) / gg::BK;
   a.N = N;
   a.out_f32 = out_dtype == LEWI_F32;
+  CUtensorMap tc;
+  if (!gg::make_out_map(&tc, out, (uint64_t)N, (uint64_t)rows, 0, a.out_f32 != 0)) return LEWI_ERR_CUDA;
   const long long tiles = (long long)a.n_blocks_host * ((N + gg::BN - 1) / gg::BN);
-  return gg::launch_auto<gg::NN, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb, a, tiles);
+  return gg::launch_auto<gg::NN, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb, a, tiles, &tc);
 }
 
 int lewi_grouped_gemm_nt(void* stream, const void* a_ptr, const void* b_ptr, void* out, const float* row_scale,
@@ -427,12 +475,32 @@ int lewi_grouped_gemm_nt(void* stream, const void* a_ptr, const void* b_ptr, voi
   a.kb_total = (K + gg::BK - 1) / gg::BK;
   a.N = N;
   a.out_f32 = out_dtype == LEWI_F32;
+  CUtensorMap tc;
+  if (!gg::make_out_map(&tc, out, (uint64_t)N, (uint64_t)rows, 0, a.out_f32 != 0)) return LEWI_ERR_CUDA;
   const long long tiles = (long long)a.n_blocks_host * ((N + gg::BN - 1) / gg::BN);
-  return gg::launch_auto<gg::NT, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb, a, tiles);
+  return gg::launch_auto<gg::NT, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb, a, tiles, &tc);
 }
+
+namespace {
+// Several experts: rows per contraction part.  Twice the mean group (so balanced routing never splits an expert and
+// only the heavy experts of a skewed batch are cut), a multiple of 64, at least 512.
+inline int tn_part_rows(int64_t rows, int E) {
+  long long r = 2 * ((rows + E - 1) / E);
+  if (r < 512) r = 512;
+  r = (r + gg::BK - 1) / gg::BK * gg::BK;
+  return r > 0x3fffffc0LL ? 0x3fffffc0 : (int)r;
+}
+// Slots of `partial` the ragged split can need: parts of multi-part experts, laid out with a stride of two per extra
+// part (see decode_tile), plus the run of the last such expert.
+inline long long tn_ragged_slots(int64_t rows, int E) {
+  const int R = tn_part_rows(rows, E);
+  return 2 * (rows / R) + 2;
+}
+}  // namespace
 
 int64_t lewi_grouped_gemm_tn_workspace_bytes(int64_t rows, int Ma, int Nb, int E, int split_out) {
   if (rows < 0 || Ma <= 0 || Nb <= 0 || E <= 0) return LEWI_ERR_ARG;
+  if (E > 1) return (int64_t)tn_ragged_slots(rows, E) * Ma * Nb * 4;
   const long long n_tiles = split_out ? 2LL * ((Nb / 2 + gg::BN - 1) / gg::BN) : (Nb + gg::BN - 1) / gg::BN;
   const int tm = gg::pair_mode() ? 2 * gg::BM : gg::BM;
   const long long tiles0 = (long long)E * ((Ma + tm - 1) / tm) * n_tiles;
@@ -443,19 +511,10 @@ int64_t lewi_grouped_gemm_tn_workspace_bytes(int64_t rows, int Ma, int Nb, int E
 int lewi_grouped_gemm_tn(void* stream, const void* a_ptr, const void* b_ptr, void* out, void* out2,
                          const int32_t* pad_offsets, int64_t rows, int Ma, int Nb, int E, int out_dtype,
                          void* workspace, int64_t workspace_bytes) {
-  return lewi_grouped_gemm_tn_gather(stream, a_ptr, b_ptr, out, out2, pad_offsets, rows, Ma, Nb, E, out_dtype, workspace,
-                                     workspace_bytes, nullptr, 1, 0, 0, 0);
-}
-
-int lewi_grouped_gemm_tn_gather(void* stream, const void* a_ptr, const void* b_ptr, void* out, void* out2,
-                                const int32_t* pad_offsets, int64_t rows, int Ma, int Nb, int E, int out_dtype,
-                                void* workspace, int64_t workspace_bytes, const int32_t* row_idx, int idx_div,
-                                int64_t src_rows, int gather_a, int gather_b) {
   if (!a_ptr || !b_ptr || !out || Ma <= 0 || Nb <= 0 || rows < 0 || E <= 0) return LEWI_ERR_ARG;
-  if ((gather_a || gather_b) && (!row_idx || idx_div <= 0 || src_rows <= 0 || src_rows > 0x7fffffffLL))
-    return LEWI_ERR_ARG;
   if (out_dtype != LEWI_BF16 && out_dtype != LEWI_F32) return LEWI_ERR_ARG;
   if (rows > 0x7fffff00LL) return LEWI_ERR_LIMIT;
+  if (E > kMaxExperts) return LEWI_ERR_LIMIT;
   if (Ma % 8 != 0 || Nb % 8 != 0 || !aligned16(a_ptr) || !aligned16(b_ptr) || !aligned16(out) || !aligned16(out2) ||
       !aligned16(workspace))
     return LEWI_ERR_SHAPE;
@@ -471,45 +530,63 @@ int lewi_grouped_gemm_tn_gather(void* stream, const void* a_ptr, const void* b_p
   a.N = Nb;
   a.Ma = Ma;
   a.out_f32 = out_dtype == LEWI_F32;
+  const bool f32 = a.out_f32 != 0;
   const long long n_tiles = out2 ? 2LL * ((Nb / 2 + gg::BN - 1) / gg::BN) : (Nb + gg::BN - 1) / gg::BN;
   const int tm = pair ? 2 * gg::BM : gg::BM;
-  const long long tiles0 = (long long)E * ((Ma + tm - 1) / tm) * n_tiles;
+  const long long per_e = (long long)((Ma + tm - 1) / tm) * n_tiles;
   cudaStream_t st = as_stream(stream);
+  const size_t half = out2 ? (size_t)Nb / 2 : (size_t)Nb;
   if (rows == 0) {
     // no rows at all: the product is all zeros
-    const size_t esz = out_dtype == LEWI_F32 ? 4 : 2;
-    const size_t half = out2 ? (size_t)Nb / 2 : (size_t)Nb;
+    const size_t esz = f32 ? 4 : 2;
     if (cudaMemsetAsync(out, 0, (size_t)E * Ma * half * esz, st) != cudaSuccess) return LEWI_ERR_CUDA;
     if (out2 && cudaMemsetAsync(out2, 0, (size_t)E * Ma * half * esz, st) != cudaSuccess) return LEWI_ERR_CUDA;
     return LEWI_OK;
   }
-  int splits = 1;
-  if (workspace != nullptr) {
-    splits = tn_pick_splits(tiles0 * (pair ? 2 : 1), rows);
-    const long long per = (long long)E * Ma * Nb * 4;
-    if ((long long)splits * per > workspace_bytes) splits = (int)(workspace_bytes / per);
+  const long long per_bytes = (long long)Ma * Nb * 4;
+  long long max_tiles = (long long)E * per_e;
+  int splits = 1, part_rows = 0;
+  long long slots = 0;
+  if (workspace != nullptr && E > 1) {
+    // ragged split: heavy experts are cut into parts of part_rows rows, summed afterwards in part order
+    const long long units = rows / tn_part_rows(rows, E) + E;
+    slots = tn_ragged_slots(rows, E);
+    if (slots * per_bytes <= workspace_bytes && units < 65535) {
+      part_rows = tn_part_rows(rows, E);
+      a.n_blocks_host = (int)units;
+      max_tiles = units * per_e;
+    }
+  } else if (workspace != nullptr) {
+    splits = tn_pick_splits(per_e * (pair ? 2 : 1), rows);
+    if ((long long)splits * per_bytes > workspace_bytes) splits = (int)(workspace_bytes / per_bytes);
     if (splits < 2) splits = 1;
+    slots = splits > 1 ? splits : 0;
+    max_tiles = per_e * splits;
   }
   a.k_splits = splits;
-  a.partial = splits > 1 ? reinterpret_cast<float*>(workspace) : nullptr;
-  CUtensorMap ta, tb;
-  if (!gg::make_map(&ta, a_ptr, (uint64_t)Ma, (uint64_t)(gather_a ? src_rows : rows), 0, 64, 64))
+  a.tn_part_rows = part_rows;
+  a.partial = (splits > 1 || part_rows > 0) ? reinterpret_cast<float*>(workspace) : nullptr;
+  CUtensorMap ta, tb, tp, tc, td;
+  if (!gg::make_map(&ta, a_ptr, (uint64_t)Ma, (uint64_t)rows, 0, 64, 64)) return LEWI_ERR_CUDA;
+  if (!gg::make_map(&tb, b_ptr, (uint64_t)Nb, (uint64_t)rows, 0, 64, 64)) return LEWI_ERR_CUDA;
+  if (!gg::make_out_map(&tc, out, (uint64_t)half, (uint64_t)Ma, (uint64_t)E, f32)) return LEWI_ERR_CUDA;
+  if (out2 != nullptr && !gg::make_out_map(&td, out2, (uint64_t)half, (uint64_t)Ma, (uint64_t)E, f32)) return LEWI_ERR_CUDA;
+  if (a.partial != nullptr && !gg::make_out_map(&tp, a.partial, (uint64_t)Nb, (uint64_t)Ma, (uint64_t)slots, true))
     return LEWI_ERR_CUDA;
-  if (!gg::make_map(&tb, b_ptr, (uint64_t)Nb, (uint64_t)(gather_b ? src_rows : rows), 0, 64, 64))
-    return LEWI_ERR_CUDA;
-  if (gather_a || gather_b) {   // the contraction rows of that operand are picked through row_idx
-    a.g_idx = row_idx;
-    a.g_div = idx_div;
-    a.g_src_rows = (int)src_rows;
-    if (gather_a) { a.ga_ptr = a_ptr; a.ga_ld = Ma; }
-    if (gather_b) { a.gb_ptr = b_ptr; a.gb_ld = Nb; }
-  }
-  if (int rc = gg::launch_auto<gg::TN, gg::TNOUT>(pair, st, ta, tb, tb, a, tiles0 * splits)) return rc;
+  if (int rc = gg::launch_auto<gg::TN, gg::TNOUT>(pair, st, ta, tb, a.partial ? tp : tb, a, max_tiles, &tc,
+                                                   out2 ? &td : &tc))
+    return rc;
   if (splits > 1) {
     const long long total4 = (long long)E * Ma * Nb / 4;
     long long grid = (total4 + 255) / 256;
     if (grid > (long long)num_sms() * 8) grid = (long long)num_sms() * 8;
     gg::tn_reduce_kernel<<<(int)grid, 256, 0, st>>>(a.partial, splits, (long long)E * Ma, Nb, out, out2, a.out_f32);
+    LEWI_CHECK_LAUNCH();
+  } else if (part_rows > 0) {
+    long long gx = ((long long)Ma * Nb / 4 + 255) / 256;
+    if (gx > 32) gx = 32;
+    gg::tn_reduce_ragged_kernel<<<dim3((unsigned)gx, (unsigned)E), 256, 0, st>>>(a.partial, pad_offsets, E, part_rows, Ma, Nb,
+                                                                                 out, out2, a.out_f32);
     LEWI_CHECK_LAUNCH();
   }
   return LEWI_OK;
@@ -518,40 +595,28 @@ int lewi_grouped_gemm_tn_gather(void* stream, const void* a_ptr, const void* b_p
 int lewi_grouped_gemm_gateup_swiglu(void* stream, const void* xs, const void* w_gate, const void* w_up, void* gu,
                                     void* h, const int32_t* block_expert, const int32_t* n_blocks,
                                     const int32_t* pad_offsets, int64_t rows, int d, int f, int E) {
-  return lewi_grouped_gemm_gateup_swiglu_gather(stream, xs, nullptr, 1, rows, nullptr, nullptr, w_gate, w_up, gu, h,
-                                                block_expert, n_blocks, pad_offsets, rows, d, f, E);
+  return lewi_grouped_gemm_gateup_swiglu_scaled(stream, xs, nullptr, nullptr, w_gate, w_up, gu, h, block_expert, n_blocks,
+                                                pad_offsets, rows, d, f, E);
 }
 
-int lewi_grouped_gemm_gateup_swiglu_gather(void* stream, const void* xs, const int32_t* row_idx, int idx_div,
-                                           int64_t src_rows, const int32_t* scale_idx, const float* h_scale_src,
-                                           const void* w_gate,
-                                           const void* w_up, void* gu, void* h, const int32_t* block_expert,
-                                           const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows, int d,
-                                           int f, int E) {
+int lewi_grouped_gemm_gateup_swiglu_scaled(void* stream, const void* xs, const int32_t* scale_idx,
+                                           const float* h_scale_src, const void* w_gate, const void* w_up, void* gu,
+                                           void* h, const int32_t* block_expert, const int32_t* n_blocks,
+                                           const int32_t* pad_offsets, int64_t rows, int d, int f, int E) {
   if (!xs || !w_gate || !w_up || !h || d <= 0 || f <= 0) return LEWI_ERR_ARG;
-  if (row_idx != nullptr && (idx_div <= 0 || src_rows <= 0 || src_rows > 0x7fffffffLL)) return LEWI_ERR_ARG;
-  if (scale_idx == nullptr) scale_idx = row_idx;   // still null: the scale table is indexed by the padded row itself
   RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
-  const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
+  const bool pair = use_pair(r);
   if (d % 8 != 0 || f % 8 != 0 || !aligned16(xs) || !aligned16(w_gate) || !aligned16(w_up) || !aligned16(gu) ||
       !aligned16(h))
     return LEWI_ERR_SHAPE;
   if (rows == 0) return LEWI_OK;
   CUtensorMap ta, tb, tb2;
-  if (!gg::make_map(&ta, xs, (uint64_t)d, (uint64_t)(row_idx ? src_rows : rows), 0, 64, 128))
-    return LEWI_ERR_CUDA;
+  if (!gg::make_map(&ta, xs, (uint64_t)d, (uint64_t)rows, 0, 64, 128)) return LEWI_ERR_CUDA;
   if (!gg::make_map(&tb, w_gate, (uint64_t)f, (uint64_t)d, (uint64_t)E, 64, 64)) return LEWI_ERR_CUDA;
   if (!gg::make_map(&tb2, w_up, (uint64_t)f, (uint64_t)d, (uint64_t)E, 64, 64)) return LEWI_ERR_CUDA;
   gg::Args a;
   fill_common(a, r);
-  if (row_idx != nullptr) {   // rows of xs are picked through row_idx instead of being materialised first
-    a.ga_ptr = xs;
-    a.ga_ld = d;
-    a.g_idx = row_idx;
-    a.g_div = idx_div;
-    a.g_src_rows = (int)src_rows;
-  }
   a.scale_src = h_scale_src;
   a.scale_idx = scale_idx;
   a.out = h;
@@ -559,48 +624,39 @@ int lewi_grouped_gemm_gateup_swiglu_gather(void* stream, const void* xs, const i
   a.K = d;
   a.kb_total = (d + gg::BK - 1) / gg::BK;
   a.N = f;
+  CUtensorMap th, tgu;
+  if (!gg::make_out_map(&th, h, (uint64_t)f, (uint64_t)rows, 0, false)) return LEWI_ERR_CUDA;
+  if (gu != nullptr && !gg::make_map(&tgu, gu, (uint64_t)f, 2, (uint64_t)rows, 64, 1, 32)) return LEWI_ERR_CUDA;
   const long long tiles = (long long)a.n_blocks_host * ((f + gg::BN / 2 - 1) / (gg::BN / 2));
-  return gg::launch_auto<gg::NN, gg::SWIGLU>(pair, as_stream(stream), ta, tb, tb2, a, tiles);
+  return gg::launch_auto<gg::NN, gg::SWIGLU>(pair, as_stream(stream), ta, tb, tb2, a, tiles, &th, gu ? &tgu : &th);
 }
 
 int lewi_grouped_gemm_dh_dswiglu(void* stream, const void* dys, const void* w_down, const void* gu, void* dgu,
                                  const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets,
                                  int64_t rows, int d, int f, int E) {
-  return lewi_grouped_gemm_dh_dswiglu_gather(stream, dys, nullptr, 1, rows, nullptr, nullptr, nullptr, w_down, gu, dgu,
-                                             block_expert, n_blocks, pad_offsets, rows, d, f, E);
+  return lewi_grouped_gemm_dh_dswiglu_scaled(stream, dys, nullptr, nullptr, nullptr, w_down, gu, dgu, block_expert,
+                                             n_blocks, pad_offsets, rows, d, f, E);
 }
 
 int lewi_dw_partial_parts(int f) { return f > 0 ? 2 * ((f + gg::BN - 1) / gg::BN) : LEWI_ERR_ARG; }
 
-int lewi_grouped_gemm_dh_dswiglu_gather(void* stream, const void* dys, const int32_t* row_idx, int idx_div,
-                                        int64_t src_rows, const int32_t* scale_idx, const float* scale_src,
-                                        float* dw_partial,
-                                        const void* w_down, const void* gu, void* dgu, const int32_t* block_expert,
-                                        const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows, int d,
-                                        int f, int E) {
+int lewi_grouped_gemm_dh_dswiglu_scaled(void* stream, const void* dys, const int32_t* scale_idx, const float* scale_src,
+                                        float* dw_partial, const void* w_down, const void* gu, void* dgu,
+                                        const int32_t* block_expert, const int32_t* n_blocks,
+                                        const int32_t* pad_offsets, int64_t rows, int d, int f, int E) {
   if (!dys || !w_down || !gu || !dgu || d <= 0 || f <= 0) return LEWI_ERR_ARG;
-  if (row_idx != nullptr && (idx_div <= 0 || src_rows <= 0 || src_rows > 0x7fffffffLL)) return LEWI_ERR_ARG;
-  if (scale_idx == nullptr) scale_idx = row_idx;   // still null: the scale table is indexed by the padded row itself
   RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
-  const bool pair = use_pair(r);
   if (int rc = check_rows(r)) return rc;
+  const bool pair = use_pair(r);
   if (d % 8 != 0 || f % 8 != 0 || !aligned16(dys) || !aligned16(w_down) || !aligned16(gu) || !aligned16(dgu))
     return LEWI_ERR_SHAPE;
   if (rows == 0) return LEWI_OK;
   CUtensorMap ta, tb;
-  if (!gg::make_map(&ta, dys, (uint64_t)d, (uint64_t)(row_idx ? src_rows : rows), 0, 64, 128))
-    return LEWI_ERR_CUDA;
+  if (!gg::make_map(&ta, dys, (uint64_t)d, (uint64_t)rows, 0, 64, 128)) return LEWI_ERR_CUDA;
   // w_down [E,f,d]: as the K-major B operand of dh[rows,f] = dys[rows,d] . w_down[e]^T
   if (!gg::make_map(&tb, w_down, (uint64_t)d, (uint64_t)f, (uint64_t)E, 64, pair ? 128 : 256)) return LEWI_ERR_CUDA;
   gg::Args a;
   fill_common(a, r);
-  if (row_idx != nullptr) {
-    a.ga_ptr = dys;
-    a.ga_ld = d;
-    a.g_idx = row_idx;
-    a.g_div = idx_div;
-    a.g_src_rows = (int)src_rows;
-  }
   a.scale_src = scale_src;
   a.scale_idx = scale_idx;
   a.dw_partial = dw_partial;
@@ -618,9 +674,30 @@ int lewi_grouped_gemm_dh_dswiglu_gather(void* stream, const void* dys, const int
   return gg::launch_auto<gg::NT, gg::DSWIGLU>(pair, as_stream(stream), ta, tb, tb, a, tiles, &tgu, &tdgu);
 }
 
+namespace {
+int grouped_gemm_dx_impl(void* stream, const void* dgu, const void* w_gate, const void* w_up, void* dxs,
+                         const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets,
+                         int64_t rows, int d, int f, int E, const float* r1_row, const float* r1_col);
+
+// Shared expert: dxs = dgu . [Wg | Wu]^T (+ dz[t] * w_sg[c], the input gradient through the gate) for one group.
+int moe_dx_rank1(void* stream, const void* dgu, const void* w_gate, const void* w_up, void* dxs, const float* dz,
+                 const float* w_sg, int64_t T, int d, int fs) {
+  return grouped_gemm_dx_impl(stream, dgu, w_gate, w_up, dxs, nullptr, nullptr, nullptr, T, d, fs, 1, dz,
+                              dz != nullptr ? w_sg : nullptr);
+}
+}  // namespace
+
 int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, const void* w_up, void* dxs,
                          const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets,
                          int64_t rows, int d, int f, int E) {
+  return grouped_gemm_dx_impl(stream, dgu, w_gate, w_up, dxs, block_expert, n_blocks, pad_offsets, rows, d, f, E, nullptr,
+                              nullptr);
+}
+
+namespace {
+int grouped_gemm_dx_impl(void* stream, const void* dgu, const void* w_gate, const void* w_up, void* dxs,
+                         const int32_t* block_expert, const int32_t* n_blocks, const int32_t* pad_offsets,
+                         int64_t rows, int d, int f, int E, const float* r1_row, const float* r1_col) {
   if (!dgu || !w_gate || !w_up || !dxs || d <= 0 || f <= 0) return LEWI_ERR_ARG;
   RowGroupArgs r{block_expert, n_blocks, pad_offsets, rows, E};
   const bool pair = use_pair(r);
@@ -636,17 +713,20 @@ int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, cons
   gg::Args a;
   fill_common(a, r);
   a.out = dxs;
+  a.r1_row = r1_row;
+  a.r1_col = r1_col;
   a.K = 2 * f;
   a.N = d;
   a.kb_split = (f + gg::BK - 1) / gg::BK;
   a.k2_offset = f;
   a.kb_total = 2 * a.kb_split;
+  CUtensorMap tc;
+  if (!gg::make_out_map(&tc, dxs, (uint64_t)d, (uint64_t)rows, 0, false)) return LEWI_ERR_CUDA;
   const long long tiles = (long long)a.n_blocks_host * ((d + gg::BN - 1) / gg::BN);
-  return gg::launch_auto<gg::NT, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb2, a, tiles);
+  return gg::launch_auto<gg::NT, gg::PLAIN>(pair, as_stream(stream), ta, tb, tb2, a, tiles, &tc);
 }
+}  // namespace
 
-// Bring-up hook: override the shared-memory descriptor geometry (bytes).  A value of 0 keeps the
-// current setting.  Not part of the drop-in surface.
 // ------------------------------------------------------------------------------------------------ expert parallel
 
 int lewi_ep_alloc(int64_t bytes, void** out_host) {
@@ -815,27 +895,307 @@ int lewi_set_sm_sharing(int on) {
   return LEWI_OK;
 }
 
-// Bring-up hook: 0 forces the single-CTA (cta_group::1) GEMM kernels, 1 (default) allows CTA pairs.
-int lewi_debug_set_cta_pair(int on) {
+// ------------------------------------------------------------------------------------------------ whole layer
+
+int64_t lewi_moe_residual_layout(int64_t T, int d, int E, int f, int k, int fs, int has_gate, int64_t* offsets_host) {
+  moe::Dims D;
+  if (!moe::make_dims(D, T, d, E, f, k, fs, has_gate)) return LEWI_ERR_ARG;
+  int64_t off[LEWI_MOE_RES_COUNT + 1];
+  moe::residual_layout(D, off);
+  if (offsets_host != nullptr) memcpy(offsets_host, off, sizeof(off));
+  return off[LEWI_MOE_RES_COUNT];
+}
+
+int64_t lewi_moe_workspace_bytes(int64_t T, int d, int E, int f, int k, int fs, int has_gate) {
+  moe::Dims D;
+  if (!moe::make_dims(D, T, d, E, f, k, fs, has_gate)) return LEWI_ERR_ARG;
+  moe::Workspace W;
+  moe::workspace_layout(D, W);
+  return W.total;
+}
+
+int lewi_moe_set_mark_callback(void (*fn)(const char*, void*)) {
+  moe::mark_fn() = fn;
+  return LEWI_OK;
+}
+
+int64_t lewi_moe_router_prepared_bytes(int d, int E) {
+  if (d <= 0 || E <= 0) return LEWI_ERR_ARG;
+  return (int64_t)4 * d * E * 2;
+}
+
+int lewi_moe_prepare_router(void* stream, const float* w_router, void* prepared, int d, int E) {
+  if (!w_router || !prepared || d <= 0 || E <= 0) return LEWI_ERR_ARG;
+  __nv_bfloat16* w3 = reinterpret_cast<__nv_bfloat16*>(prepared);
+  const long long n = (long long)d * E;
+  long long sgrid = (n + 255) / 256;
+  if (sgrid > (long long)num_sms() * 8) sgrid = (long long)num_sms() * 8;
+  split3_bf16_kernel<<<(int)sgrid, 256, 0, as_stream(stream)>>>(w_router, w3, w3 + 3 * n, n);
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+#define LEWI_TRY(call)            \
+  do {                            \
+    const int rc_ = (call);       \
+    if (rc_ != LEWI_OK) return rc_; \
+  } while (0)
+
+int lewi_moe_fwd(void* stream, void* side_stream, const void* x, const float* w_router, const float* router_bias,
+                 const void* router_prepared, const void* w_gate, const void* w_up, const void* w_down,
+                 const void* ws_gate, const void* ws_up, const void* ws_down, const float* w_sg, void* out,
+                 float* aux_loss, void* residual, int64_t residual_bytes, void* workspace, int64_t workspace_bytes,
+                 int64_t T, int d, int E, int f, int k, int fs) {
+  if (!x || !w_router || !w_gate || !w_up || !w_down || !out || !residual || !workspace) return LEWI_ERR_ARG;
+  if (fs > 0 && (!ws_gate || !ws_up || !ws_down)) return LEWI_ERR_ARG;
+  if (fs == 0 && w_sg != nullptr) return LEWI_ERR_ARG;
+  moe::Dims D;
+  if (!moe::make_dims(D, T, d, E, f, k, fs, w_sg != nullptr)) return LEWI_ERR_ARG;
+  if (E > kMaxExperts || k > kMaxTopK || k > E) return LEWI_ERR_LIMIT;
+  if (d % 8 != 0 || f % 8 != 0 || fs % 8 != 0 || !aligned16(residual) || !aligned16(workspace)) return LEWI_ERR_SHAPE;
+  int64_t ro[LEWI_MOE_RES_COUNT + 1];
+  moe::residual_layout(D, ro);
+  moe::Workspace W;
+  moe::workspace_layout(D, W);
+  if (residual_bytes < ro[LEWI_MOE_RES_COUNT] || workspace_bytes < W.total) return LEWI_ERR_WORKSPACE;
+  if (T == 0) return LEWI_OK;
+  uint8_t* R = reinterpret_cast<uint8_t*>(residual);
+  uint8_t* Wk = reinterpret_cast<uint8_t*>(workspace);
+  auto res = [&](int i) { return R + ro[i]; };
+  cudaStream_t st = as_stream(stream), sd = as_stream(side_stream);
+  const bool shared = fs > 0;
+  const bool fork = shared && side_stream != nullptr && side_stream != stream;
+  moe::Events* ev = fork ? moe::events() : nullptr;
+  if (fork && ev == nullptr) return LEWI_ERR_CUDA;
+  void* sh_stream = fork ? side_stream : stream;
+
+  float* logits = reinterpret_cast<float*>(res(LEWI_MOE_RES_LOGITS));
+  int32_t* topk_idx = reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_TOPK_IDX));
+  float* topk_w = reinterpret_cast<float*>(res(LEWI_MOE_RES_TOPK_W));
+  int32_t* pad_offsets = reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_PAD_OFFSETS));
+  int32_t* block_expert = reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_BLOCK_EXPERT));
+  int32_t* n_blocks = reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_N_BLOCKS));
+  int32_t* pad_pos = reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_PAD_POS));
+  int32_t* row_slot = reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_ROW_SLOT));
+  float* gate = D.gate ? reinterpret_cast<float*>(res(LEWI_MOE_RES_GATE)) : nullptr;
+  void* ysh = shared ? Wk + W.ysh : nullptr;
+
+  // the shared expert needs only x: on the side stream it runs beside the memory-bound routing and dispatch
+  if (fork) {
+    if (cudaEventRecord(ev->fork_fwd, st) != cudaSuccess || cudaStreamWaitEvent(sd, ev->fork_fwd, 0) != cudaSuccess)
+      return LEWI_ERR_CUDA;
+    moe::mark("side_begin", sh_stream);
+  }
+  auto shared_fwd = [&]() -> int {
+    if (D.gate) {
+      moe::shared_gate_fwd_kernel<<<gather_grid(T), 256, 0, as_stream(sh_stream)>>>(
+          reinterpret_cast<const __nv_bfloat16*>(x), w_sg, gate, T, d);
+      LEWI_CHECK_LAUNCH();
+      moe::mark("shared_gate", sh_stream);
+    }
+    // with a gate, hs (and so the shared output) is stored already multiplied by it
+    LEWI_TRY(lewi_grouped_gemm_gateup_swiglu_scaled(sh_stream, x, nullptr, gate, ws_gate, ws_up, res(LEWI_MOE_RES_GUS),
+                                                    res(LEWI_MOE_RES_HS), nullptr, nullptr, nullptr, T, d, fs, 1));
+    moe::mark("shared_gateup_swiglu", sh_stream);
+    LEWI_TRY(lewi_grouped_gemm_nn(sh_stream, res(LEWI_MOE_RES_HS), ws_down, ysh, nullptr, nullptr, nullptr, nullptr, T, fs,
+                                  d, 1, LEWI_BF16));
+    moe::mark("shared_down", sh_stream);
+    return LEWI_OK;
+  };
+  if (shared && fork) LEWI_TRY(shared_fwd());
+
+  // router
+  const bool tensor_router = router_tensor_ok(x, logits, T, d, E);
+  if (tensor_router) {
+    const void* w3 = router_prepared;
+    if (w3 == nullptr) {
+      LEWI_TRY(lewi_moe_prepare_router(stream, w_router, Wk + W.w3, d, E));
+      w3 = Wk + W.w3;
+    }
+    LEWI_TRY(router_logits_tensor(st, x, w3, router_bias, logits, T, d, E));
+  } else {
+    LEWI_TRY(lewi_router_logits(stream, x, w_router, router_bias, logits, T, d, E, nullptr, 0));
+  }
+  moe::mark("router_logits", stream);
+  LEWI_TRY(lewi_router_topk(stream, logits, T, E, k, moe::kBlock, topk_idx, topk_w,
+                            reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_COUNTS)),
+                            reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_OFFSETS)), pad_offsets, block_expert, n_blocks,
+                            reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_ORDER)),
+                            reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_POS)), pad_pos, row_slot,
+                            reinterpret_cast<float*>(res(LEWI_MOE_RES_PROBS_SUM)), aux_loss, Wk + W.route,
+                            lewi_route_workspace_bytes(D.M, E)));
+  moe::mark("router_topk", stream);
+  // dispatch: padded row r holds token row_slot[r] / k (zero row where row_slot[r] < 0)
+  LEWI_TRY(lewi_gather_rows(stream, x, row_slot, nullptr, res(LEWI_MOE_RES_XS), T, D.Mpad, d, LEWI_BF16, k, 0, n_blocks,
+                            moe::kBlock));
+  moe::mark("dispatch_gather", stream);
+  // h carries the router weight of its row, so the down projection yields weighted outputs
+  LEWI_TRY(lewi_grouped_gemm_gateup_swiglu_scaled(stream, res(LEWI_MOE_RES_XS), row_slot, topk_w, w_gate, w_up,
+                                                  res(LEWI_MOE_RES_GU), res(LEWI_MOE_RES_H), block_expert, n_blocks,
+                                                  pad_offsets, D.Mpad, d, f, E));
+  moe::mark("gemm_gateup_swiglu", stream);
+  LEWI_TRY(lewi_grouped_gemm_nn(stream, res(LEWI_MOE_RES_H), w_down, Wk + W.ys, nullptr, block_expert, n_blocks,
+                                pad_offsets, D.Mpad, f, d, E, LEWI_BF16));
+  moe::mark("gemm_down", stream);
+  if (shared && !fork) LEWI_TRY(shared_fwd());
+  if (fork) {
+    if (cudaEventRecord(ev->join_fwd, sd) != cudaSuccess || cudaStreamWaitEvent(st, ev->join_fwd, 0) != cudaSuccess)
+      return LEWI_ERR_CUDA;
+  }
+  // combine: out[t] = sum_j ys[pad_pos[t,j]] + shared[t]
+  LEWI_TRY(lewi_gather_reduce(stream, Wk + W.ys, pad_pos, nullptr, ysh, nullptr, out, T, k, d, LEWI_BF16, LEWI_BF16,
+                              D.Mpad));
+  moe::mark("combine_gather_reduce", stream);
+  return LEWI_OK;
+}
+
+int lewi_moe_bwd(void* stream, void* side_stream, const void* dout, const void* x, const float* w_router,
+                 const void* router_prepared, const void* w_gate, const void* w_up, const void* w_down,
+                 const void* ws_gate, const void* ws_up, const void* ws_down, const float* w_sg, const void* residual,
+                 int64_t residual_bytes, void* workspace, int64_t workspace_bytes, void* dx, float* dw_router,
+                 float* d_router_bias, void* dw_gate, void* dw_up, void* dw_down, void* dws_gate, void* dws_up,
+                 void* dws_down, float* dw_sg, float* dw_topk, float aux_grad, int wgrad_dtype, int64_t T, int d, int E,
+                 int f, int k, int fs) {
+  if (!dout || !x || !w_router || !w_gate || !w_up || !w_down || !residual || !workspace) return LEWI_ERR_ARG;
+  if (!dx || !dw_router || !dw_gate || !dw_up || !dw_down) return LEWI_ERR_ARG;
+  if (fs > 0 && (!ws_gate || !ws_up || !ws_down || !dws_gate || !dws_up || !dws_down)) return LEWI_ERR_ARG;
+  if ((w_sg != nullptr) != (dw_sg != nullptr) || (fs == 0 && w_sg != nullptr)) return LEWI_ERR_ARG;
+  if (wgrad_dtype != LEWI_BF16 && wgrad_dtype != LEWI_F32) return LEWI_ERR_ARG;
+  moe::Dims D;
+  if (!moe::make_dims(D, T, d, E, f, k, fs, w_sg != nullptr)) return LEWI_ERR_ARG;
+  if (E > kMaxExperts || k > kMaxTopK || k > E) return LEWI_ERR_LIMIT;
+  if (d % 8 != 0 || f % 8 != 0 || fs % 8 != 0 || E % 8 != 0 || !aligned16(residual) || !aligned16(workspace))
+    return LEWI_ERR_SHAPE;
+  int64_t ro[LEWI_MOE_RES_COUNT + 1];
+  moe::residual_layout(D, ro);
+  moe::Workspace W;
+  moe::workspace_layout(D, W);
+  if (residual_bytes < ro[LEWI_MOE_RES_COUNT] || workspace_bytes < W.total) return LEWI_ERR_WORKSPACE;
+  cudaStream_t st = as_stream(stream), sd = as_stream(side_stream);
+  const size_t wsz = wgrad_dtype == LEWI_F32 ? 4 : 2;
+  if (T == 0) {   // no tokens: every weight gradient is zero
+    if (cudaMemsetAsync(dw_router, 0, (size_t)d * E * 4, st) != cudaSuccess ||
+        cudaMemsetAsync(dw_gate, 0, (size_t)E * d * f * wsz, st) != cudaSuccess ||
+        cudaMemsetAsync(dw_up, 0, (size_t)E * d * f * wsz, st) != cudaSuccess ||
+        cudaMemsetAsync(dw_down, 0, (size_t)E * d * f * wsz, st) != cudaSuccess)
+      return LEWI_ERR_CUDA;
+    if (fs > 0 && (cudaMemsetAsync(dws_gate, 0, (size_t)d * fs * wsz, st) != cudaSuccess ||
+                   cudaMemsetAsync(dws_up, 0, (size_t)d * fs * wsz, st) != cudaSuccess ||
+                   cudaMemsetAsync(dws_down, 0, (size_t)d * fs * wsz, st) != cudaSuccess))
+      return LEWI_ERR_CUDA;
+    if (dw_sg && cudaMemsetAsync(dw_sg, 0, (size_t)d * 4, st) != cudaSuccess) return LEWI_ERR_CUDA;
+    if (d_router_bias && cudaMemsetAsync(d_router_bias, 0, (size_t)E * 4, st) != cudaSuccess) return LEWI_ERR_CUDA;
+    return LEWI_OK;
+  }
+  const uint8_t* R = reinterpret_cast<const uint8_t*>(residual);
+  uint8_t* Wk = reinterpret_cast<uint8_t*>(workspace);
+  auto res = [&](int i) { return R + ro[i]; };
+  const bool shared = fs > 0;
+  const bool fork = shared && side_stream != nullptr && side_stream != stream;
+  moe::Events* ev = fork ? moe::events() : nullptr;
+  if (fork && ev == nullptr) return LEWI_ERR_CUDA;
+  void* sh_stream = fork ? side_stream : stream;
+
+  const float* logits = reinterpret_cast<const float*>(res(LEWI_MOE_RES_LOGITS));
+  const int32_t* topk_idx = reinterpret_cast<const int32_t*>(res(LEWI_MOE_RES_TOPK_IDX));
+  const float* topk_w = reinterpret_cast<const float*>(res(LEWI_MOE_RES_TOPK_W));
+  const int32_t* counts = reinterpret_cast<const int32_t*>(res(LEWI_MOE_RES_COUNTS));
+  const int32_t* pad_offsets = reinterpret_cast<const int32_t*>(res(LEWI_MOE_RES_PAD_OFFSETS));
+  const int32_t* block_expert = reinterpret_cast<const int32_t*>(res(LEWI_MOE_RES_BLOCK_EXPERT));
+  const int32_t* n_blocks = reinterpret_cast<const int32_t*>(res(LEWI_MOE_RES_N_BLOCKS));
+  const int32_t* pad_pos = reinterpret_cast<const int32_t*>(res(LEWI_MOE_RES_PAD_POS));
+  const int32_t* row_slot = reinterpret_cast<const int32_t*>(res(LEWI_MOE_RES_ROW_SLOT));
+  const float* gate = D.gate ? reinterpret_cast<const float*>(res(LEWI_MOE_RES_GATE)) : nullptr;
+  void* dxsh = shared ? Wk + W.dxsh : nullptr;
+  float* dz = D.gate ? reinterpret_cast<float*>(Wk + W.dz) : nullptr;
+
+  // shared expert backward: needs only dout, x and its own saved activations
+  if (fork) {
+    if (cudaEventRecord(ev->fork_bwd, st) != cudaSuccess || cudaStreamWaitEvent(sd, ev->fork_bwd, 0) != cudaSuccess)
+      return LEWI_ERR_CUDA;
+    moe::mark("side_begin", sh_stream);
+  }
+  auto shared_bwd = [&]() -> int {
+    float* dwps = D.gate ? reinterpret_cast<float*>(Wk + W.dwps) : nullptr;
+    // dh is scaled by the gate; the epilogue also leaves <dout[t], ungated shared output[t]> in pieces
+    LEWI_TRY(lewi_grouped_gemm_dh_dswiglu_scaled(sh_stream, dout, nullptr, gate, dwps, ws_down, res(LEWI_MOE_RES_GUS),
+                                                 Wk + W.dgus, nullptr, nullptr, nullptr, T, d, fs, 1));
+    moe::mark("shared_dh_dswiglu", sh_stream);
+    if (D.gate) {
+      float* partial = reinterpret_cast<float*>(Wk + W.colsum);
+      const int nparts = moe::colsum_parts(T);
+      moe::shared_gate_bwd_kernel<<<nparts, 256, 0, as_stream(sh_stream)>>>(
+          reinterpret_cast<const __nv_bfloat16*>(x), dwps, D.parts_s, gate, dz, partial, T, d);
+      LEWI_CHECK_LAUNCH();
+      col_sum_reduce_kernel<<<d, 256, 0, as_stream(sh_stream)>>>(partial, nparts, d, dw_sg);
+      LEWI_CHECK_LAUNCH();
+      moe::mark("shared_gate_bwd", sh_stream);
+    }
+    LEWI_TRY(lewi_grouped_gemm_tn(sh_stream, res(LEWI_MOE_RES_HS), dout, dws_down, nullptr, nullptr, T, fs, d, 1,
+                                  wgrad_dtype, W.tn_s_bytes > 0 ? Wk + W.tn_s : nullptr, W.tn_s_bytes));
+    moe::mark("shared_dw_down", sh_stream);
+    LEWI_TRY(moe_dx_rank1(sh_stream, Wk + W.dgus, ws_gate, ws_up, dxsh, dz, w_sg, T, d, fs));
+    moe::mark("shared_dx", sh_stream);
+    LEWI_TRY(lewi_grouped_gemm_tn(sh_stream, x, Wk + W.dgus, dws_gate, dws_up, nullptr, T, d, 2 * fs, 1, wgrad_dtype,
+                                  W.tn_s_bytes > 0 ? Wk + W.tn_s : nullptr, W.tn_s_bytes));
+    moe::mark("shared_dw_gateup", sh_stream);
+    return LEWI_OK;
+  };
+  if (shared && fork) LEWI_TRY(shared_bwd());
+
+  // combine backward: unscaled gather of dout into padded order; the router weight scales dh in the dH epilogue,
+  // which also emits the pieces of the routing-weight gradient <dout[t], y[row]>
+  LEWI_TRY(lewi_gather_rows(stream, dout, row_slot, nullptr, Wk + W.dys, T, D.Mpad, d, LEWI_BF16, k, 0, n_blocks,
+                            moe::kBlock));
+  moe::mark("combine_bwd_gather", stream);
+  LEWI_TRY(lewi_grouped_gemm_dh_dswiglu_scaled(stream, Wk + W.dys, row_slot, topk_w, reinterpret_cast<float*>(Wk + W.dwp),
+                                               w_down, res(LEWI_MOE_RES_GU), Wk + W.dgu, block_expert, n_blocks, pad_offsets,
+                                               D.Mpad, d, f, E));
+  moe::mark("gemm_dh_dswiglu", stream);
+  LEWI_TRY(lewi_grouped_gemm_tn(stream, res(LEWI_MOE_RES_H), Wk + W.dys, dw_down, nullptr, pad_offsets, D.Mpad, f, d, E,
+                                wgrad_dtype, W.tn_e_bytes > 0 ? Wk + W.tn_e : nullptr, W.tn_e_bytes));
+  moe::mark("gemm_dw_down", stream);
+  LEWI_TRY(lewi_grouped_gemm_dx(stream, Wk + W.dgu, w_gate, w_up, Wk + W.dxs, block_expert, n_blocks, pad_offsets, D.Mpad,
+                                d, f, E));
+  moe::mark("gemm_dx", stream);
+  LEWI_TRY(lewi_grouped_gemm_tn(stream, res(LEWI_MOE_RES_XS), Wk + W.dgu, dw_gate, dw_up, pad_offsets, D.Mpad, d, 2 * f, E,
+                                wgrad_dtype, W.tn_e_bytes > 0 ? Wk + W.tn_e : nullptr, W.tn_e_bytes));
+  moe::mark("gemm_dw_gateup", stream);
+  // router backward
+  LEWI_TRY(lewi_router_topk_bwd_full(stream, logits, topk_idx, nullptr, reinterpret_cast<const float*>(Wk + W.dwp), D.parts,
+                                     pad_pos, dw_topk, nullptr, Wk + W.dlb, T, E, k, counts, aux_grad, d_router_bias,
+                                     Wk + W.bias, W.bias_bytes));
+  moe::mark("router_topk_bwd", stream);
+  const __nv_bfloat16* w_r_bf16 = reinterpret_cast<const __nv_bfloat16*>(router_prepared);
+  if (w_r_bf16 == nullptr) {
+    LEWI_TRY(lewi_cast_f32_to_bf16(stream, w_router, Wk + W.w3, (int64_t)d * E));
+    w_r_bf16 = reinterpret_cast<const __nv_bfloat16*>(Wk + W.w3);
+  } else {
+    w_r_bf16 += (size_t)3 * d * E;
+  }
+  // dx_r [T,d] = dlogits . W_r^T  (W_r [d,E] is the K-major operand over E)
+  LEWI_TRY(lewi_grouped_gemm_nt(stream, Wk + W.dlb, w_r_bf16, Wk + W.dx_r, nullptr, nullptr, nullptr, nullptr, T, E, d, 1,
+                                LEWI_BF16));
+  moe::mark("router_dx", stream);
+  // dW_r [d,E] = x^T . dlogits
+  LEWI_TRY(lewi_grouped_gemm_tn(stream, x, Wk + W.dlb, dw_router, nullptr, nullptr, T, d, E, 1, LEWI_F32,
+                                W.tn_r_bytes > 0 ? Wk + W.tn_r : nullptr, W.tn_r_bytes));
+  moe::mark("router_dw", stream);
+  if (shared && !fork) LEWI_TRY(shared_bwd());
+  if (fork) {
+    if (cudaEventRecord(ev->join_bwd, sd) != cudaSuccess || cudaStreamWaitEvent(st, ev->join_bwd, 0) != cudaSuccess)
+      return LEWI_ERR_CUDA;
+  }
+  // dispatch backward: dx[t] = sum_j dxs[pad_pos[t,j]] + shared-expert and router terms
+  LEWI_TRY(lewi_gather_reduce(stream, Wk + W.dxs, pad_pos, nullptr, dxsh, Wk + W.dx_r, dx, T, k, d, LEWI_BF16, LEWI_BF16,
+                              D.Mpad));
+  moe::mark("dispatch_bwd_gather_reduce", stream);
+  return LEWI_OK;
+}
+
+// A/B switch: 0 forces the single-CTA (cta_group::1) GEMM kernels, 1 (default) allows CTA pairs.
+int lewi_set_cta_pair(int on) {
   gg::pair_mode() = on != 0;
-  return LEWI_OK;
-}
-
-// Bring-up hook: timing experiments that switch off parts of the GEMM kernels (results become wrong).
-int lewi_debug_set_flags(int flags) {
-  g_debug_flags = flags & 7;
-  route_wide() = (flags & 8) != 0;
-  return LEWI_OK;
-}
-
-int lewi_debug_set_desc(int k_lbo, int k_sbo, int k_step, int mn_lbo, int mn_sbo, int mn_step) {
-  gg::DescGeometry& g = gg::desc_geometry();
-  if (k_lbo > 0) g.k_lbo = (uint32_t)k_lbo;
-  if (k_sbo > 0) g.k_sbo = (uint32_t)k_sbo;
-  if (k_step > 0) g.k_step = (uint32_t)k_step;
-  if (mn_lbo > 0) g.mn_lbo = (uint32_t)mn_lbo;
-  if (mn_sbo > 0) g.mn_sbo = (uint32_t)mn_sbo;
-  if (mn_step > 0) g.mn_step = (uint32_t)mn_step;
   return LEWI_OK;
 }
 

@@ -17,7 +17,6 @@ namespace lewi {
 
 constexpr int kRouteThreads = 256;
 constexpr int kRouteWarps = kRouteThreads / kWarp;
-constexpr int kRouteTopkThreads = 1024;  // the soft-max/top-k phase uses 32 warps; histogram phases use the first 8
 constexpr int kRouteChunkTokens = 128;  // tokens per chunk when fed logits
 constexpr int kSortChunkSlots = 1024;   // slots per chunk when fed expert ids
 constexpr int kMaxExperts = 512;
@@ -127,7 +126,7 @@ struct RouteChunkArgs {
 };
 
 template <int ER>
-__global__ void __launch_bounds__(kRouteTopkThreads) route_chunk_kernel(RouteChunkArgs a) {
+__global__ void __launch_bounds__(kRouteThreads) route_chunk_kernel(RouteChunkArgs a) {
   extern __shared__ int s_mem[];
   int* s_e = s_mem;                                 // [chunk_slots]
   int* s_run = s_mem + a.chunk_slots;               // [kRouteWarps][E]
@@ -221,6 +220,8 @@ struct RouteScanArgs {
   int32_t* block_expert; // [nbmax] or null
   int32_t* n_blocks;     // [1] or null
   float* probs_sum;      // [E] or null
+  float* aux_loss;       // [1] or null: E * sum_e (counts_e / num_slots) * (probs_sum_e / num_tokens)
+  long long num_slots, num_tokens;
   int n_chunks, E, block, nbmax;
 };
 
@@ -231,6 +232,7 @@ __global__ void __launch_bounds__(kScanThreads) route_scan_kernel(RouteScanArgs 
   __shared__ int s_cnt[kMaxExperts];
   __shared__ int s_off[kMaxExperts + 1];
   __shared__ int s_pad[kMaxExperts + 1];
+  __shared__ float s_ps[kMaxExperts];
   const int tid = threadIdx.x;
   // parts: each expert's chunk range is split among P threads (P a power of two).
   int P = 1;
@@ -305,6 +307,17 @@ __global__ void __launch_bounds__(kScanThreads) route_scan_kernel(RouteScanArgs 
       float tot_p = 0.f;
       for (int q = 0; q < P; ++q) tot_p += __int_as_float(s_part[q * a.E + tid]);
       a.probs_sum[tid] = tot_p;
+      s_ps[tid] = tot_p;
+    }
+    if (a.aux_loss != nullptr) {
+      // load-balance loss: one thread adds the E terms in index order, so the value is reproducible
+      __syncthreads();
+      if (tid == 0) {
+        float acc = 0.f;
+        for (int x = 0; x < a.E; ++x) acc += (float)s_cnt[x] * s_ps[x];
+        const float denom = (float)a.num_slots * (float)a.num_tokens;
+        a.aux_loss[0] = denom > 0.f ? acc * (float)a.E / denom : 0.f;
+      }
     }
   }
 }
@@ -387,10 +400,21 @@ __global__ void __launch_bounds__(256) router_topk_bwd_kernel(const float* __res
                                                               float* __restrict__ dw_out,
                                                               float* __restrict__ dlogits,
                                                               __nv_bfloat16* __restrict__ dlogits_bf16, long long T,
-                                                              int E, int k) {
+                                                              int E, int k, const int32_t* __restrict__ counts,
+                                                              float aux_coef, float* __restrict__ bias_partial) {
+  __shared__ float s_bias[kMaxExperts];
   const int lane = threadIdx.x & 31;
   const long long warp_global = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  // gradient of the load-balance loss with respect to the soft-max probabilities of any token: the token
+  // fractions are constants, so dL/dp[t,e] = aux_coef * counts[e]
+  float cvec[ER], bias_acc[ER];
+#pragma unroll
+  for (int r = 0; r < ER; ++r) {
+    const int e = lane + r * kWarp;
+    cvec[r] = (counts != nullptr && e < E) ? aux_coef * (float)counts[e] : 0.f;
+    bias_acc[r] = 0.f;
+  }
   for (long long t = warp_global; t < T; t += n_warps) {
     const float* row = logits + t * E;
     float l[ER], p[ER];
@@ -433,8 +457,14 @@ __global__ void __launch_bounds__(256) router_topk_bwd_kernel(const float* __res
     const float dv = (lane < k) ? (my_dw - dot) / S : 0.f;
     const float pdp = warp_sum(my_v * dv);
     float dl[ER];
+    float pc = 0.f;
+    if (counts != nullptr) {
 #pragma unroll
-    for (int r = 0; r < ER; ++r) dl[r] = -p[r] * pdp;
+      for (int r = 0; r < ER; ++r) pc += p[r] * cvec[r];
+      pc = warp_sum(pc);
+    }
+#pragma unroll
+    for (int r = 0; r < ER; ++r) dl[r] = -p[r] * pdp + p[r] * (cvec[r] - pc);
     for (int j = 0; j < k; ++j) {
       int ej = __shfl_sync(0xffffffffu, my_e, j);
       float dvj = __shfl_sync(0xffffffffu, dv, j);
@@ -451,8 +481,40 @@ __global__ void __launch_bounds__(256) router_topk_bwd_kernel(const float* __res
         if (dlogits != nullptr) dlogits[t * E + e] = dl[r];
         if (dlogits_bf16 != nullptr) dlogits_bf16[t * E + e] = __float2bfloat16_rn(dl[r]);
       }
+      bias_acc[r] += dl[r];
     }
   }
+  if (bias_partial != nullptr) {
+    // column sums of dlogits over this CTA's tokens: warps fold in one after the other (fixed order)
+    const int warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    for (int w = 0; w < nwarps; ++w) {
+      if (warp == w) {
+#pragma unroll
+        for (int r = 0; r < ER; ++r) {
+          const int e = lane + r * kWarp;
+          if (e < E) s_bias[e] = (w == 0 ? 0.f : s_bias[e]) + bias_acc[r];
+        }
+      }
+      __syncthreads();
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) bias_partial[(long long)blockIdx.x * E + e] = s_bias[e];
+  }
+}
+
+// out[c] = sum over parts of partial[part, c]; one CTA per column group, fixed summation order.
+__global__ void __launch_bounds__(256) col_sum_reduce_kernel(const float* __restrict__ partial, int n_parts, int n_cols,
+                                                             float* __restrict__ out) {
+  __shared__ float s_red[256];
+  const int c = blockIdx.x;
+  float acc = 0.f;
+  for (int p = threadIdx.x; p < n_parts; p += blockDim.x) acc += partial[(long long)p * n_cols + c];
+  s_red[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = 128; o > 0; o >>= 1) {
+    if (threadIdx.x < o) s_red[threadIdx.x] += s_red[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) out[c] = s_red[0];
 }
 
 // ------------------------------------------------------------------------------------------------
@@ -531,9 +593,11 @@ __global__ void __launch_bounds__(256) cast_f32_bf16_kernel(const float* __restr
     dst[i] = __float2bfloat16_rn(src[i]);
 }
 
-// f32 -> three bf16 pieces with hi + mid + lo == w to 24 mantissa bits; dst is [3][n].
+// f32 -> three bf16 pieces with hi + mid + lo == w to 24 mantissa bits; dst is [3][n].  `rounded` (optional, [n])
+// receives hi alone: the weight rounded to bf16.
 __global__ void __launch_bounds__(256) split3_bf16_kernel(const float* __restrict__ src,
-                                                          __nv_bfloat16* __restrict__ dst, long long n) {
+                                                          __nv_bfloat16* __restrict__ dst,
+                                                          __nv_bfloat16* __restrict__ rounded, long long n) {
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
     const float w = src[i];
     const __nv_bfloat16 hi = __float2bfloat16_rn(w);
@@ -541,6 +605,7 @@ __global__ void __launch_bounds__(256) split3_bf16_kernel(const float* __restric
     const __nv_bfloat16 mid = __float2bfloat16_rn(r1);
     const float r2 = r1 - __bfloat162float(mid);
     dst[i] = hi;
+    if (rounded != nullptr) rounded[i] = hi;
     dst[n + i] = mid;
     dst[2 * n + i] = __float2bfloat16_rn(r2);
   }
@@ -548,27 +613,20 @@ __global__ void __launch_bounds__(256) split3_bf16_kernel(const float* __restric
 
 // ------------------------------------------------------------------------------------------------ host
 
-// Bring-up switch: run the soft-max/top-k phase with 32 warps per CTA instead of 8 (measured: no gain, and
-// 1024-thread CTAs cannot share an SM with a GEMM CTA).
-inline bool& route_wide() {
-  static bool v = false;
-  return v;
-}
-
 inline int route_n_chunks(long long num_slots, int chunk_slots) {
   return (int)((num_slots + chunk_slots - 1) / chunk_slots);
 }
 
 template <int ER>
 inline void launch_route_chunk(cudaStream_t st, const RouteChunkArgs& a, int n_chunks, size_t smem) {
-  route_chunk_kernel<ER><<<n_chunks, (a.logits && route_wide()) ? kRouteTopkThreads : kRouteThreads, smem, st>>>(a);
+  route_chunk_kernel<ER><<<n_chunks, kRouteThreads, smem, st>>>(a);
 }
 
 inline int route_common(cudaStream_t st, const float* logits, const int32_t* flat_in, long long T, long long M,
                         int E, int k, int block, int32_t* topk_idx, float* topk_w, int32_t* counts,
                         int32_t* offsets, int32_t* pad_offsets, int32_t* block_expert, int32_t* n_blocks,
                         int32_t* order, int32_t* pos, int32_t* pad_pos, int32_t* row_slot, float* probs_sum,
-                        void* ws, long long ws_bytes) {
+                        void* ws, long long ws_bytes, float* aux_loss = nullptr) {
   if (E <= 0 || E > kMaxExperts) return LEWI_ERR_LIMIT;
   if (M > 0x7fffffffLL) return LEWI_ERR_LIMIT;
   const int chunk_slots = logits ? kRouteChunkTokens * k : kSortChunkSlots;
@@ -618,6 +676,9 @@ inline int route_common(cudaStream_t st, const float* logits, const int32_t* fla
   sa.block_expert = padded ? block_expert : nullptr;
   sa.n_blocks = padded ? n_blocks : nullptr;
   sa.probs_sum = probs_sum;
+  sa.aux_loss = (logits && probs_sum) ? aux_loss : nullptr;
+  sa.num_slots = M;
+  sa.num_tokens = T;
   sa.n_chunks = n_chunks;
   sa.E = E;
   sa.block = padded ? block : 0;

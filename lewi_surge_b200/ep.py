@@ -244,6 +244,11 @@ class _DevBuf:
     _lib.check(self.lib.lewi_ep_ipc_export(self.ptr, buf), "lewi_ep_ipc_export")
     return bytes(buf.raw)
 
+  def free(self):
+    if self.ptr:
+      self.lib.lewi_ep_free(self.ptr)
+      self.ptr = None
+
 
 class _SymmetricBuffer:
   """One buffer of the same size on every rank, each rank holding device pointers to all of them."""
@@ -266,6 +271,16 @@ class _SymmetricBuffer:
         self.ptrs.append(out.value)
     self.c_ptrs = (ctypes.c_void_p * self.world)(*self.ptrs)   # host array handed to the C entry points
 
+  def close(self):
+    """Unmaps the peers' buffers and frees this rank's own (call on every rank, after a barrier)."""
+    from . import _lib
+    lib = _lib.load()
+    for r, p in enumerate(self.ptrs):
+      if r != self.rank and p:
+        lib.lewi_ep_ipc_release(p)
+    self.ptrs = []
+    self.local.free()
+
 
 class ExpertParallelP2P:
   """Expert-parallel MoE layer whose dispatch and combine are kernels over peer memory.
@@ -287,8 +302,10 @@ class ExpertParallelP2P:
   passes only when every rank has finished the kernels queued before it.  No host synchronisation.
 
   `capacity` bounds the rows a rank can receive as a multiple of its own routed rows (M = T*k); the buffers are
-  allocated once for that bound.  More rows than that raise LEWI_STATUS_EP_OVERFLOW (rows are dropped, not
-  written out of bounds).
+  allocated once for that bound.  The default is the number of ranks: even if every token of every rank chose this
+  rank's experts nothing is dropped, like the reference (configs/stage1.yml: capacity_factor -1).  A smaller value
+  saves memory; rows beyond it are then dropped (never written out of bounds) and the device status gets
+  LEWI_STATUS_EP_OVERFLOW, which `overflowed()` reads: check it after a step when running with a reduced capacity.
   """
 
   BARRIER_TIMEOUT_MS = 4000
@@ -316,7 +333,7 @@ class ExpertParallelP2P:
     want = int(phases) if phases is not None else (1 if self.world == 1 else 4)
     self.phases = max(1, min(want, self.el))
     self.bounds = [self.el * p // self.phases for p in range(self.phases + 1)]
-    cap = float(capacity) if capacity is not None else min(float(self.world), 2.0)
+    cap = float(capacity) if capacity is not None else float(self.world)
     rows = int(self.m * cap)
     self.rmax = (rows + self.el * (BLOCK - 1)) // BLOCK * BLOCK
     self.parts = int(self.lib.lewi_dw_partial_parts(self.f))
@@ -359,6 +376,27 @@ class ExpertParallelP2P:
     self.counts_all.zero_()
     torch.cuda.synchronize(self.dev)
     dist.barrier(group=group)
+
+  def overflowed(self):
+    """Synchronises and reports whether a receive buffer was too small since the last status read (rows dropped).
+    Any other device-side problem raises."""
+    status = self._lib.last_status()
+    if status & ~self._lib.STATUS_EP_OVERFLOW:
+      raise self._lib.LewiError(f"device status {status}")
+    return bool(status & self._lib.STATUS_EP_OVERFLOW)
+
+  def close(self):
+    """Releases the peer mappings and this rank's exchange buffers.  Collective: every rank calls it."""
+    torch.cuda.synchronize(self.dev)
+    dist.barrier(group=self.group)
+    for name in ("s_x", "s_w", "s_ret", "s_dy", "s_yslot", "s_dxslot", "s_dwslot", "s_counts", "s_flags"):
+      buf = getattr(self, name, None)
+      if buf is not None:
+        buf.close()
+        setattr(self, name, None)
+    for view in ("recv_x", "recv_w", "ret", "recv_dy", "y_slot", "dx_slot", "dw_slot", "counts_all", "flags"):
+      setattr(self, view, None)   # these pointed into the freed buffers
+    dist.barrier(group=self.group)
 
   def _sync_ranks(self):
     """Barrier between the ranks in the order of the current stream."""
@@ -435,6 +473,7 @@ class ExpertParallelP2P:
     main, comm = torch.cuda.current_stream(self.dev), self.comm
     logits = L.router_logits(x, w.w_router, w.router_bias)
     L._mark("router_logits")
+    self.last_logits = logits
     tb = L.router_topk(logits, k)
     L._mark("router_topk")
     routed = main.record_event()
@@ -466,7 +505,7 @@ class ExpertParallelP2P:
 
     def gemms(p, mark_done):
       lo, hi, po, be, nb = self._range(p)
-      check(lib.lewi_grouped_gemm_gateup_swiglu_gather(st(), ptr(self.recv_x), None, 1, self.rmax, None, ptr(self.recv_w),
+      check(lib.lewi_grouped_gemm_gateup_swiglu_scaled(st(), ptr(self.recv_x), None, ptr(self.recv_w),
                                                        ptr(w.w_gate[lo:hi]), ptr(w.w_up[lo:hi]), ptr(gu), ptr(h), ptr(be),
                                                        ptr(nb), ptr(po), self.rmax, d, f, hi - lo),
             "lewi_grouped_gemm_gateup_swiglu")
@@ -545,7 +584,7 @@ class ExpertParallelP2P:
 
     def gemms(p, mark_done):
       lo, hi, po, be, nb = self._range(p)
-      check(lib.lewi_grouped_gemm_dh_dswiglu_gather(st(), ptr(self.recv_dy), None, 1, self.rmax, None, ptr(self.recv_w),
+      check(lib.lewi_grouped_gemm_dh_dswiglu_scaled(st(), ptr(self.recv_dy), None, ptr(self.recv_w),
                                                     ptr(self.dwp), ptr(w.w_down[lo:hi]), ptr(c["gu"]), ptr(dgu), ptr(be),
                                                     ptr(nb), ptr(po), self.rmax, d, f, hi - lo),
             "lewi_grouped_gemm_dh_dswiglu")

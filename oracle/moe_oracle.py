@@ -28,7 +28,7 @@ import math
 import numpy as np
 
 __all__ = [
-    "bf16_round", "rel_err", "softmax", "router_topk", "router_topk_bwd", "aux_loss",
+    "bf16_round", "rel_err", "softmax", "router_topk", "router_topk_bwd", "aux_loss", "aux_loss_bwd",
     "sort_indices", "block_layout", "padded_rows_bound",
     "gather_rows", "gather_reduce", "gather_dot",
     "dispatch", "dispatch_bwd", "combine", "combine_bwd", "permute_rows", "permute_rows_bwd",
@@ -435,9 +435,19 @@ def moe_layer_fwd(x, w_router, w_gate, w_up, w_down, ws_gate, ws_up, ws_down, k,
   return out.astype(np.float32), cache
 
 
+def aux_loss_bwd(probs, idx, num_experts):
+  """Gradient of aux_loss with respect to the LOGITS [T,E]; the token fractions f_e are constants
+  (they come from an arg-max), so only the mean probabilities carry gradient."""
+  p = np.asarray(probs, np.float64)
+  t, k = idx.shape
+  counts = np.bincount(idx.reshape(-1), minlength=num_experts).astype(np.float64)
+  c = num_experts * counts / float(t * k) / float(t)          # d loss / d p[t,e], the same for every token
+  return (p * (c[None, :] - (p * c[None, :]).sum(axis=-1, keepdims=True))).astype(np.float32)
+
+
 def moe_layer_bwd(dout, x, w_router, w_gate, w_up, w_down, ws_gate, ws_up, ws_down, k, cache,
-                  shared_gate=None):
-  """Gradients of moe_layer_fwd for every differentiable input.
+                  shared_gate=None, aux_weight=0.0):
+  """Gradients of moe_layer_fwd for every differentiable input (plus ``aux_weight`` times the load-balance loss).
 
   Structure is the reference's gather-only backward (modal/moe_permute.py:282-309):
   dy = scaled gather of dout, dw = gather_dot, dx = gather_reduce.
@@ -469,13 +479,15 @@ def moe_layer_bwd(dout, x, w_router, w_gate, w_up, w_down, ws_gate, ws_up, ws_do
   dx = dx + dsg @ np.asarray(ws_gate, np.float32).T + dsu @ np.asarray(ws_up, np.float32).T
   # router
   dlogits = router_topk_bwd(c["logits"], c["idx"], dw)
+  if aux_weight:
+    dlogits = dlogits + np.float32(aux_weight) * aux_loss_bwd(c["p"], c["idx"], w_gate.shape[0])
   dw_router = x.T @ dlogits
   drouter_bias = dlogits.sum(axis=0)
   dx = dx + dlogits @ np.asarray(w_router, np.float32).T
   return dict(dx=dx.astype(np.float32), dw_router=dw_router.astype(np.float32), drouter_bias=drouter_bias,
               dw_gate=dwg, dw_up=dwu, dw_down=dwd, dws_gate=dws_gate.astype(np.float32),
               dws_up=dws_up.astype(np.float32), dws_down=dws_down.astype(np.float32),
-              dshared_gate=dshared_gate, dw=dw, dlogits=dlogits)
+              dshared_gate=dshared_gate, shared_gate_in=shared_gate, dw=dw, dlogits=dlogits)
 
 
 # ----------------------------------------------------------------------------- synthetic inputs

@@ -5,7 +5,10 @@
 The reference's `modal/moe_permute.py` and `modal/padded_gmm.py` are imported from the reference tree
 (never copied) under the NumPy stand-in of `jax_numpy_shim.py`, because real JAX is not installable
 where this runs.  With `CFG["enabled"] = False` every reference function takes its XLA (pure jnp)
-branch, which is the executable specification the CUDA kernels and the oracle must match.
+branch, which is the executable specification the CUDA kernels and the oracle must match.  The backward
+functions the reference registers with `defvjp` (`_dispatch_bwd`, `_combine_bwd`, `_permute_rows_bwd`:
+modal/moe_permute.py:282-329; `_perm_gather_bwd`: modal/padded_gmm.py:35-39) are called through the `fwd` / `bwd`
+pair the stand-in keeps, so gradients are pinned by the reference's own code as well.
 Inputs are seeded NumPy arrays with the shapes of the reference's unit test
 (modal/test_moe_permute.py:20,37: n=64, E=16, k in {6,12}; d=128 keeps the fixtures small).
 """
@@ -47,7 +50,21 @@ def main(ref_root):
     order_a, pos_a = mp.sort_indices(A(flat), E, "argsort")
     order_c, pos_c = mp.sort_indices(A(flat), E, "count")
     pos2 = np.asarray(pos_a).reshape(n, k)
+    # backward passes exactly as jax.custom_vjp would run them: residuals from fwd, cotangents into bwd
+    gy = prep(rng.standard_normal((m, d)).astype(np.float32))          # cotangent of dispatch / permute_rows outputs
+    gc = rng.standard_normal((n, d)).astype(np.float32)                # cotangent of combine's float32 output
+    perm = rng.permutation(m).astype(np.int32)
+    _, res_d = mp.dispatch.fwd(A(x), order_a, pos_a)
+    dispatch_dx = mp.dispatch.bwd(res_d, A(gy))[0]
+    comb_out, res_c = mp.combine.fwd(A(y), order_a, pos_a, A(np.asarray(w)))
+    combine_dy, _, _, combine_dw = mp.combine.bwd(res_c, A(gc))
+    perm_out, res_p = mp.permute_rows.fwd(A(y), A(perm))
+    permute_dx = mp.permute_rows.bwd(res_p, A(gy))[0]
     out = dict(
+        gy=gy, gc=gc, perm=perm, dispatch_dx=np.asarray(dispatch_dx, np.float32),
+        combine_fwd=np.asarray(comb_out), combine_dy=np.asarray(combine_dy, np.float32),
+        combine_dw=np.asarray(combine_dw, np.float32), permute_fwd=np.asarray(perm_out, np.float32),
+        permute_dx=np.asarray(permute_dx, np.float32),
         k=k, bf16=int(bf16), x=x, flat=flat, w=np.asarray(w), y=y, g=g, idx=idx, scale=scale,
         order_argsort=np.asarray(order_a), pos_argsort=np.asarray(pos_a),
         order_count=np.asarray(order_c), pos_count=np.asarray(pos_c),
@@ -69,13 +86,27 @@ def main(ref_root):
   mrows = int(gs.sum()) + 3
   rng = np.random.default_rng(7)
   a = bf16_round(rng.standard_normal((mrows, 64)).astype(np.float32))
-  b = bf16_round(rng.standard_normal((8, 64, 64)).astype(np.float32))
+  b = bf16_round(rng.standard_normal((8, 64, 48)).astype(np.float32))   # K=64, N=48 as in modal/te_run.py:73
   res = dict(gs=gs, a=a, b=b)
   for factor in (2.0, 1.0):
     pg.FACTOR = factor
     res[f"out_factor{int(factor)}"] = np.asarray(pg.padded_ragged_dot(np.asarray(a).view(jax_numpy_shim.Arr),
                                                                       np.asarray(b).view(jax_numpy_shim.Arr),
                                                                       np.asarray(gs).view(jax_numpy_shim.Arr)))
+  # _perm_gather and its registered backward on the row <-> slot maps padded_ragged_dot builds for factor 2
+  e, c = 8, 16
+  starts = np.cumsum(gs) - gs
+  rows = np.arange(mrows, dtype=np.int32)
+  expert = np.minimum(np.searchsorted(np.cumsum(gs), rows, side="right"), e - 1).astype(np.int32)
+  pos = rows - starts[expert]
+  slot = np.where((rows < gs.sum()) & (pos < c), expert * c + pos, e * c).astype(np.int32)
+  se, sc = np.arange(e * c, dtype=np.int32) // c, np.arange(e * c, dtype=np.int32) % c
+  src = np.where(sc < np.minimum(gs[se], c), starts[se] + sc, mrows).astype(np.int32)
+  V = lambda v: np.asarray(v).view(jax_numpy_shim.Arr)
+  buf, res_g = pg._perm_gather.fwd(V(a), V(src), V(slot))
+  gbuf = bf16_round(rng.standard_normal(np.asarray(buf).shape).astype(np.float32))
+  res.update(pg_src=src, pg_slot=slot, pg_fwd=np.asarray(buf, np.float32), pg_g=gbuf,
+             pg_bwd=np.asarray(pg._perm_gather.bwd(res_g, V(gbuf))[0], np.float32))
   np.savez_compressed(os.path.join(HERE, "padded_ragged_dot_te_shapes.npz"), **res)
   print("wrote padded_ragged_dot", {a_: b_.shape for a_, b_ in res.items()})
 

@@ -15,9 +15,9 @@ def cta_pair(request, cuda):
   """Runs a test once with the CTA-pair (cta_group::2) kernels and once with the single-CTA ones."""
   from lewi_surge_b200 import _lib
   lib = _lib.load()
-  lib.lewi_debug_set_cta_pair(request.param)
+  lib.lewi_set_cta_pair(request.param)
   yield request.param
-  lib.lewi_debug_set_cta_pair(1)
+  lib.lewi_set_cta_pair(1)
 
 
 def padded_problem(rng, gs, k_dim, block=128):
@@ -201,8 +201,9 @@ def test_single_group_long_contraction_is_split(cuda, cta_pair, t, ma, nb, split
 
 
 @pytest.mark.parametrize("t,d,e,f,k", [(300, 128, 8, 64, 2), (2048, 1024, 64, 512, 6), (777, 256, 16, 192, 4)])
-def test_gather_fused_kernels_equal_materialised_ones(cuda, cta_pair, t, d, e, f, k):
-  """Picking rows through row_slot inside the producer warp gives bit-identical results to gathering first."""
+def test_scaled_epilogues_and_routing_weight_gradient_pieces(cuda, cta_pair, t, d, e, f, k):
+  """The router weight folded into h (SwiGLU epilogue) and into dh (dSwiGLU epilogue), and the routing-weight
+  gradient pieces that epilogue emits, against the unfused kernels."""
   from lewi_surge_b200 import ops, layer, _lib
   g = torch.Generator(device="cpu").manual_seed(t + d)
   rn = lambda *s, std=1.0: (torch.randn(s, generator=g) * std)
@@ -216,39 +217,60 @@ def test_gather_fused_kernels_equal_materialised_ones(cuda, cta_pair, t, d, e, f
   ops.gather_rows(x, tb.row_slot, idx_div=k, out=xs, n_rows_dev=tb.n_blocks, rows_per_unit=128)
   nb = int(tb.n_blocks.item()) * 128
   gu0, h0 = layer.gateup_swiglu(xs, wg, wu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
-  gu1, h1 = layer.gateup_swiglu(x, wg, wu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets, row_idx=tb.row_slot,
-                                idx_div=k, rows=tb.mpad)
-  assert torch.equal(gu0[:nb], gu1[:nb]) and torch.equal(h0[:nb], h1[:nb])
-  # h scaled by the slot's router weight
   wflat = tb.topk_w.view(-1)
-  _, h2 = layer.gateup_swiglu(x, wg, wu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets, row_idx=tb.row_slot,
-                              idx_div=k, rows=tb.mpad, h_scale_src=wflat)
+  gu2, h2 = layer.gateup_swiglu(xs, wg, wu, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets,
+                                scale_idx=tb.row_slot, h_scale_src=wflat)
+  assert torch.equal(gu0[:nb], gu2[:nb])      # the pre-activations are stored unscaled
   rs = tb.row_slot[:nb].long()
   sc = torch.where(rs >= 0, wflat[rs.clamp(min=0)], torch.zeros_like(wflat[:1]))
   gf = gu0[:nb, :f].float()
   want_h2 = (gf * torch.sigmoid(gf) * gu0[:nb, f:].float()) * sc[:, None]   # from the bf16-rounded g|u: 1e-2 is ample
   assert float((h2[:nb].float() - want_h2).abs().max() / (want_h2.abs().max() + 1e-6)) <= 1e-2
-  # dH with gathered, scaled upstream gradient + routing-weight gradient pieces
+  # dH: scaled by the router weight, plus the pieces of <dout[t], y[row]>
   dys = torch.zeros((tb.mpad, d), dtype=torch.bfloat16, device=cuda)
   ops.gather_rows(dout, tb.row_slot, idx_div=k, out=dys, n_rows_dev=tb.n_blocks, rows_per_unit=128)
   dgu0 = layer.dh_dswiglu(dys, wd, gu0, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets)
-  dgu1, dwp = layer.dh_dswiglu(dout, wd, gu0, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets,
-                               row_idx=tb.row_slot, idx_div=k, want_dw_partial=True)
-  assert torch.equal(dgu0[:nb], dgu1[:nb])
+  dgu1, dwp = layer.dh_dswiglu(dys, wd, gu0, tb.block_expert, tb.n_blocks, pad_offsets=tb.pad_offsets,
+                               scale_idx=tb.row_slot, scale_src=wflat, want_dw_partial=True)
+  want_dgu = dgu0[:nb].float() * sc[:, None]
+  assert float((dgu1[:nb].float() - want_dgu).abs().max() / (want_dgu.abs().max() + 1e-6)) <= 1e-2
   ys = ops.grouped_gemm_nn(h0, wd, tb.block_expert, tb.n_blocks, out_dtype=torch.float32, pad_offsets=tb.pad_offsets)
   dw_want = ops.gather_dot(ys, tb.pad_pos.view(t, k), dout.float())
   dw_got = dwp.sum(1)[tb.pad_pos.long()].view(t, k)
   assert float((dw_got - dw_want).abs().max() / (dw_want.abs().max() + 1e-6)) <= 1e-2
-  # weight gradients with gathered contraction rows
-  a0 = ops.grouped_gemm_tn(xs, dgu0, tb.pad_offsets, e, out_dtype=torch.float32)
-  a1 = ops.grouped_gemm_tn(x, dgu0, tb.pad_offsets, e, out_dtype=torch.float32, row_idx=tb.row_slot, idx_div=k,
-                           gather_a=True, rows=tb.mpad)
-  assert torch.equal(a0, a1)
-  b0 = ops.grouped_gemm_tn(h0, dys, tb.pad_offsets, e, out_dtype=torch.float32)
-  b1 = ops.grouped_gemm_tn(h0, dout, tb.pad_offsets, e, out_dtype=torch.float32, row_idx=tb.row_slot, idx_div=k,
-                           gather_b=True, rows=tb.mpad)
-  assert torch.equal(b0, b1)
   assert _lib.last_status() == 0
+
+
+def test_weight_gradient_ragged_split_matches_unsplit(cuda, cta_pair):
+  """A few experts own most rows (their contractions are cut into parts and summed in part order); the result
+  equals the float64 product, empty experts are exact zeros, and two runs give the same bits."""
+  from lewi_surge_b200 import ops, _lib
+  e, ma, nb = 16, 128, 192
+  sizes = np.array([0, 3000, 5, 0, 128, 9000, 1, 257, 0, 0, 640, 77, 0, 4100, 129, 0], np.int64)
+  pad = (sizes + 127) // 128 * 128
+  pad_offsets = np.zeros(e + 1, np.int32)
+  pad_offsets[1:] = np.cumsum(pad)
+  rows = int(pad_offsets[-1])
+  rng = np.random.default_rng(5)
+  a = O.bf16_round(rng.standard_normal((rows, ma)).astype(np.float32))
+  b = O.bf16_round(rng.standard_normal((rows, nb)).astype(np.float32))
+  for x in range(e):   # padding rows of the layout are zero rows
+    a[pad_offsets[x] + sizes[x]:pad_offsets[x + 1]] = 0
+    b[pad_offsets[x] + sizes[x]:pad_offsets[x + 1]] = 0
+  A, B = to_dev(a, torch.bfloat16, cuda), to_dev(b, torch.bfloat16, cuda)
+  po = to_dev(pad_offsets, torch.int32, cuda)
+  _lib.last_status()
+  got = ops.grouped_gemm_tn(A, B, po, e, out_dtype=torch.float32)
+  again = ops.grouped_gemm_tn(A, B, po, e, out_dtype=torch.float32)
+  assert torch.equal(got, again)
+  g1, g2 = ops.grouped_gemm_tn(A, B, po, e, out_dtype=torch.bfloat16, split=True)
+  assert _lib.last_status() == 0
+  want = np.stack([a[pad_offsets[x]:pad_offsets[x + 1]].astype(np.float64).T @ b[pad_offsets[x]:pad_offsets[x + 1]].astype(np.float64)
+                   for x in range(e)])
+  assert O.rel_err(to_np(got), want) <= 1e-4
+  assert O.rel_err(np.concatenate([to_np(g1), to_np(g2)], axis=2), want) <= TOL
+  for x in np.nonzero(sizes == 0)[0]:
+    assert not to_np(got)[x].any() and not to_np(g1)[x].any() and not to_np(g2)[x].any()
 
 
 def test_ragged_dot_drop_in_known_answer(cuda):
@@ -260,7 +282,7 @@ def test_ragged_dot_drop_in_known_answer(cuda):
   m = s + 3
   rng = np.random.default_rng(0)
   a = O.bf16_round(rng.standard_normal((m, 64)))
-  b = O.bf16_round(rng.standard_normal((8, 64, 48 + 16)))   # N = 64 (kernel granularity); te_run uses 48
+  b = O.bf16_round(rng.standard_normal((8, 64, 48)))        # K = 64, N = 48 as in modal/te_run.py:73
   A = to_dev(a, torch.bfloat16, cuda).requires_grad_(True)
   B = to_dev(b, torch.bfloat16, cuda).requires_grad_(True)
   out = ops.ragged_dot(A, B, to_dev(gs, torch.int32, cuda))
@@ -268,7 +290,7 @@ def test_ragged_dot_drop_in_known_answer(cuda):
   assert O.rel_err(to_np(out)[:s], want[:s]) <= 2e-2
   assert np.all(to_np(out)[s:] == 0)
   (out[:s].float() ** 2).sum().backward()
-  dout = np.concatenate([2 * O.bf16_round(want[:s]), np.zeros((3, 64), np.float32)])
+  dout = np.concatenate([2 * O.bf16_round(want[:s]), np.zeros((3, 48), np.float32)])
   dl, dr = O.ragged_dot_bwd(dout, a, b, gs)
   assert O.rel_err(to_np(A.grad)[:s], dl[:s]) <= 2e-2 and np.all(to_np(A.grad)[s:] == 0)
   assert O.rel_err(to_np(B.grad), dr) <= 2e-2

@@ -253,6 +253,61 @@ def test_aux_loss_uniform_is_one():
   assert abs(O.aux_loss(probs, idx, e) - 1.0) < 1e-6
 
 
+def test_aux_loss_backward_matches_autograd():
+  """aux = E * sum_e f_e * mean_t softmax(logits)[t,e] with the token fractions f_e held constant."""
+  rng = np.random.default_rng(3)
+  t, e, k = 96, 16, 3
+  logits = rng.standard_normal((t, e)).astype(np.float32)
+  idx, w, p = O.router_topk(logits, k)
+  lt = torch.tensor(logits, dtype=torch.float64, requires_grad=True)
+  f = torch.tensor(np.bincount(idx.reshape(-1), minlength=e) / float(t * k))
+  loss = e * (f * torch.softmax(lt, -1).mean(0)).sum()
+  assert abs(float(loss) - O.aux_loss(p, idx, e)) <= 1e-6
+  loss.backward()
+  assert O.rel_err(O.aux_loss_bwd(p, idx, e), lt.grad.numpy()) <= 1e-5
+
+
+def test_layer_backward_with_gate_bias_and_aux_matches_autograd():
+  """The optional terms of the whole-layer backward (sigmoid gate on the shared expert, router bias, load-balance
+  loss) against torch autograd of the same forward."""
+  inp, k = small_layer()
+  names = ("x", "w_router", "w_gate", "w_up", "w_down", "ws_gate", "ws_up", "ws_down")
+  args = [inp[n] for n in names]
+  rng = np.random.default_rng(11)
+  t, d = inp["x"].shape
+  e = inp["w_gate"].shape[0]
+  bias = (rng.standard_normal(e) * 0.3).astype(np.float32)
+  sgate = (rng.standard_normal(d) * 0.2).astype(np.float32)
+  aux_w = 0.3
+  out, cache = O.moe_layer_fwd(*args, k, router_bias=bias, shared_gate=sgate)
+  g = O.moe_layer_bwd(inp["dout"], *args, k, cache, shared_gate=sgate, aux_weight=aux_w)
+  T = {n: torch.tensor(inp[n], dtype=torch.float64, requires_grad=True) for n in names}
+  tb = torch.tensor(bias, dtype=torch.float64, requires_grad=True)
+  tg = torch.tensor(sgate, dtype=torch.float64, requires_grad=True)
+  x = T["x"]
+  probs = torch.softmax(x @ T["w_router"] + tb, -1)
+  idx = torch.as_tensor(cache["idx"]).long()
+  v = torch.gather(probs, 1, idx)
+  wts = v / v.sum(-1, keepdim=True)
+  routed = torch.zeros_like(x)
+  for j in range(k):
+    ex = idx[:, j]
+    h = torch.nn.functional.silu(torch.einsum("td,tdf->tf", x, T["w_gate"][ex])) * torch.einsum("td,tdf->tf", x, T["w_up"][ex])
+    routed = routed + wts[:, j:j + 1] * torch.einsum("tf,tfd->td", h, T["w_down"][ex])
+  sh = (torch.nn.functional.silu(x @ T["ws_gate"]) * (x @ T["ws_up"])) @ T["ws_down"]
+  ref = routed + torch.sigmoid(x @ tg)[:, None] * sh
+  assert O.rel_err(out, ref.detach().numpy()) <= 1e-5
+  f = torch.tensor(np.bincount(cache["idx"].reshape(-1), minlength=e) / float(t * k))
+  total = (ref * torch.tensor(inp["dout"], dtype=torch.float64)).sum() + aux_w * e * (f * probs.mean(0)).sum()
+  total.backward()
+  pairs = dict(dx="x", dw_router="w_router", dw_gate="w_gate", dw_up="w_up", dw_down="w_down", dws_gate="ws_gate",
+               dws_up="ws_up", dws_down="ws_down")
+  for gn, pn in pairs.items():
+    assert O.rel_err(g[gn], T[pn].grad.numpy()) <= 2e-5, gn
+  assert O.rel_err(g["drouter_bias"], tb.grad.numpy()) <= 2e-5
+  assert O.rel_err(g["dshared_gate"], tg.grad.numpy()) <= 2e-5
+
+
 def test_bf16_round():
   a = np.array([1.0, 1.00390625, 1.005859375, -3.14159, 1e-30, 65504.0], np.float32)
   got = O.bf16_round(a)

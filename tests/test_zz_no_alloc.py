@@ -50,6 +50,14 @@ def test_static_scratch_variant_matches_workspace_variant_twice(cuda):
       w = getattr(want, name)
       n = got[name].numel()
       assert torch.equal(got[name].reshape(-1), w.reshape(-1)[:n]), name
+    # and directly against the CPU restatement of the router and of the reference's stable slot sort
+    import oracle as O
+    idx, wts, _ = O.router_topk(logits.cpu().numpy(), k)
+    lay = O.block_layout(idx.reshape(-1), e)
+    assert np.array_equal(got["topk_idx"].cpu().numpy(), idx)
+    assert O.rel_err(got["topk_w"].cpu().numpy(), wts) <= 1e-5
+    for name in ("counts", "offsets", "pad_offsets", "order", "pos", "pad_pos", "row_slot"):
+      assert np.array_equal(got[name].cpu().numpy(), lay[name]), name
   # and once more on the first shape: same answer after the array has held other data
   logits = torch.randn((4096, 64), generator=torch.Generator(device="cpu").manual_seed(123), dtype=torch.float32).to(cuda)
   want = layer.router_topk(logits, 6)
