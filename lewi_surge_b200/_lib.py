@@ -40,6 +40,7 @@ SIGNATURES = {
     "lewi_grouped_gemm_dh_dswiglu_scaled": (c_int, [P, P, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_group_tables": (c_int, [P, P, c_int64, c_int, c_int, P, P, P, P, P]),
     "lewi_gather_rows": (c_int, [P, P, P, P, P, c_int64, c_int64, c_int, c_int, c_int, c_int, P, c_int]),
+    "lewi_dispatch_rows": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int64, P, c_int]),
     "lewi_gather_reduce": (c_int, [P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int64]),
     "lewi_gather_dot": (c_int, [P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int64]),
     "lewi_grouped_gemm_nn": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int]),
@@ -67,6 +68,7 @@ SIGNATURES = {
     "lewi_ep_return_rows": (c_int, [P, P, P, P, P, c_int, c_int, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int]),
     "lewi_ep_zero_pad": (c_int, [P, P, P, P, P, c_int, c_int, c_int64]),
     "lewi_set_sm_sharing": (c_int, [c_int]),
+    "lewi_set_exchange_sms": (c_int, [c_int]),
     "lewi_ep_put_i32": (c_int, [P, P, P, c_int64, c_int, c_int]),
     "lewi_ep_barrier": (c_int, [P, P, P, P, c_int, c_int, c_int64]),
     "lewi_set_cta_pair": (c_int, [c_int]),

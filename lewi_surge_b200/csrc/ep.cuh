@@ -8,12 +8,14 @@
 // Dispatch is then one gather kernel whose stores go straight into the owners' buffers, together with a
 // return address per row (source rank and slot); the owners send expert outputs back the same way, with
 // stores into the source's slot-ordered buffer, where the combine is a sum over k consecutive rows.
-// Stores only cross NVLink (a store holds no register while in flight, a load does), and the kernels
-// are "thin": one CTA of 256 threads and at most 40 registers per SM, no shared memory, so that a CTA of
-// these fits on an SM beside a resident grouped-GEMM CTA (320 threads x 168 registers, all of shared
-// memory) whichever of the two arrives first; transfers of one range of experts then overlap the GEMMs
-// of another.  Ordering between ranks is either a stream-ordered collective issued by the host code or
-// the flag barrier below.  Plain loads/stores only (no multimem, no TMA).
+// Stores only cross NVLink (a store holds no register while in flight, a load does).  The two bulk kernels come
+// in two shapes that overlap a range's transfer with the GEMMs of another range in different ways:
+//   thin   one CTA of <= 256 threads and at most 40 registers per SM, no shared memory: it fits on an SM beside a
+//          resident grouped-GEMM CTA (which then shares its issue slots and memory pipes with it);
+//   fat    a few CTA pairs of 1024 threads that each claim a whole SM (they ask for most of its shared memory, so
+//          no GEMM CTA can join them), while the GEMM grids leave exactly that many SMs free.
+// Ordering between ranks is either a stream-ordered collective issued by the host code or the flag barrier
+// below.  Plain loads/stores only (no multimem, no TMA).
 #pragma once
 
 #include "common.cuh"
@@ -105,7 +107,9 @@ __device__ __forceinline__ unsigned long long ep_timer_ns() {
   return t;
 }
 
-constexpr int kEpThreads = 256;      // 8 warps x 40 registers: what is left beside a GEMM CTA (12 warps measured no faster)
+constexpr int kEpThreads = 256;      // thin: 8 warps x 40 registers, what is left beside a GEMM CTA (12 warps measured no faster)
+constexpr int kEpFatThreads = 1024;  // fat: the CTA has its SM to itself
+constexpr int kEpFatSmem = 160 * 1024;   // dynamic shared memory a fat CTA asks for (unused): keeps GEMM CTAs off its SM
 constexpr int kEpChunk = 4;          // 16-byte vectors per lane and pass
 constexpr int kEpSlotBits = 28;      // return address = source rank << 28 | slot
 
@@ -136,7 +140,8 @@ __device__ __forceinline__ void ep_copy_row(const __nv_bfloat16* __restrict__ sr
 // then the whole warp copies the 32 rows one after the other.  Consecutive rows of a batch go to consecutive
 // destinations, starting at this rank's right-hand neighbour, so at any moment every rank is sending to all the
 // others and no destination's ingress port is everybody's target.
-__global__ void __launch_bounds__(kEpThreads, 6) ep_push_rows_kernel(
+template <bool FAT>
+__global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6) ep_push_rows_kernel(
     const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ order, const int32_t* __restrict__ flat_expert,
     const int32_t* __restrict__ offsets, const int32_t* __restrict__ dst_base, const float* __restrict__ slot_w,
     PeerPtrs peer_rows, PeerPtrs peer_w, PeerPtrs peer_ret, long long m, int k, int d, int El, int G,
@@ -193,7 +198,8 @@ __global__ void __launch_bounds__(kEpThreads, 6) ep_push_rows_kernel(
 // `slot` of the source rank's slot-ordered buffer, and (optionally) its `parts` routing-weight gradient
 // pieces to the source's [slots, parts] buffer.  Padding rows carry the return address -1.  Same batching as
 // the push kernel: a lane reads one row's return address (and sends its pieces), the warp then copies 32 rows.
-__global__ void __launch_bounds__(kEpThreads, 6) ep_return_rows_kernel(
+template <bool FAT>
+__global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6) ep_return_rows_kernel(
     const __nv_bfloat16* __restrict__ rows, const float* __restrict__ pieces, const int32_t* __restrict__ ret,
     const int32_t* __restrict__ pad_offsets, int el_lo, int el_hi, PeerPtrs peer_slot_rows, PeerPtrs peer_slot_pieces,
     int d, int parts, int G, long long m_slots, long long rmax_pad) {

@@ -85,6 +85,54 @@ __global__ void __launch_bounds__(kGatherThreads) gather_rows_kernel(
   }
 }
 
+// Dispatch in token order: out[pos[t,j]] = x[t] for the k slots of token t; padded rows that hold no slot
+// (row_slot[r] < 0) become zero rows.  Every output row has exactly one writer, so this is the same function as
+// the row gather out[r] = x[row_slot[r] / k] -- but each source row is read once instead of k times at k distant
+// moments, which keeps the read side at T rows of DRAM traffic however large the source is against the L2.
+template <int VPL>
+__global__ void __launch_bounds__(kGatherThreads) dispatch_rows_kernel(
+    const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ pos, const int32_t* __restrict__ row_slot,
+    __nv_bfloat16* __restrict__ out, long long n_tokens, int k, int d, long long out_rows,
+    const int32_t* __restrict__ n_rows_dev, int rows_per_unit) {
+  const int lane = threadIdx.x & 31;
+  const long long warp0 = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long n_warps = ((long long)gridDim.x * blockDim.x) >> 5;
+  const int nvec = d / 8;
+  long long rows = out_rows;
+  if (n_rows_dev != nullptr) rows = min(rows, (long long)n_rows_dev[0] * rows_per_unit);
+  for (long long t = warp0; t < n_tokens; t += n_warps) {
+    const int my_pos = lane < k ? pos[t * k + lane] : -1;
+    uint4 v[VPL];
+#pragma unroll
+    for (int c = 0; c < VPL; ++c) {
+      const int vi = lane + c * kWarp;
+      v[c] = make_uint4(0, 0, 0, 0);
+      if (vi < nvec) v[c] = ld_nc_v4(reinterpret_cast<const uint4*>(x + t * d) + vi);
+    }
+    for (int j = 0; j < k; ++j) {
+      const long long p = __shfl_sync(0xffffffffu, my_pos, j);
+      if (p < 0 || p >= rows) {
+        if (lane == 0 && p >= rows) raise_status(LEWI_STATUS_BAD_INDEX);
+        continue;
+      }
+#pragma unroll
+      for (int c = 0; c < VPL; ++c) {
+        const int vi = lane + c * kWarp;
+        if (vi < nvec) st_v4(reinterpret_cast<uint4*>(out + p * d) + vi, v[c]);
+      }
+    }
+  }
+  // zero rows of the padded layout
+  for (long long r0 = warp0 * kWarp; r0 < rows; r0 += n_warps * kWarp) {
+    const long long r = r0 + lane;
+    const unsigned empty = __ballot_sync(0xffffffffu, r < rows && row_slot[r] < 0);
+    for (unsigned m = empty; m != 0; m &= m - 1) {
+      const long long rr = r0 + (__ffs(m) - 1);
+      for (int vi = lane; vi < nvec; vi += kWarp) st_v4(reinterpret_cast<uint4*>(out + rr * d) + vi, make_uint4(0, 0, 0, 0));
+    }
+  }
+}
+
 // out[t] = sum_j w[t,j] * y[pos[t,j]] (+ add0[t] + add1[t]); f32 accumulate.
 template <typename TI, typename TO, int VPL>
 __global__ void __launch_bounds__(kGatherThreads) gather_reduce_kernel(

@@ -309,9 +309,10 @@ class ExpertParallelP2P:
   """
 
   BARRIER_TIMEOUT_MS = 4000
+  DEFAULT_EXCHANGE_SMS = 16
 
   def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None, phases=None, sync="flags",
-               exchange_threads=(256, 256), dw_down_last=True):
+               exchange_threads=(0, 0), dw_down_last=True, exchange_sms=None):
     from . import _lib, layer, ops
     self.lib, self.layer, self.ops, self._lib = _lib.load(), layer, ops, _lib
     self.w, self.k, self.e, self.d, self.t = w, k, num_experts, d, tokens
@@ -324,7 +325,10 @@ class ExpertParallelP2P:
     if sync not in ("flags", "nccl"):
       raise ValueError("sync must be 'flags' or 'nccl'")
     self.sync = sync
-    self.fwd_threads, self.bwd_threads = (int(v) for v in exchange_threads)   # CTA size of the exchange kernels
+    self.fwd_threads, self.bwd_threads = (int(v) for v in exchange_threads)   # CTA size of the exchange kernels (0: largest)
+    # SMs the exchange kernels own while a pass runs (the GEMM grids leave them free); 0 = thin exchange CTAs that
+    # share every SM with a GEMM CTA
+    self.exchange_sms = int(exchange_sms) if exchange_sms is not None else (0 if self.world == 1 else self.DEFAULT_EXCHANGE_SMS)
     self.dw_down_last = bool(dw_down_last)
     self.el = num_experts // self.world
     self.f = w.w_gate.shape[2]
@@ -415,12 +419,19 @@ class ExpertParallelP2P:
     # a sub-range has no block table of its own: the CTA-pair kernels read pad_offsets alone
     return lo, hi, self.pad_offsets[lo:hi + 1], None, None
 
+  def _overlap_mode(self, on):
+    """How the exchange kernels of a pass coexist with its GEMMs: on their own SMs, or thin beside every GEMM CTA."""
+    if self.exchange_sms > 0:
+      self._lib.check(self.lib.lewi_set_exchange_sms(self.exchange_sms if on else 0), "lewi_set_exchange_sms")
+    else:
+      self.lib.lewi_set_sm_sharing(1 if on else 0)
+
   def forward(self, x):
-    self.lib.lewi_set_sm_sharing(1)   # exchange CTAs run beside the GEMM CTAs
+    self._overlap_mode(True)
     try:
       return self._forward(x)
     finally:
-      self.lib.lewi_set_sm_sharing(0)
+      self._overlap_mode(False)
 
   def _pipeline(self, push, gemms, give_back, first=None):
     """Issue order of one pass.  On the exchange stream: push 0, push 1, then for every range p >= 1 push p+1 followed
@@ -534,11 +545,11 @@ class ExpertParallelP2P:
     return out, dict(x=x, logits=logits, tb=tb, gu=gu, h=h, shared=tuple(shared) or None)
 
   def backward(self, dout, c):
-    self.lib.lewi_set_sm_sharing(1)
+    self._overlap_mode(True)
     try:
       return self._backward(dout, c)
     finally:
-      self.lib.lewi_set_sm_sharing(0)
+      self._overlap_mode(False)
 
   def _backward(self, dout, c):
     lib, L, ops, _lib, w, k = self.lib, self.layer, self.ops, self._lib, self.w, self.k

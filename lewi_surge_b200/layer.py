@@ -370,6 +370,12 @@ class HostPipeline:
     self.out_free = [None, None]   # result set i has been copied out
     self.device = device
     self.n = 0
+    self.holder = {}
+
+  @property
+  def grads(self):
+    """The weight gradients of the most recent step (device tensors), when the step function publishes them."""
+    return self.holder.get("grads")
 
   def step(self, x_host, dout_host, out_host, dx_host):
     i = self.n & 1
@@ -418,7 +424,7 @@ def host_pipeline(w: MoEWeights, k, tokens, graph=True):
     return CapturedStep(step) if graph else step
 
   pipe = HostPipeline(make_step, tokens, d, dev)
-  pipe.grads = holder["grads"]
+  pipe.holder = holder
   return pipe
 
 

@@ -72,6 +72,23 @@ def gather_rows(x, idx, scale=None, *, idx_div=1, scale_by_idx=False, out=None, 
   return out
 
 
+def dispatch_rows(x, pad_pos, row_slot, *, out=None, n_rows_dev=None, rows_per_unit=1):
+  """out[pad_pos[t,j]] = x[t]; padded rows without a slot become zero rows.  x: (T, D) bf16, pad_pos: (T, k) int32,
+  row_slot: (Mpad,) int32 -> (Mpad, D).  Equals ``gather_rows(x, row_slot, idx_div=k)`` (the dispatch of
+  modal/moe_permute.py:399-404), reading every token row once."""
+  lib = _lib.load()
+  t, k = pad_pos.shape
+  d = x.shape[1]
+  rows = row_slot.shape[0]
+  if out is None:
+    out = torch.empty((rows, d), dtype=x.dtype, device=x.device)
+  if x.dtype != torch.bfloat16:
+    raise LewiError("dispatch_rows takes bfloat16 rows")
+  check(lib.lewi_dispatch_rows(stream(), ptr(x.contiguous()), ptr(_i32(pad_pos).contiguous()), ptr(_i32(row_slot).contiguous()),
+                               ptr(out), t, k, d, rows, ptr(n_rows_dev), int(rows_per_unit)), "lewi_dispatch_rows")
+  return out
+
+
 def gather_reduce(y, pos, w=None, out_dtype=None, *, add0=None, add1=None, out=None):
   """out[t] = sum_j w[t,j] * y[pos[t,j]] in f32.  y: (M, D), pos: (N, k) int32, w: (N, k) or None -> (N, D).
 

@@ -115,3 +115,24 @@ def test_full_size_dispatch_combine_round_trip(cuda):
   assert torch.equal(xs, x[(tb.order // k).long()])
   back = ops.gather_reduce(xs, tb.pos.view(t, k), None, torch.float32)
   assert torch.equal(back, x.float() * k)
+
+
+@pytest.mark.parametrize("t,e,k,d,skew", [(300, 8, 2, 128, False), (4096, 64, 6, 1024, False), (5000, 128, 6, 256, True)])
+def test_dispatch_rows_equals_the_row_gather(cuda, t, e, k, d, skew):
+  """The token-order dispatch writes exactly what the gather through row_slot writes, zero padding rows included."""
+  from lewi_surge_b200 import layer, ops, _lib
+  g = torch.Generator(device="cpu").manual_seed(t + k)
+  logits = torch.randn((t, e), generator=g) * 2
+  if skew:
+    logits = logits + torch.from_numpy(O.zipf_bias(e, 0))
+  tb = layer.router_topk(logits.to(cuda), k)
+  x = torch.randn((t, d), generator=g).to(torch.bfloat16).to(cuda)
+  _lib.last_status()
+  want = torch.full((tb.mpad, d), 7.0, dtype=torch.bfloat16, device=cuda)
+  got = want.clone()
+  ops.gather_rows(x, tb.row_slot, idx_div=k, out=want, n_rows_dev=tb.n_blocks, rows_per_unit=128)
+  ops.dispatch_rows(x, tb.pad_pos.view(t, k), tb.row_slot, out=got, n_rows_dev=tb.n_blocks, rows_per_unit=128)
+  assert _lib.last_status() == 0
+  assert torch.equal(got, want)           # rows past the live blocks keep the fill value in both
+  nb = int(tb.n_blocks.item()) * 128
+  assert bool((got[nb:] == 7).all()) and nb <= tb.mpad
