@@ -108,10 +108,37 @@ __device__ __forceinline__ unsigned long long ep_timer_ns() {
 }
 
 constexpr int kEpThreads = 256;      // thin: 8 warps x 40 registers, what is left beside a GEMM CTA (12 warps measured no faster)
-constexpr int kEpFatThreads = 1024;  // fat: the CTA has its SM to itself
+constexpr int kEpFatThreads = 512;   // fat: the CTA has its SM to itself; 16 warps x 4 rows of 2 KB in flight
 constexpr int kEpFatSmem = 160 * 1024;   // dynamic shared memory a fat CTA asks for (unused): keeps GEMM CTAs off its SM
 constexpr int kEpChunk = 4;          // 16-byte vectors per lane and pass
 constexpr int kEpSlotBits = 28;      // return address = source rank << 28 | slot
+
+// ROWS rows at once (null source = no row): all loads of a pass are issued before the first store, so a warp keeps
+// ROWS x kEpChunk x 512 bytes in flight.
+template <int ROWS>
+__device__ __forceinline__ void ep_copy_rows(const __nv_bfloat16* const (&src)[ROWS], __nv_bfloat16* const (&dst)[ROWS],
+                                             int nvec, int lane) {
+  for (int c0 = 0; c0 < nvec; c0 += kEpChunk * kWarp) {
+    uint4 v[ROWS][kEpChunk];
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+      for (int c = 0; c < kEpChunk; ++c) {
+        const int vi = c0 + lane + c * kWarp;
+        v[r][c] = make_uint4(0, 0, 0, 0);
+        if (src[r] != nullptr && vi < nvec) v[r][c] = ld_nc_v4(reinterpret_cast<const uint4*>(src[r]) + vi);
+      }
+    }
+#pragma unroll
+    for (int r = 0; r < ROWS; ++r) {
+#pragma unroll
+      for (int c = 0; c < kEpChunk; ++c) {
+        const int vi = c0 + lane + c * kWarp;
+        if (src[r] != nullptr && vi < nvec) st_v4(reinterpret_cast<uint4*>(dst[r]) + vi, v[r][c]);
+      }
+    }
+  }
+}
 
 __device__ __forceinline__ void ep_copy_row(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                             int nvec, int lane) {
@@ -184,12 +211,28 @@ __global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6)
         }
       }
     }
-    for (int i = 0; i < kWarp; ++i) {
-      const int r = __shfl_sync(0xffffffffu, my_r, i);
-      const long long tok = __shfl_sync(0xffffffffu, my_tok, i);
-      const long long row = __shfl_sync(0xffffffffu, my_row, i);
-      if (r < 0) continue;
-      ep_copy_row(x + tok * d, reinterpret_cast<__nv_bfloat16*>(peer_rows.p[r]) + row * d, nvec, lane);
+    if constexpr (FAT) {
+      for (int i = 0; i < kWarp; i += 4) {
+        const __nv_bfloat16* src[4];
+        __nv_bfloat16* dst[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int r = __shfl_sync(0xffffffffu, my_r, i + q);
+          const long long tok = __shfl_sync(0xffffffffu, my_tok, i + q);
+          const long long row = __shfl_sync(0xffffffffu, my_row, i + q);
+          src[q] = r < 0 ? nullptr : x + tok * d;
+          dst[q] = r < 0 ? nullptr : reinterpret_cast<__nv_bfloat16*>(peer_rows.p[r]) + row * d;
+        }
+        ep_copy_rows<4>(src, dst, nvec, lane);
+      }
+    } else {
+      for (int i = 0; i < kWarp; ++i) {
+        const int r = __shfl_sync(0xffffffffu, my_r, i);
+        const long long tok = __shfl_sync(0xffffffffu, my_tok, i);
+        const long long row = __shfl_sync(0xffffffffu, my_row, i);
+        if (r < 0) continue;
+        ep_copy_row(x + tok * d, reinterpret_cast<__nv_bfloat16*>(peer_rows.p[r]) + row * d, nvec, lane);
+      }
     }
   }
 }
@@ -228,11 +271,26 @@ __global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6)
       }
     }
     if (rows == nullptr) continue;
-    for (int i = 0; i < kWarp; ++i) {
-      const int src = __shfl_sync(0xffffffffu, my_src, i);
-      const long long slot = __shfl_sync(0xffffffffu, my_slot, i);
-      if (src < 0) continue;
-      ep_copy_row(rows + (base + i) * d, reinterpret_cast<__nv_bfloat16*>(peer_slot_rows.p[src]) + slot * d, nvec, lane);
+    if constexpr (FAT) {
+      for (int i = 0; i < kWarp; i += 4) {
+        const __nv_bfloat16* from[4];
+        __nv_bfloat16* to[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const int src = __shfl_sync(0xffffffffu, my_src, i + q);
+          const long long slot = __shfl_sync(0xffffffffu, my_slot, i + q);
+          from[q] = src < 0 ? nullptr : rows + (base + i + q) * d;
+          to[q] = src < 0 ? nullptr : reinterpret_cast<__nv_bfloat16*>(peer_slot_rows.p[src]) + slot * d;
+        }
+        ep_copy_rows<4>(from, to, nvec, lane);
+      }
+    } else {
+      for (int i = 0; i < kWarp; ++i) {
+        const int src = __shfl_sync(0xffffffffu, my_src, i);
+        const long long slot = __shfl_sync(0xffffffffu, my_slot, i);
+        if (src < 0) continue;
+        ep_copy_row(rows + (base + i) * d, reinterpret_cast<__nv_bfloat16*>(peer_slot_rows.p[src]) + slot * d, nvec, lane);
+      }
     }
   }
 }

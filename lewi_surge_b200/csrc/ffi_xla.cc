@@ -1,12 +1,15 @@
-// XLA FFI handlers over the C ABI of liblewi_moe.so.  Compiled only where jaxlib's headers exist:
-//   nvcc -shared -Xcompiler -fPIC -std=c++17 -I$(python -c "import jax; print(jax.ffi.include_dir())") \
-//        -Iinclude lewi_surge_b200/csrc/ffi_xla.cc -Llewi_surge_b200 -llewi_moe -o liblewi_moe_ffi.so
-// Each handler reads device pointers, dimensions and the CUDA stream from the call frame and forwards
-// to the entry point of the same name; a non-zero return code becomes an ffi::Error.  All scratch is
-// passed in as extra result buffers, so XLA owns every allocation.
-#include <cstdint>
+// XLA FFI handlers over the C ABI of liblewi_moe.so.  Built only where jaxlib's headers exist:
+//   g++ -shared -fPIC -std=c++17 -I$(python -c "import jax; print(jax.ffi.include_dir())") -I$CUDA_HOME/include -Iinclude \
+//       lewi_surge_b200/csrc/ffi_xla.cc lewi_surge_b200/csrc/ffi_core.cc -Llewi_surge_b200 -llewi_moe -o liblewi_moe_ffi.so
+// Each handler reads device pointers, extents and attributes from its call frame and forwards them to the XLA-free
+// core (ffi_core.h); a non-zero return code becomes an ffi::Error.  All scratch is passed in as extra result buffers,
+// so XLA owns every allocation and the handlers can run under command-buffer (CUDA graph) capture.
+#include <cuda_runtime.h>
 
-#include "../../include/lewi_moe.h"
+#include <cstdint>
+#include <string>
+
+#include "ffi_core.h"
 #include "xla/ffi/api/ffi.h"
 
 namespace ffi = xla::ffi;
@@ -23,10 +26,9 @@ int DType(ffi::DataType t) { return t == ffi::DataType::F32 ? LEWI_F32 : LEWI_BF
 // sort_indices(flat_experts[M], num_experts) -> order[M], pos[M]; scratch u8[workspace]
 ffi::Error SortIndices(cudaStream_t stream, ffi::Buffer<ffi::S32> flat, ffi::ResultBuffer<ffi::S32> order,
                        ffi::ResultBuffer<ffi::S32> pos, ffi::ResultBuffer<ffi::U8> scratch, int32_t num_experts) {
-  const int64_t m = flat.element_count();
-  return Check(lewi_sort_indices(stream, flat.typed_data(), m, num_experts, 0, order->typed_data(), pos->typed_data(),
-                                 nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, scratch->typed_data(),
-                                 (int64_t)scratch->element_count()),
+  return Check(lewi_ffi::sort_indices(stream, flat.typed_data(), (int64_t)flat.element_count(), num_experts,
+                                      order->typed_data(), pos->typed_data(), scratch->typed_data(),
+                                      (int64_t)scratch->element_count()),
                "lewi_sort_indices");
 }
 
@@ -34,9 +36,9 @@ ffi::Error SortIndices(cudaStream_t stream, ffi::Buffer<ffi::S32> flat, ffi::Res
 ffi::Error GatherRows(cudaStream_t stream, ffi::AnyBuffer x, ffi::Buffer<ffi::S32> idx, ffi::Buffer<ffi::F32> scale,
                       ffi::Result<ffi::AnyBuffer> out, bool has_scale, int32_t idx_div, bool scale_by_idx) {
   const auto dims = x.dimensions();
-  return Check(lewi_gather_rows(stream, x.untyped_data(), idx.typed_data(), has_scale ? scale.typed_data() : nullptr,
-                                out->untyped_data(), dims[0], idx.element_count(), (int)dims[1], DType(x.element_type()),
-                                idx_div, scale_by_idx ? 1 : 0, nullptr, 1),
+  return Check(lewi_ffi::gather_rows(stream, x.untyped_data(), dims[0], (int)dims[1], DType(x.element_type()), idx.typed_data(),
+                                     (int64_t)idx.element_count(), has_scale ? scale.typed_data() : nullptr,
+                                     out->untyped_data(), idx_div, scale_by_idx),
                "lewi_gather_rows");
 }
 
@@ -45,9 +47,9 @@ ffi::Error GatherReduce(cudaStream_t stream, ffi::AnyBuffer y, ffi::Buffer<ffi::
                         ffi::Result<ffi::AnyBuffer> out, bool has_w) {
   const auto yd = y.dimensions();
   const auto pd = pos.dimensions();
-  return Check(lewi_gather_reduce(stream, y.untyped_data(), pos.typed_data(), has_w ? w.typed_data() : nullptr, nullptr,
-                                  nullptr, out->untyped_data(), pd[0], (int)pd[1], (int)yd[1], DType(y.element_type()),
-                                  DType(out->element_type()), yd[0]),
+  return Check(lewi_ffi::gather_reduce(stream, y.untyped_data(), yd[0], (int)yd[1], DType(y.element_type()), pos.typed_data(),
+                                       pd[0], (int)pd[1], has_w ? w.typed_data() : nullptr, out->untyped_data(),
+                                       DType(out->element_type())),
                "lewi_gather_reduce");
 }
 
@@ -56,14 +58,14 @@ ffi::Error GatherDot(cudaStream_t stream, ffi::AnyBuffer y, ffi::Buffer<ffi::S32
                      ffi::ResultBuffer<ffi::F32> out) {
   const auto yd = y.dimensions();
   const auto pd = pos.dimensions();
-  return Check(lewi_gather_dot(stream, y.untyped_data(), pos.typed_data(), g.untyped_data(), out->typed_data(), pd[0],
-                               (int)pd[1], (int)yd[1], DType(y.element_type()), yd[0]),
+  return Check(lewi_ffi::gather_dot(stream, y.untyped_data(), yd[0], (int)yd[1], DType(y.element_type()), pos.typed_data(),
+                                    pd[0], (int)pd[1], g.untyped_data(), out->typed_data()),
                "lewi_gather_dot");
 }
 
-// ragged_dot forward: lhs[M,K] bf16 (sorted by expert), rhs[E,K,N] bf16, group_sizes[E] -> out[M,N] bf16.
-// Scratch results: tables (pad_offsets[E+1], block_expert[Mpad/128], n_blocks[1], row_of_padded[Mpad],
-// padded_of_row[M]) and the two padded buffers lhs_pad[Mpad,K], out_pad[Mpad,N].
+// ragged_dot forward: lhs[M,K] bf16 (sorted by expert), rhs[E,K,N] bf16, group_sizes[E] -> out[M,N] bf16, the tables
+// (pad_offsets[E+1], block_expert[Mpad/128], n_blocks[1], row_of_padded[Mpad], padded_of_row[M]) and the padded
+// buffers lhs_pad[Mpad,K], out_pad[Mpad,N]
 ffi::Error RaggedDotFwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> lhs, ffi::Buffer<ffi::BF16> rhs,
                         ffi::Buffer<ffi::S32> gs, ffi::ResultBuffer<ffi::BF16> out, ffi::ResultBuffer<ffi::S32> pad_offsets,
                         ffi::ResultBuffer<ffi::S32> block_expert, ffi::ResultBuffer<ffi::S32> n_blocks,
@@ -71,80 +73,126 @@ ffi::Error RaggedDotFwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> lhs, ffi::Bu
                         ffi::ResultBuffer<ffi::BF16> lhs_pad, ffi::ResultBuffer<ffi::BF16> out_pad) {
   const int64_t m = lhs.dimensions()[0];
   const int k = (int)lhs.dimensions()[1], e = (int)rhs.dimensions()[0], n = (int)rhs.dimensions()[2];
-  const int64_t mpad = lewi_padded_rows_bound(m, e, 128);
-  if (int rc = lewi_group_tables(stream, gs.typed_data(), m, e, 128, pad_offsets->typed_data(), block_expert->typed_data(),
-                                 n_blocks->typed_data(), row_of_padded->typed_data(), padded_of_row->typed_data()))
-    return Check(rc, "lewi_group_tables");
-  if (int rc = lewi_gather_rows(stream, lhs.typed_data(), row_of_padded->typed_data(), nullptr, lhs_pad->typed_data(), m,
-                                mpad, k, LEWI_BF16, 1, 0, n_blocks->typed_data(), 128))
-    return Check(rc, "lewi_gather_rows");
-  if (int rc = lewi_grouped_gemm_nn(stream, lhs_pad->typed_data(), rhs.typed_data(), out_pad->typed_data(), nullptr,
-                                    block_expert->typed_data(), n_blocks->typed_data(), mpad, k, n, e, LEWI_BF16))
-    return Check(rc, "lewi_grouped_gemm_nn");
-  return Check(lewi_gather_rows(stream, out_pad->typed_data(), padded_of_row->typed_data(), nullptr, out->typed_data(),
-                                mpad, m, n, LEWI_BF16, 1, 0, nullptr, 1),
-               "lewi_gather_rows");
+  return Check(lewi_ffi::ragged_dot_fwd(stream, lhs.typed_data(), rhs.typed_data(), gs.typed_data(), m, k, n, e,
+                                        out->typed_data(), pad_offsets->typed_data(), block_expert->typed_data(),
+                                        n_blocks->typed_data(), row_of_padded->typed_data(), padded_of_row->typed_data(),
+                                        lhs_pad->typed_data(), out_pad->typed_data()),
+               "ragged_dot forward");
 }
 
 // dlhs = g . rhs[e]^T over the tables saved by the forward: g[M,N], rhs[E,K,N] -> dlhs[M,K]
 ffi::Error RaggedDotDlhs(cudaStream_t stream, ffi::Buffer<ffi::BF16> g, ffi::Buffer<ffi::BF16> rhs,
-                         ffi::Buffer<ffi::S32> block_expert, ffi::Buffer<ffi::S32> n_blocks,
-                         ffi::Buffer<ffi::S32> row_of_padded, ffi::Buffer<ffi::S32> padded_of_row,
-                         ffi::ResultBuffer<ffi::BF16> dlhs, ffi::ResultBuffer<ffi::BF16> g_pad,
-                         ffi::ResultBuffer<ffi::BF16> dl_pad) {
-  const int64_t m = g.dimensions()[0], mpad = row_of_padded.element_count();
+                         ffi::Buffer<ffi::S32> pad_offsets, ffi::Buffer<ffi::S32> block_expert,
+                         ffi::Buffer<ffi::S32> n_blocks, ffi::Buffer<ffi::S32> row_of_padded,
+                         ffi::Buffer<ffi::S32> padded_of_row, ffi::ResultBuffer<ffi::BF16> dlhs,
+                         ffi::ResultBuffer<ffi::BF16> g_pad, ffi::ResultBuffer<ffi::BF16> dl_pad) {
+  const int64_t m = g.dimensions()[0], mpad = (int64_t)row_of_padded.element_count();
   const int n = (int)g.dimensions()[1], e = (int)rhs.dimensions()[0], k = (int)rhs.dimensions()[1];
-  if (int rc = lewi_gather_rows(stream, g.typed_data(), row_of_padded.typed_data(), nullptr, g_pad->typed_data(), m, mpad,
-                                n, LEWI_BF16, 1, 0, n_blocks.typed_data(), 128))
-    return Check(rc, "lewi_gather_rows");
-  // rhs [E,K,N] read as the K-major operand [E, N'=K, K'=N] of g . rhs^T
-  if (int rc = lewi_grouped_gemm_nt(stream, g_pad->typed_data(), rhs.typed_data(), dl_pad->typed_data(), nullptr,
-                                    block_expert.typed_data(), n_blocks.typed_data(), mpad, n, k, e, LEWI_BF16))
-    return Check(rc, "lewi_grouped_gemm_nt");
-  return Check(lewi_gather_rows(stream, dl_pad->typed_data(), padded_of_row.typed_data(), nullptr, dlhs->typed_data(),
-                                mpad, m, k, LEWI_BF16, 1, 0, nullptr, 1),
-               "lewi_gather_rows");
+  return Check(lewi_ffi::ragged_dot_dlhs(stream, g.typed_data(), rhs.typed_data(), pad_offsets.typed_data(),
+                                         block_expert.typed_data(), n_blocks.typed_data(), row_of_padded.typed_data(),
+                                         padded_of_row.typed_data(), m, mpad, k, n, e, dlhs->typed_data(),
+                                         g_pad->typed_data(), dl_pad->typed_data()),
+               "ragged_dot dlhs");
 }
 
-// drhs[e] = lhs_pad[rows of e]^T . g_pad[rows of e]  -> [E,K,N] f32
+// drhs[e] = lhs_pad[rows of e]^T . g_pad[rows of e]  -> [E,K,N] f32; scratch u8 for split contractions
 ffi::Error RaggedDotDrhs(cudaStream_t stream, ffi::Buffer<ffi::BF16> lhs_pad, ffi::Buffer<ffi::BF16> g_pad,
-                         ffi::Buffer<ffi::S32> pad_offsets, ffi::ResultBuffer<ffi::F32> drhs) {
+                         ffi::Buffer<ffi::S32> pad_offsets, ffi::ResultBuffer<ffi::F32> drhs,
+                         ffi::ResultBuffer<ffi::U8> scratch) {
   const int64_t mpad = lhs_pad.dimensions()[0];
   const int k = (int)lhs_pad.dimensions()[1], n = (int)g_pad.dimensions()[1];
   const int e = (int)pad_offsets.element_count() - 1;
-  return Check(lewi_grouped_gemm_tn(stream, lhs_pad.typed_data(), g_pad.typed_data(), drhs->typed_data(), nullptr,
-                                    pad_offsets.typed_data(), mpad, k, n, e, LEWI_F32, nullptr, 0),
-               "lewi_grouped_gemm_tn");
+  return Check(lewi_ffi::ragged_dot_drhs(stream, lhs_pad.typed_data(), g_pad.typed_data(), pad_offsets.typed_data(), mpad, k,
+                                         n, e, drhs->typed_data(), scratch->typed_data(), (int64_t)scratch->element_count()),
+               "ragged_dot drhs");
+}
+
+lewi_ffi::MoeDims Dims(const ffi::Buffer<ffi::BF16>& x, const ffi::Buffer<ffi::BF16>& w_gate,
+                       const ffi::Buffer<ffi::BF16>& ws_gate, int32_t k, bool has_bias, bool has_gate) {
+  lewi_ffi::MoeDims D;
+  D.T = x.dimensions()[0];
+  D.d = (int)x.dimensions()[1];
+  D.E = (int)w_gate.dimensions()[0];
+  D.f = (int)w_gate.dimensions()[2];
+  D.k = k;
+  D.fs = ws_gate.element_count() > 0 ? (int)ws_gate.dimensions()[1] : 0;
+  D.has_bias = has_bias;
+  D.has_gate = has_gate;
+  return D;
+}
+
+// The whole layer, forward.  Optional operands (router_bias, shared expert, w_sg) arrive as zero-size buffers when
+// absent.  Results: out [T,d], aux_loss [1], the residual blob for the backward call and a scratch blob.
+ffi::Error MoeFwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> x, ffi::Buffer<ffi::F32> w_router,
+                  ffi::Buffer<ffi::F32> router_bias, ffi::Buffer<ffi::BF16> w_gate, ffi::Buffer<ffi::BF16> w_up,
+                  ffi::Buffer<ffi::BF16> w_down, ffi::Buffer<ffi::BF16> ws_gate, ffi::Buffer<ffi::BF16> ws_up,
+                  ffi::Buffer<ffi::BF16> ws_down, ffi::Buffer<ffi::F32> w_sg, ffi::ResultBuffer<ffi::BF16> out,
+                  ffi::ResultBuffer<ffi::F32> aux_loss, ffi::ResultBuffer<ffi::U8> residual,
+                  ffi::ResultBuffer<ffi::U8> workspace, int32_t k, bool has_bias, bool has_gate) {
+  const lewi_ffi::MoeDims D = Dims(x, w_gate, ws_gate, k, has_bias, has_gate);
+  return Check(lewi_ffi::moe_fwd(stream, D, x.typed_data(), w_router.typed_data(), router_bias.typed_data(),
+                                 w_gate.typed_data(), w_up.typed_data(), w_down.typed_data(), ws_gate.typed_data(),
+                                 ws_up.typed_data(), ws_down.typed_data(), w_sg.typed_data(), out->typed_data(),
+                                 aux_loss->typed_data(), residual->typed_data(), (int64_t)residual->element_count(),
+                                 workspace->typed_data(), (int64_t)workspace->element_count()),
+               "lewi_moe_fwd");
+}
+
+// The whole layer, backward.  Gradients of absent optional operands are zero-size results.
+ffi::Error MoeBwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> dout, ffi::Buffer<ffi::BF16> x,
+                  ffi::Buffer<ffi::F32> w_router, ffi::Buffer<ffi::BF16> w_gate, ffi::Buffer<ffi::BF16> w_up,
+                  ffi::Buffer<ffi::BF16> w_down, ffi::Buffer<ffi::BF16> ws_gate, ffi::Buffer<ffi::BF16> ws_up,
+                  ffi::Buffer<ffi::BF16> ws_down, ffi::Buffer<ffi::F32> w_sg, ffi::Buffer<ffi::U8> residual,
+                  ffi::ResultBuffer<ffi::BF16> dx, ffi::ResultBuffer<ffi::F32> dw_router,
+                  ffi::ResultBuffer<ffi::F32> d_router_bias, ffi::ResultBuffer<ffi::BF16> dw_gate,
+                  ffi::ResultBuffer<ffi::BF16> dw_up, ffi::ResultBuffer<ffi::BF16> dw_down,
+                  ffi::ResultBuffer<ffi::BF16> dws_gate, ffi::ResultBuffer<ffi::BF16> dws_up,
+                  ffi::ResultBuffer<ffi::BF16> dws_down, ffi::ResultBuffer<ffi::F32> dw_sg,
+                  ffi::ResultBuffer<ffi::U8> workspace, int32_t k, bool has_bias, bool has_gate, float aux_grad) {
+  const lewi_ffi::MoeDims D = Dims(x, w_gate, ws_gate, k, has_bias, has_gate);
+  return Check(lewi_ffi::moe_bwd(stream, D, dout.typed_data(), x.typed_data(), w_router.typed_data(), w_gate.typed_data(),
+                                 w_up.typed_data(), w_down.typed_data(), ws_gate.typed_data(), ws_up.typed_data(),
+                                 ws_down.typed_data(), w_sg.typed_data(), residual.typed_data(),
+                                 (int64_t)residual.element_count(), workspace->typed_data(),
+                                 (int64_t)workspace->element_count(), dx->typed_data(), dw_router->typed_data(),
+                                 d_router_bias->typed_data(), dw_gate->typed_data(), dw_up->typed_data(),
+                                 dw_down->typed_data(), dws_gate->typed_data(), dws_up->typed_data(), dws_down->typed_data(),
+                                 dw_sg->typed_data(), aux_grad, LEWI_BF16),
+               "lewi_moe_bwd");
 }
 
 }  // namespace
 
+#define LEWI_STREAM ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>()
+#define B16 ffi::Buffer<ffi::BF16>
+#define F32B ffi::Buffer<ffi::F32>
+#define S32B ffi::Buffer<ffi::S32>
+#define U8B ffi::Buffer<ffi::U8>
+
 XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_sort_indices, SortIndices,
-                              ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<ffi::Buffer<ffi::S32>>()
-                                  .Ret<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::U8>>()
-                                  .Attr<int32_t>("num_experts"));
+                              LEWI_STREAM.Arg<S32B>().Ret<S32B>().Ret<S32B>().Ret<U8B>().Attr<int32_t>("num_experts"));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_gather_rows, GatherRows,
-                              ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<ffi::AnyBuffer>()
-                                  .Arg<ffi::Buffer<ffi::S32>>().Arg<ffi::Buffer<ffi::F32>>().Ret<ffi::AnyBuffer>()
+                              LEWI_STREAM.Arg<ffi::AnyBuffer>().Arg<S32B>().Arg<F32B>().Ret<ffi::AnyBuffer>()
                                   .Attr<bool>("has_scale").Attr<int32_t>("idx_div").Attr<bool>("scale_by_idx"));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_gather_reduce, GatherReduce,
-                              ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<ffi::AnyBuffer>()
-                                  .Arg<ffi::Buffer<ffi::S32>>().Arg<ffi::Buffer<ffi::F32>>().Ret<ffi::AnyBuffer>()
+                              LEWI_STREAM.Arg<ffi::AnyBuffer>().Arg<S32B>().Arg<F32B>().Ret<ffi::AnyBuffer>()
                                   .Attr<bool>("has_w"));
 XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_gather_dot, GatherDot,
-                              ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<ffi::AnyBuffer>()
-                                  .Arg<ffi::Buffer<ffi::S32>>().Arg<ffi::AnyBuffer>().Ret<ffi::Buffer<ffi::F32>>());
+                              LEWI_STREAM.Arg<ffi::AnyBuffer>().Arg<S32B>().Arg<ffi::AnyBuffer>().Ret<F32B>());
 XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_ragged_dot_fwd, RaggedDotFwd,
-                              ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<ffi::Buffer<ffi::BF16>>()
-                                  .Arg<ffi::Buffer<ffi::BF16>>().Arg<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::BF16>>()
-                                  .Ret<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::S32>>()
-                                  .Ret<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::BF16>>()
-                                  .Ret<ffi::Buffer<ffi::BF16>>());
+                              LEWI_STREAM.Arg<B16>().Arg<B16>().Arg<S32B>().Ret<B16>().Ret<S32B>().Ret<S32B>().Ret<S32B>()
+                                  .Ret<S32B>().Ret<S32B>().Ret<B16>().Ret<B16>());
 XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_ragged_dot_dlhs, RaggedDotDlhs,
-                              ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<ffi::Buffer<ffi::BF16>>()
-                                  .Arg<ffi::Buffer<ffi::BF16>>().Arg<ffi::Buffer<ffi::S32>>().Arg<ffi::Buffer<ffi::S32>>()
-                                  .Arg<ffi::Buffer<ffi::S32>>().Arg<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::BF16>>()
-                                  .Ret<ffi::Buffer<ffi::BF16>>().Ret<ffi::Buffer<ffi::BF16>>());
+                              LEWI_STREAM.Arg<B16>().Arg<B16>().Arg<S32B>().Arg<S32B>().Arg<S32B>().Arg<S32B>().Arg<S32B>()
+                                  .Ret<B16>().Ret<B16>().Ret<B16>());
 XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_ragged_dot_drhs, RaggedDotDrhs,
-                              ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>().Arg<ffi::Buffer<ffi::BF16>>()
-                                  .Arg<ffi::Buffer<ffi::BF16>>().Arg<ffi::Buffer<ffi::S32>>().Ret<ffi::Buffer<ffi::F32>>());
+                              LEWI_STREAM.Arg<B16>().Arg<B16>().Arg<S32B>().Ret<F32B>().Ret<U8B>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_moe_fwd, MoeFwd,
+                              LEWI_STREAM.Arg<B16>().Arg<F32B>().Arg<F32B>().Arg<B16>().Arg<B16>().Arg<B16>().Arg<B16>()
+                                  .Arg<B16>().Arg<B16>().Arg<F32B>().Ret<B16>().Ret<F32B>().Ret<U8B>().Ret<U8B>()
+                                  .Attr<int32_t>("k").Attr<bool>("has_bias").Attr<bool>("has_gate"));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_moe_bwd, MoeBwd,
+                              LEWI_STREAM.Arg<B16>().Arg<B16>().Arg<F32B>().Arg<B16>().Arg<B16>().Arg<B16>().Arg<B16>()
+                                  .Arg<B16>().Arg<B16>().Arg<F32B>().Arg<U8B>().Ret<B16>().Ret<F32B>().Ret<F32B>().Ret<B16>()
+                                  .Ret<B16>().Ret<B16>().Ret<B16>().Ret<B16>().Ret<B16>().Ret<F32B>().Ret<U8B>()
+                                  .Attr<int32_t>("k").Attr<bool>("has_bias").Attr<bool>("has_gate").Attr<float>("aux_grad"));

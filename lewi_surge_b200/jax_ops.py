@@ -1,11 +1,12 @@
 """JAX-facing operators: `jax.ffi` custom calls with `custom_vjp` wrappers that keep the signatures of the
-reference's `moe_permute` / `padded_gmm` functions, and `install()` which patches MaxText exactly where the
-reference does (modal/moe_permute.py:386-436, modal/padded_gmm.py:72-76).
+reference's `moe_permute` / `padded_gmm` functions, a fused `moe_layer`, and `install()` which patches MaxText at the
+reference's patch points (modal/moe_permute.py:386-436, modal/padded_gmm.py:72-76).
 
-JAX is imported lazily: this module can be imported without it (the torch-facing mirror is `ops.py`).  It needs
-`liblewi_moe_ffi.so` (csrc/ffi_xla.cc built against jaxlib's FFI headers).  COMPILE-UNVERIFIED: neither JAX nor
-jaxlib could be installed where this repository was built; all numerics are validated through the same C entry
-points via ctypes.
+JAX is imported lazily: this module can be imported without it (the torch-facing mirror is `ops.py` / `layer.py`).
+It needs `liblewi_moe_ffi.so`: csrc/ffi_xla.cc + csrc/ffi_core.cc built against jaxlib's FFI headers.  NOT RUN
+ANYWHERE YET: neither JAX nor jaxlib could be installed where this repository was built.  What is checked without
+JAX: the XLA-free core compiles and links against the library, and the handler layer type-checks against a stand-in
+of the FFI header (tests/test_ffi_compile.py); all numerics are validated through the same C entry points via ctypes.
 """
 from __future__ import annotations
 
@@ -17,7 +18,8 @@ FFI_LIB = os.path.join(HERE, "liblewi_moe_ffi.so")
 BLOCK = 128
 CFG = {"num_experts": None, "registered": False}
 _TARGETS = ("lewi_ffi_sort_indices", "lewi_ffi_gather_rows", "lewi_ffi_gather_reduce", "lewi_ffi_gather_dot",
-            "lewi_ffi_ragged_dot_fwd", "lewi_ffi_ragged_dot_dlhs", "lewi_ffi_ragged_dot_drhs")
+            "lewi_ffi_ragged_dot_fwd", "lewi_ffi_ragged_dot_dlhs", "lewi_ffi_ragged_dot_drhs", "lewi_ffi_moe_fwd",
+            "lewi_ffi_moe_bwd")
 
 
 def _register():
@@ -26,8 +28,8 @@ def _register():
     return
   import jax
   if not os.path.exists(FFI_LIB):
-    raise RuntimeError(f"{FFI_LIB} not built: compile csrc/ffi_xla.cc against jax.ffi.include_dir() first. "
-                       "There is no fallback path.")
+    raise RuntimeError(f"{FFI_LIB} not built: compile csrc/ffi_xla.cc and csrc/ffi_core.cc against "
+                       "jax.ffi.include_dir() first.  There is no fallback path.")
   ctypes.CDLL(os.path.join(HERE, "liblewi_moe.so"), mode=ctypes.RTLD_GLOBAL)
   lib = ctypes.CDLL(FFI_LIB)
   for name in _TARGETS:
@@ -43,6 +45,9 @@ def _core():
 def _check_rows(x):
   if x.ndim != 2 or (x.shape[1] * x.dtype.itemsize) % 16 != 0:
     raise ValueError("lewi_surge_b200: rows must be 2-D with a multiple of 16 bytes per row (no fallback path)")
+
+
+# ----------------------------------------------------------------------------------- per-op custom calls
 
 
 def gather_rows(x, idx, scale=None, idx_div=1, scale_by_idx=False):
@@ -93,155 +98,280 @@ def sort_indices(flat_experts, num_experts=None, method=None):
   return order, pos
 
 
-def _make_vjp_ops():
-  """Builds dispatch / combine / permute_rows / ragged_dot with the reference's gather-only backward passes."""
-  import jax
-  import jax.numpy as jnp
+class _Ops:
+  """The differentiable operators, built once JAX is importable.  Residuals hold JAX values only: dtypes travel as
+  zero-size carrier arrays (the reference's trick, modal/moe_permute.py:277-279), never as Python objects."""
 
-  @jax.custom_vjp
-  def dispatch(x, order, pos):
-    k = order.shape[0] // x.shape[0]
-    return gather_rows(x, order, idx_div=k)
+  def __init__(self):
+    import jax
+    import jax.numpy as jnp
+    self.jax, self.jnp = jax, jnp
+    carrier = lambda a: jnp.empty((a.shape[0], 0), a.dtype)
 
-  def dispatch_fwd(x, order, pos):
-    return dispatch(x, order, pos), (order, pos, jnp.empty((x.shape[0], 0), x.dtype))
+    # dispatch: rows grouped by expert; backward = unweighted gather-reduce (modal/moe_permute.py:270-289)
+    def dispatch(x, order, pos):
+      return gather_rows(x, order, idx_div=order.shape[0] // x.shape[0])
+    self.dispatch = jax.custom_vjp(dispatch)
+    self.dispatch.defvjp(
+        lambda x, order, pos: (dispatch(x, order, pos), (order, pos, carrier(x))),
+        lambda res, g: (gather_reduce(g, res[1].reshape(res[2].shape[0], -1), None, res[2].dtype), None, None))
 
-  def dispatch_bwd(res, g):
-    order, pos, carrier = res
-    n = carrier.shape[0]
-    return gather_reduce(g, pos.reshape(n, order.shape[0] // n), None, carrier.dtype), None, None
+    # combine: weighted sum of each token's k rows in f32; backward = scaled gather + gather-dot (:292-312)
+    def combine(y, order, pos, w):
+      return gather_reduce(y, pos.reshape(w.shape), w, jnp.float32)
 
-  dispatch.defvjp(dispatch_fwd, dispatch_bwd)
+    def combine_bwd(res, g):
+      y, order, pos, w = res
+      k = w.shape[1]
+      dy = gather_rows(g.astype(y.dtype), order, w.reshape(-1), idx_div=k, scale_by_idx=True)
+      return dy, None, None, gather_dot(y, pos.reshape(w.shape), g).astype(w.dtype)
+    self.combine = jax.custom_vjp(combine)
+    self.combine.defvjp(lambda y, order, pos, w: (combine(y, order, pos, w), (y, order, pos, w)), combine_bwd)
 
-  @jax.custom_vjp
-  def combine(y, order, pos, w):
-    n, k = w.shape
-    return gather_reduce(y, pos.reshape(n, k), w, jnp.float32)
+    # permute_rows: x[idx] for a permutation; backward gathers through the inverse permutation (:315-329)
+    def permute_rows(x, idx):
+      return gather_rows(x, idx)
 
-  def combine_fwd(y, order, pos, w):
-    return combine(y, order, pos, w), (y, order, pos, w)
+    def permute_bwd(idx, g):
+      inverse = jnp.zeros_like(idx).at[idx].set(jnp.arange(idx.shape[0], dtype=idx.dtype))
+      return gather_rows(g, inverse), None
+    self.permute_rows = jax.custom_vjp(permute_rows)
+    self.permute_rows.defvjp(lambda x, idx: (permute_rows(x, idx), idx), permute_bwd)
 
-  def combine_bwd(res, g):
-    y, order, pos, w = res
-    n, k = w.shape
-    dy = gather_rows(g.astype(y.dtype), order, w.reshape(-1), idx_div=k, scale_by_idx=True)
-    dw = gather_dot(y, pos.reshape(n, k), g).astype(w.dtype)
-    return dy, None, None, dw
+    self.ragged_dot = jax.custom_vjp(lambda lhs, rhs, gs: self._ragged_call(lhs, rhs, gs)[0])
+    self.ragged_dot.defvjp(self._ragged_fwd, self._ragged_bwd)
 
-  combine.defvjp(combine_fwd, combine_bwd)
-
-  @jax.custom_vjp
-  def permute_rows(x, idx):
-    return gather_rows(x, idx)
-
-  def permute_fwd(x, idx):
-    return permute_rows(x, idx), idx
-
-  def permute_bwd(idx, g):
-    inv = jnp.zeros_like(idx).at[idx].set(jnp.arange(idx.shape[0], dtype=idx.dtype))
-    return gather_rows(g, inv), None
-
-  permute_rows.defvjp(permute_fwd, permute_bwd)
-
-  def _shapes(m, k, n, e):
+  # ragged_dot: gather -> grouped GEMM -> gather, forward and backward (modal/padded_gmm.py:45-69 made dropless)
+  def _ragged_call(self, lhs, rhs, gs):
+    jax, jnp = self.jax, self.jnp
+    m, k = lhs.shape
+    e, _, n = rhs.shape
     mpad = int(_core().lewi_padded_rows_bound(m, e, BLOCK))
     i32 = lambda *s: jax.ShapeDtypeStruct(s, jnp.int32)
     b16 = lambda *s: jax.ShapeDtypeStruct(s, jnp.bfloat16)
-    return mpad, i32, b16
-
-  @jax.custom_vjp
-  def ragged_dot_core(lhs, rhs, gs):
-    return _ragged_fwd(lhs, rhs, gs)[0]
-
-  def _ragged_fwd(lhs, rhs, gs):
-    m, k = lhs.shape
-    e, _, n = rhs.shape
-    mpad, i32, b16 = _shapes(m, k, n, e)
     call = jax.ffi.ffi_call("lewi_ffi_ragged_dot_fwd",
                             (b16(m, n), i32(e + 1), i32(mpad // BLOCK), i32(1), i32(mpad), i32(m), b16(mpad, k), b16(mpad, n)))
     return call(lhs.astype(jnp.bfloat16), rhs.astype(jnp.bfloat16), gs.astype(jnp.int32))
 
-  def ragged_fwd(lhs, rhs, gs):
-    out, pad_offsets, block_expert, n_blocks, rop, por, lhs_pad, _ = _ragged_fwd(lhs, rhs, gs)
-    return out, (rhs.astype(jnp.bfloat16), pad_offsets, block_expert, n_blocks, rop, por, lhs_pad, lhs.dtype, rhs.dtype)
+  def _ragged_fwd(self, lhs, rhs, gs):
+    jnp = self.jnp
+    out, pad_offsets, block_expert, n_blocks, rop, por, lhs_pad, _ = self._ragged_call(lhs, rhs, gs)
+    residual = (rhs.astype(jnp.bfloat16), pad_offsets, block_expert, n_blocks, rop, por, lhs_pad,
+                jnp.empty((0,), lhs.dtype), jnp.empty((0,), rhs.dtype))
+    return out, residual
 
-  def ragged_bwd(res, g):
-    rhs, pad_offsets, block_expert, n_blocks, rop, por, lhs_pad, ldt, rdt = res
+  def _ragged_bwd(self, res, g):
+    jax, jnp = self.jax, self.jnp
+    rhs, pad_offsets, block_expert, n_blocks, rop, por, lhs_pad, lhs_like, rhs_like = res
     m, n = g.shape
     e, k, _ = rhs.shape
     mpad = lhs_pad.shape[0]
     b16 = lambda *s: jax.ShapeDtypeStruct(s, jnp.bfloat16)
     dlhs, g_pad, _ = jax.ffi.ffi_call("lewi_ffi_ragged_dot_dlhs", (b16(m, k), b16(mpad, n), b16(mpad, k)))(
-        g.astype(jnp.bfloat16), rhs, block_expert, n_blocks, rop, por)
-    drhs = jax.ffi.ffi_call("lewi_ffi_ragged_dot_drhs", jax.ShapeDtypeStruct((e, k, n), jnp.float32))(lhs_pad, g_pad,
-                                                                                                      pad_offsets)
-    return dlhs.astype(ldt), drhs.astype(rdt), None
-
-  ragged_dot_core.defvjp(ragged_fwd, ragged_bwd)
-  return dispatch, combine, permute_rows, ragged_dot_core
+        g.astype(jnp.bfloat16), rhs, pad_offsets, block_expert, n_blocks, rop, por)
+    scratch = max(int(_core().lewi_grouped_gemm_tn_workspace_bytes(mpad, k, n, e, 0)), 16)
+    drhs, _ = jax.ffi.ffi_call("lewi_ffi_ragged_dot_drhs", (jax.ShapeDtypeStruct((e, k, n), jnp.float32),
+                                                            jax.ShapeDtypeStruct((scratch,), jnp.uint8)))(lhs_pad, g_pad, pad_offsets)
+    return dlhs.astype(lhs_like.dtype), drhs.astype(rhs_like.dtype), None
 
 
-def install(mode="full", num_experts=None, tile=None, sort=None, factor=None, probe=True, patch_ragged_dot=True):
-  """Patch `jax.lax.ragged_dot` and `maxtext.layers.moe` (0.2.5); call BEFORE `import maxtext` is used.
+_OPS = None
 
-  Same arguments as the reference's installers; `tile`, `sort`, `factor`, `probe` are accepted and ignored
-  (block size is 128, the sort is a counting sort, the layout is dropless, there is no packing to probe).
-  """
+
+def _ops():
+  global _OPS
+  if _OPS is None:
+    _register()
+    _OPS = _Ops()
+  return _OPS
+
+
+def dispatch(x, order, pos):
+  """Signature of modal/moe_permute.py:271."""
+  return _ops().dispatch(x, order, pos)
+
+
+def combine(y, order, pos, w):
+  """Signature of modal/moe_permute.py:293."""
+  return _ops().combine(y, order, pos, w)
+
+
+def permute_rows(x, idx):
+  """Signature of modal/moe_permute.py:316."""
+  return _ops().permute_rows(x, idx)
+
+
+def padded_ragged_dot(lhs, rhs, group_sizes, precision=None, preferred_element_type=None, **kw):
+  """Drop-in for `jax.lax.ragged_dot` with the signature of modal/padded_gmm.py:45 (dropless layout)."""
+  del precision
+  if lhs.ndim != 2 or rhs.ndim != 3 or kw.get("group_offset") is not None:
+    raise ValueError("lewi_surge_b200.padded_ragged_dot: only lhs [M,K], rhs [E,K,N] without group_offset")
+  return _ops().ragged_dot(lhs, rhs, group_sizes).astype(preferred_element_type or lhs.dtype)
+
+
+te_ragged_dot = padded_ragged_dot
+
+
+# ----------------------------------------------------------------------------------- the fused layer
+
+
+def moe_layer(x, w_router, w_gate, w_up, w_down, ws_gate=None, ws_up=None, ws_down=None, w_sg=None, router_bias=None, *,
+              k, aux_weight=0.0):
+  """The whole MoE layer as ONE custom call each way: (out [T,d], aux_loss [1]) = layer(x; weights).
+
+  Weight orientation is MaxText's (modal/stage2.py:338-345).  Differentiable in x and every weight through
+  `lewi_ffi_moe_bwd`; `aux_weight` adds the gradient of `aux_weight * aux_loss` to the router (aux_loss itself is
+  returned as a value without gradient)."""
   import jax
   import jax.numpy as jnp
-  del tile, sort, factor, probe
   _register()
-  if num_experts:
-    CFG["num_experts"] = int(num_experts)
-  dispatch, combine, permute_rows, ragged_dot_core = _make_vjp_ops()
-  orig_ragged_dot = jax.lax.ragged_dot
+  t, d = x.shape
+  e, _, f = w_gate.shape
+  has_shared, has_gate, has_bias = ws_gate is not None, w_sg is not None, router_bias is not None
+  fs = ws_gate.shape[1] if has_shared else 0
+  core = _core()
+  res_bytes = int(core.lewi_moe_residual_layout(t, d, e, f, int(k), fs, int(has_gate), None))
+  ws_bytes = int(core.lewi_moe_workspace_bytes(t, d, e, f, int(k), fs, int(has_gate)))
+  empty16 = jnp.zeros((0, 0), jnp.bfloat16)
+  empty32 = jnp.zeros((0,), jnp.float32)
+  u8 = lambda n: jax.ShapeDtypeStruct((max(n, 16),), jnp.uint8)
+  like = lambda a, dt=None: jax.ShapeDtypeStruct(a.shape, dt or a.dtype)
+  attrs = dict(k=int(k), has_bias=has_bias, has_gate=has_gate)
 
-  def ragged_dot(lhs, rhs, group_sizes, precision=None, preferred_element_type=None, **kw):
-    # same guard as modal/padded_gmm.py:46-48: other forms go to the original op
-    if lhs.ndim != 2 or rhs.ndim != 3 or kw.get("group_offset") is not None:
-      return orig_ragged_dot(lhs, rhs, group_sizes, precision=precision, preferred_element_type=preferred_element_type, **kw)
-    out = ragged_dot_core(lhs, rhs, group_sizes)
-    return out.astype(preferred_element_type or lhs.dtype)
+  def operands(xv, wr, wg, wu, wd, sg, su, sd, gate, bias):
+    b16 = lambda a: a.astype(jnp.bfloat16)
+    return (b16(xv), wr.astype(jnp.float32), bias.astype(jnp.float32) if has_bias else empty32, b16(wg), b16(wu), b16(wd),
+            b16(sg) if has_shared else empty16, b16(su) if has_shared else empty16, b16(sd) if has_shared else empty16,
+            gate.astype(jnp.float32) if has_gate else empty32)
 
-  if patch_ragged_dot:
-    jax.lax.ragged_dot = ragged_dot
+  def forward(*args):
+    ops = operands(*args)
+    out, aux, residual, _ = jax.ffi.ffi_call(
+        "lewi_ffi_moe_fwd", (jax.ShapeDtypeStruct((t, d), jnp.bfloat16), jax.ShapeDtypeStruct((1,), jnp.float32),
+                             u8(res_bytes), u8(ws_bytes)))(*ops, **attrs)
+    return (out.astype(x.dtype), aux), (ops, residual)
 
-  import maxtext.layers.moe as moe  # pylint: disable=import-outside-toplevel
+  @jax.custom_vjp
+  def layer(*args):
+    return forward(*args)[0]
 
-  def _route_activations(inputs, selected_experts):
-    flat = selected_experts.reshape(-1)
-    order, pos = sort_indices(flat, CFG["num_experts"])
+  def backward(saved, cot):
+    ops, residual = saved
+    g_out, _ = cot
+    xv, wr, bias, wg, wu, wd, sg, su, sd, gate = ops
+    z16 = jax.ShapeDtypeStruct((0, 0), jnp.bfloat16)
+    z32 = jax.ShapeDtypeStruct((0,), jnp.float32)
+    outs = jax.ffi.ffi_call(
+        "lewi_ffi_moe_bwd",
+        (like(xv), like(wr), like(bias) if has_bias else z32, like(wg), like(wu), like(wd),
+         like(sg) if has_shared else z16, like(su) if has_shared else z16, like(sd) if has_shared else z16,
+         like(gate) if has_gate else z32, u8(ws_bytes)))(
+             g_out.astype(jnp.bfloat16), xv, wr, wg, wu, wd, sg, su, sd, gate, residual, aux_grad=float(aux_weight), **attrs)
+    dx, dwr, dbias, dwg, dwu, dwd, dsg, dsu, dsd, dgate, _ = outs
+    grads = (dx.astype(x.dtype), dwr.astype(w_router.dtype), dwg.astype(w_gate.dtype), dwu.astype(w_up.dtype),
+             dwd.astype(w_down.dtype), dsg.astype(ws_gate.dtype) if has_shared else None,
+             dsu.astype(ws_up.dtype) if has_shared else None, dsd.astype(ws_down.dtype) if has_shared else None,
+             dgate.astype(w_sg.dtype) if has_gate else None, dbias.astype(router_bias.dtype) if has_bias else None)
+    return grads
+
+  layer.defvjp(forward, backward)
+  return layer(x, w_router, w_gate, w_up, w_down, ws_gate, ws_up, ws_down, w_sg, router_bias)
+
+
+# ----------------------------------------------------------------------------------- MaxText patch
+
+
+class MaxTextPatch:
+  """The three callables the reference swaps into `maxtext.layers.moe` (0.2.5), kept together with the originals so
+  that the patch can be undone.  Signatures are MaxText's; see modal/moe_permute.py:399-433 for the reference bodies."""
+
+  def __init__(self, moe_module, mode):
+    self.moe, self.mode = moe_module, mode
+    self.saved = {}
+
+  def route_activations(self, inputs, selected_experts):
+    import jax
+    order, pos = sort_indices(selected_experts.reshape(-1), CFG["num_experts"])
     with jax.named_scope("moe_permute_dispatch"):
       return dispatch(inputs, order, pos)
 
-  def _sort_activations(inputs, sort_idx, use_custom_vjp=True):
+  def sort_activations(self, inputs, sort_idx, use_custom_vjp=True):
+    import jax
+    import jax.numpy as jnp
     del use_custom_vjp
     with jax.named_scope("moe_permute_sort"):
       return permute_rows(inputs, sort_idx.astype(jnp.int32))
 
-  moe._route_activations = _route_activations  # pylint: disable=protected-access
-  moe._sort_activations = _sort_activations  # pylint: disable=protected-access
+  def _plain_dropless_case(self, block, intermediate, kw):
+    """Whether this call is the plain dropless case the kernels cover; the special routings (tc_routing, ragged sort
+    with ring of experts, the LLAMA4 block, quantised activations) stay with MaxText's own unpermute."""
+    moe, cfg = self.moe, block.config
+    if kw.get("tc_routing"):
+      return False
+    if cfg.use_ragged_sort and cfg.use_ring_of_experts:
+      return False
+    if cfg.decoder_block == moe.ctypes.DecoderBlockType.LLAMA4:
+      return False
+    return not isinstance(intermediate, moe.qpl.QArray)
 
-  if mode == "full":
-    orig_unpermute = moe.RoutedMoE.unpermute
+  def make_unpermute(self):
+    import jax
+    import jax.numpy as jnp
+    original = self.saved["unpermute"]
+    patch = self
 
     def unpermute(self, intermediate, sorted_selected_experts, weights, batch_size, sequence_length,
                   use_custom_sort_vjp=True, group_sizes=None, topk_argsort_indices=None, **kw):
-      simple = (not kw.get("tc_routing")
-                and not (self.config.use_ragged_sort and self.config.use_ring_of_experts)
-                and self.config.decoder_block != moe.ctypes.DecoderBlockType.LLAMA4
-                and not isinstance(intermediate, moe.qpl.QArray))
-      if not simple:
-        return orig_unpermute(self, intermediate, sorted_selected_experts, weights, batch_size, sequence_length,
-                              use_custom_sort_vjp, group_sizes, topk_argsort_indices, **kw)
+      if not patch._plain_dropless_case(self, intermediate, kw):
+        return original(self, intermediate, sorted_selected_experts, weights, batch_size, sequence_length,
+                        use_custom_sort_vjp, group_sizes, topk_argsort_indices, **kw)
       order = sorted_selected_experts.astype(jnp.int32)
-      m = order.shape[0]
-      pos = jnp.zeros((m,), jnp.int32).at[order].set(jnp.arange(m, dtype=jnp.int32))
+      slots = order.shape[0]
+      pos = jnp.zeros((slots,), jnp.int32).at[order].set(jnp.arange(slots, dtype=jnp.int32))   # inverse permutation
       w = jnp.reshape(weights, (-1, self.num_experts_per_tok)).astype(jnp.float32)
       with jax.named_scope("moe_permute_combine"):
         out = combine(intermediate, order, pos, w)
       return out.reshape(batch_size, sequence_length, -1).astype(self.dtype)
 
-    moe.RoutedMoE.unpermute = unpermute
+    return unpermute
+
+  def apply(self):
+    moe = self.moe
+    self.saved.update(route=moe._route_activations, sort=moe._sort_activations, unpermute=moe.RoutedMoE.unpermute)  # pylint: disable=protected-access
+    moe._route_activations = self.route_activations  # pylint: disable=protected-access
+    moe._sort_activations = self.sort_activations  # pylint: disable=protected-access
+    if self.mode == "full":
+      moe.RoutedMoE.unpermute = self.make_unpermute()
+    return self
+
+  def restore(self):
+    moe = self.moe
+    moe._route_activations, moe._sort_activations = self.saved["route"], self.saved["sort"]  # pylint: disable=protected-access
+    moe.RoutedMoE.unpermute = self.saved["unpermute"]
+
+
+def install(mode="full", num_experts=None, tile=None, sort=None, factor=None, probe=True, patch_ragged_dot=True):
+  """Patch `jax.lax.ragged_dot` and `maxtext.layers.moe` (0.2.5); call BEFORE `import maxtext` is used, like the
+  reference's installers (modal/padded_gmm.py:12).  Same arguments as theirs; `tile`, `sort`, `factor`, `probe` are
+  accepted and ignored (the block size is 128, the sort is a counting sort, the layout is dropless, there is no packing
+  to probe).  Returns the `MaxTextPatch` (its `restore()` undoes the MaxText part)."""
+  import jax
+  del tile, sort, factor, probe
+  _register()
+  if num_experts:
+    CFG["num_experts"] = int(num_experts)
+  if patch_ragged_dot:
+    stock = jax.lax.ragged_dot
+
+    def ragged_dot(lhs, rhs, group_sizes, precision=None, preferred_element_type=None, **kw):
+      # forms the kernels do not cover go to the stock op, as in modal/padded_gmm.py:46-48
+      if lhs.ndim != 2 or rhs.ndim != 3 or kw.get("group_offset") is not None:
+        return stock(lhs, rhs, group_sizes, precision=precision, preferred_element_type=preferred_element_type, **kw)
+      return padded_ragged_dot(lhs, rhs, group_sizes, preferred_element_type=preferred_element_type)
+
+    jax.lax.ragged_dot = ragged_dot
+  import maxtext.layers.moe as moe  # pylint: disable=import-outside-toplevel
+  patch = MaxTextPatch(moe, mode).apply()
   print(f"[lewi_surge_b200] installed mode={mode} block={BLOCK} num_experts={CFG['num_experts']} "
         f"(sm_100a kernels behind jax.ffi)", flush=True)
+  return patch
