@@ -281,6 +281,33 @@ int lewi_grouped_gemm_dx(void* stream, const void* dgu, const void* w_gate, cons
                          const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
 
 /* ------------------------------------------------------------------------------------------------
+ * Sequence mixing beside the MoE layer: the causal depthwise 1-D convolution of the Gated-DeltaNet block.
+ * Replaces the reference's shift-add rewrite of flax `nnx.Conv(padding="CAUSAL", feature_group_count=C)`
+ * (modal/fast_conv.py:14-31):  y[b,t,c] = sum_{j<K} w[j,c] * x[b, t-(K-1)+j, c], inputs before t = 0 are zero.
+ * x, y, g, dx bf16 [B,T,C]; w bf16 [K,1,C] (flax kernel layout, read as [K,C]); K <= 8; C a multiple of 8.
+ * Products and sums in f32, one rounding at the end.  The backward call gives dx (the same convolution run
+ * backwards in time over g) and/or dw [K,C] (dw_dtype; needs lewi_causal_conv1d_workspace_bytes of scratch;
+ * partial sums are added in a fixed order).
+ * ---------------------------------------------------------------------------------------------- */
+int64_t lewi_causal_conv1d_workspace_bytes(int B, int T, int C, int K);
+int lewi_causal_conv1d_fwd(void* stream, const void* x, const void* w, void* y, int B, int T, int C, int K);
+int lewi_causal_conv1d_bwd(void* stream, const void* x, const void* w, const void* g, void* dx, void* dw,
+                           int dw_dtype, void* workspace, int64_t workspace_bytes, int B, int T, int C, int K);
+
+/* Chunked gated delta rule, forward: replaces the reference's `fast_chunk_gated_delta_rule`
+ * (modal/gdn_fast.py:37-113) for compute_dtype = bfloat16, chunk size 64, no context parallelism.
+ *   per (batch, head):  h <- h*exp(g_t) + k_t (x) beta_t*(v_t - k_t^T h),   o_t = (q_t / sqrt(K))^T h
+ * q, k bf16 [B,S,H,K]; v, o bf16 [B,S,H,V]; g f32 [B,S,H] (log decay, <= 0); beta bf16 [B,S,H];
+ * h0 f32 [B,H,K,V] or null (zero state); h_final f32 [B,H,K,V] or null.  K <= 128 and a multiple of 8, V a
+ * multiple of 8.  S need not be a multiple of 64 (the tail is padded with empty tokens, as the reference pads).
+ * workspace: lewi_gdn_chunk_workspace_bytes(...) bytes (per-chunk u, w, in-chunk attention and cumulative decay).
+ * Forward only: the reference differentiates this function through JAX autodiff; no backward kernel exists here. */
+int64_t lewi_gdn_chunk_workspace_bytes(int B, int S, int H, int K, int V);
+int lewi_gdn_chunk_fwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
+                       const float* h0, void* o, float* h_final, void* workspace, int64_t workspace_bytes, int B,
+                       int S, int H, int K, int V);
+
+/* ------------------------------------------------------------------------------------------------
  * The whole layer in two calls.  lewi_moe_fwd / lewi_moe_bwd queue the complete launch sequence of the MoE layer of
  * the MaxText `qwen3_5` block as the reference patches it: router (softmax -> top-k -> renormalise,
  * configs/stage1.yml:33-41) -> `_route_activations` (modal/moe_permute.py:399-404) -> the three `ragged_dot`s of the

@@ -50,6 +50,11 @@ SIGNATURES = {
     "lewi_grouped_gemm_gateup_swiglu": (c_int, [P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dh_dswiglu": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dx": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_causal_conv1d_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int]),
+    "lewi_causal_conv1d_fwd": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int]),
+    "lewi_causal_conv1d_bwd": (c_int, [P, P, P, P, P, P, c_int, P, c_int64, c_int, c_int, c_int, c_int]),
+    "lewi_gdn_chunk_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int]),
+    "lewi_gdn_chunk_fwd": (c_int, [P, P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int, c_int, c_int]),
     "lewi_moe_residual_layout": (c_int64, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int, P]),
     "lewi_moe_workspace_bytes": (c_int64, [c_int64, c_int, c_int, c_int, c_int, c_int, c_int]),
     "lewi_moe_router_prepared_bytes": (c_int64, [c_int, c_int]),

@@ -6,6 +6,7 @@
 #include "moe_layer.cuh"
 #include "router_gemm.cuh"
 #include "routing.cuh"
+#include "seqmix.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -979,6 +980,112 @@ int lewi_set_exchange_sms(int n) {
   return LEWI_OK;
 }
 
+// ------------------------------------------------------------------------------------------------ sequence mixing
+
+#define LEWI_DISPATCH_TAPS(K_VALUE, ...)                    \
+  switch (K_VALUE) {                                        \
+    case 1: { constexpr int KT = 1; __VA_ARGS__; } break;   \
+    case 2: { constexpr int KT = 2; __VA_ARGS__; } break;   \
+    case 3: { constexpr int KT = 3; __VA_ARGS__; } break;   \
+    case 4: { constexpr int KT = 4; __VA_ARGS__; } break;   \
+    case 5: { constexpr int KT = 5; __VA_ARGS__; } break;   \
+    case 6: { constexpr int KT = 6; __VA_ARGS__; } break;   \
+    case 7: { constexpr int KT = 7; __VA_ARGS__; } break;   \
+    default: { constexpr int KT = 8; __VA_ARGS__; } break;  \
+  }
+
+int64_t lewi_causal_conv1d_workspace_bytes(int B, int T, int C, int K) {
+  if (B <= 0 || T <= 0 || C <= 0 || K <= 0) return LEWI_ERR_ARG;
+  const int64_t runs = (T + kConvRun - 1) / kConvRun;
+  return ((int64_t)B * runs * K * C * 4 + 255) / 256 * 256;
+}
+
+int lewi_causal_conv1d_fwd(void* stream, const void* x, const void* w, void* y, int B, int T, int C, int K) {
+  if (!x || !w || !y || B <= 0 || T <= 0 || C <= 0 || K <= 0) return LEWI_ERR_ARG;
+  if (K > kConvMaxTaps) return LEWI_ERR_LIMIT;
+  if (C % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(y)) return LEWI_ERR_SHAPE;
+  const dim3 grid((unsigned)((C / 8 + kConvThreads - 1) / kConvThreads), (unsigned)((T + kConvRun - 1) / kConvRun), (unsigned)B);
+  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w);
+  __nv_bfloat16* yb = reinterpret_cast<__nv_bfloat16*>(y);
+  cudaStream_t st = as_stream(stream);
+  LEWI_DISPATCH_TAPS(K, (causal_conv1d_kernel<false, KT><<<grid, kConvThreads, 0, st>>>(xb, wb, yb, B, T, C)));
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+int lewi_causal_conv1d_bwd(void* stream, const void* x, const void* w, const void* g, void* dx, void* dw, int dw_dtype,
+                           void* workspace, int64_t workspace_bytes, int B, int T, int C, int K) {
+  if (!x || !w || !g || (!dx && !dw) || B <= 0 || T <= 0 || C <= 0 || K <= 0) return LEWI_ERR_ARG;
+  if (dw_dtype != LEWI_BF16 && dw_dtype != LEWI_F32) return LEWI_ERR_ARG;
+  if (K > kConvMaxTaps) return LEWI_ERR_LIMIT;
+  if (C % 8 != 0 || !aligned16(x) || !aligned16(w) || !aligned16(g) || !aligned16(dx) || !aligned16(workspace))
+    return LEWI_ERR_SHAPE;
+  const int runs = (T + kConvRun - 1) / kConvRun;
+  if (dw != nullptr && (workspace == nullptr || workspace_bytes < (int64_t)B * runs * K * C * 4)) return LEWI_ERR_WORKSPACE;
+  cudaStream_t st = as_stream(stream);
+  const dim3 grid((unsigned)((C / 8 + kConvThreads - 1) / kConvThreads), (unsigned)runs, (unsigned)B);
+  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* wb = reinterpret_cast<const __nv_bfloat16*>(w);
+  const __nv_bfloat16* gb = reinterpret_cast<const __nv_bfloat16*>(g);
+  if (dx != nullptr) {
+    __nv_bfloat16* dxb = reinterpret_cast<__nv_bfloat16*>(dx);
+    LEWI_DISPATCH_TAPS(K, (causal_conv1d_kernel<true, KT><<<grid, kConvThreads, 0, st>>>(gb, wb, dxb, B, T, C)));
+    LEWI_CHECK_LAUNCH();
+  }
+  if (dw != nullptr) {
+    float* partial = reinterpret_cast<float*>(workspace);
+    LEWI_DISPATCH_TAPS(K, (causal_conv1d_dw_kernel<KT><<<grid, kConvThreads, 0, st>>>(xb, gb, partial, B, T, C)));
+    LEWI_CHECK_LAUNCH();
+    const int n = K * C;
+    conv_dw_reduce_kernel<<<(n + 255) / 256, 256, 0, st>>>(partial, B * runs, n,
+                                                          dw_dtype == LEWI_BF16 ? reinterpret_cast<__nv_bfloat16*>(dw) : nullptr,
+                                                          dw_dtype == LEWI_F32 ? reinterpret_cast<float*>(dw) : nullptr);
+    LEWI_CHECK_LAUNCH();
+  }
+  return LEWI_OK;
+}
+
+int64_t lewi_gdn_chunk_workspace_bytes(int B, int S, int H, int K, int V) {
+  if (B <= 0 || S <= 0 || H <= 0 || K <= 0 || V <= 0) return LEWI_ERR_ARG;
+  const int64_t n = (S + kGdnChunk - 1) / kGdnChunk;
+  return ((int64_t)B * n * H * gdn_chunk_ws_bytes(K, V) + 255) / 256 * 256;
+}
+
+int lewi_gdn_chunk_fwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
+                       const float* h0, void* o, float* h_final, void* workspace, int64_t workspace_bytes, int B, int S,
+                       int H, int K, int V) {
+  if (!q || !k || !v || !g || !beta || !o || !workspace || B <= 0 || S <= 0 || H <= 0 || K <= 0 || V <= 0) return LEWI_ERR_ARG;
+  if (K > kGdnMaxDim || V > 4 * kGdnMaxDim) return LEWI_ERR_LIMIT;
+  if (K % 8 != 0 || V % 8 != 0) return LEWI_ERR_SHAPE;
+  if (workspace_bytes < lewi_gdn_chunk_workspace_bytes(B, S, H, K, V)) return LEWI_ERR_WORKSPACE;
+  GdnDims D{B, S, H, K, V, (S + kGdnChunk - 1) / kGdnChunk};
+  const size_t smem_a = gdn_prep_smem_bytes(K, V), smem_b = gdn_scan_smem_bytes(K);
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LEWI_ERR_CUDA;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gdn_chunk_prep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gdn_chunk_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return LEWI_ERR_CUDA;
+    }
+    attr_set[dev] = true;
+  }
+  if (smem_a > 200 * 1024 || smem_b > 200 * 1024) return LEWI_ERR_LIMIT;
+  cudaStream_t st = as_stream(stream);
+  const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(k);
+  gdn_chunk_prep_kernel<<<dim3((unsigned)D.N, (unsigned)H, (unsigned)B), kGdnThreads, smem_a, st>>>(
+      qb, kb, reinterpret_cast<const __nv_bfloat16*>(v), g, reinterpret_cast<const __nv_bfloat16*>(beta),
+      reinterpret_cast<uint8_t*>(workspace), D);
+  LEWI_CHECK_LAUNCH();
+  gdn_chunk_scan_kernel<<<dim3((unsigned)((V + kGdnVBlock - 1) / kGdnVBlock), (unsigned)H, (unsigned)B), kGdnThreads, smem_b, st>>>(
+      qb, kb, reinterpret_cast<const uint8_t*>(workspace), h0, reinterpret_cast<__nv_bfloat16*>(o), h_final, D);
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
 // ------------------------------------------------------------------------------------------------ whole layer
 
 int64_t lewi_moe_residual_layout(int64_t T, int d, int E, int f, int k, int fs, int has_gate, int64_t* offsets_host) {
@@ -1101,6 +1208,8 @@ int lewi_moe_fwd(void* stream, void* side_stream, const void* x, const float* w_
     LEWI_TRY(lewi_router_logits(stream, x, w_router, router_bias, logits, T, d, E, nullptr, 0));
   }
   moe::mark("router_logits", stream);
+  {
+  moe::Range nvtx_sort("moe_permute_sort");
   LEWI_TRY(lewi_router_topk(stream, logits, T, E, k, moe::kBlock, topk_idx, topk_w,
                             reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_COUNTS)),
                             reinterpret_cast<int32_t*>(res(LEWI_MOE_RES_OFFSETS)), pad_offsets, block_expert, n_blocks,
@@ -1109,9 +1218,13 @@ int lewi_moe_fwd(void* stream, void* side_stream, const void* x, const float* w_
                             reinterpret_cast<float*>(res(LEWI_MOE_RES_PROBS_SUM)), aux_loss, Wk + W.route,
                             lewi_route_workspace_bytes(D.M, E)));
   moe::mark("router_topk", stream);
+  }
+  {
   // dispatch: padded row r holds token row_slot[r] / k (zero row where row_slot[r] < 0), written in token order
+  moe::Range nvtx_dispatch("moe_permute_dispatch");
   LEWI_TRY(lewi_dispatch_rows(stream, x, pad_pos, row_slot, res(LEWI_MOE_RES_XS), T, k, d, D.Mpad, n_blocks, moe::kBlock));
   moe::mark("dispatch_gather", stream);
+  }
   // h carries the router weight of its row, so the down projection yields weighted outputs
   LEWI_TRY(lewi_grouped_gemm_gateup_swiglu_scaled(stream, res(LEWI_MOE_RES_XS), row_slot, topk_w, w_gate, w_up,
                                                   res(LEWI_MOE_RES_GU), res(LEWI_MOE_RES_H), block_expert, n_blocks,
@@ -1126,6 +1239,7 @@ int lewi_moe_fwd(void* stream, void* side_stream, const void* x, const float* w_
       return LEWI_ERR_CUDA;
   }
   // combine: out[t] = sum_j ys[pad_pos[t,j]] + shared[t]
+  moe::Range nvtx_combine("moe_permute_combine");
   LEWI_TRY(lewi_gather_reduce(stream, Wk + W.ys, pad_pos, nullptr, ysh, nullptr, out, T, k, d, LEWI_BF16, LEWI_BF16,
                               D.Mpad));
   moe::mark("combine_gather_reduce", stream);

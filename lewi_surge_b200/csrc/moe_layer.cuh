@@ -6,6 +6,8 @@
 // `ragged_dot`s -> `unpermute` (modal/moe_permute.py:399-433, modal/padded_gmm.py:45-69) and their gradients.
 #pragma once
 
+#include <nvtx3/nvToolsExt.h>
+
 #include "common.cuh"
 #include "gather.cuh"
 
@@ -198,6 +200,16 @@ inline Events* events() {
   }
   return ev[dev].ok ? &ev[dev] : nullptr;
 }
+
+// NVTX range on the host thread around the launches of one stage, named like the reference's profiler scopes
+// (`jax.named_scope("moe_permute_dispatch" / "moe_permute_sort" / "moe_permute_combine")`,
+// modal/moe_permute.py:403,408,431), so that timelines of the two implementations line up.
+struct Range {
+  explicit Range(const char* name) { nvtxRangePushA(name); }
+  ~Range() { nvtxRangePop(); }
+  Range(const Range&) = delete;
+  Range& operator=(const Range&) = delete;
+};
 
 typedef void (*MarkFn)(const char*, void*);
 inline MarkFn& mark_fn() {

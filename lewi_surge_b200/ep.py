@@ -309,7 +309,7 @@ class ExpertParallelP2P:
   """
 
   BARRIER_TIMEOUT_MS = 4000
-  DEFAULT_EXCHANGE_SMS = 16
+  DEFAULT_EXCHANGE_SMS = 0    # thin exchange CTAs beside the GEMM CTAs; > 0 gives the exchange that many SMs of its own
 
   def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None, phases=None, sync="flags",
                exchange_threads=(0, 0), dw_down_last=True, exchange_sms=None):

@@ -4,3 +4,4 @@ Nothing in the product package imports this.  Only the tests, the smoke check an
 the CPU-baseline leg of the benchmark may call it, and only as the checker.
 """
 from .moe_oracle import *  # noqa: F401,F403
+from .seqmix_oracle import *  # noqa: F401,F403

@@ -103,7 +103,7 @@ def _ragged_dot(lhs, rhs, group_sizes, **kw):
 def install():
   jnp = types.ModuleType("jax.numpy")
   for name in ("zeros", "ones", "arange", "cumsum", "concatenate", "minimum", "maximum", "where", "sum", "tanh",
-               "take_along_axis", "array_equal", "empty", "reshape", "abs", "exp"):
+               "take_along_axis", "array_equal", "empty", "reshape", "abs", "exp", "pad"):
     setattr(jnp, name, _wrap(getattr(np, name)))
   jnp.take, jnp.argsort, jnp.einsum, jnp.searchsorted = _take, _argsort, _einsum, _searchsorted
   jnp.float32, jnp.int32, jnp.uint32, jnp.uint16, jnp.float16, jnp.bfloat16 = (np.float32, np.int32, np.uint32,

@@ -128,6 +128,30 @@ def test_barrier_alone_on_one_gpu(cuda):
   assert lib.lewi_ep_barrier(st(), peers, ptr(flags), None, 0, 1, 1000) != 0           # epoch counter is required
 
 
+def test_barrier_gives_up_after_its_time_limit_and_the_context_stays_usable(cuda):
+  """A peer that never arrives: the barrier's wait is bounded, so after the limit (5 ms here) the kernel records
+  LEWI_STATUS_WAIT_TIMEOUT and returns normally.  The "peer" is a second flag array on the same GPU that nothing
+  writes; no kernel waits for another launch.  The next barrier, whose peer flag is already set, passes cleanly."""
+  import time
+  from lewi_surge_b200 import _lib
+  lib, ptr, st, check = _lib.load(), _lib.ptr, _lib.stream, _lib.check
+  mine = torch.zeros(2, dtype=torch.int32, device=cuda)      # flags written by rank 0 (myself) and by rank 1
+  theirs = torch.zeros(2, dtype=torch.int32, device=cuda)    # rank 1's flag array: receives my epoch, is never read
+  epoch = torch.zeros(1, dtype=torch.int32, device=cuda)
+  peers = (ctypes.c_void_p * 2)(mine.data_ptr(), theirs.data_ptr())
+  _lib.last_status()
+  t0 = time.perf_counter()
+  check(lib.lewi_ep_barrier(st(), peers, ptr(mine), ptr(epoch), 0, 2, 5), "barrier")
+  assert _lib.last_status() == _lib.STATUS_WAIT_TIMEOUT          # synchronises: the kernel has returned
+  assert time.perf_counter() - t0 < 2.0
+  assert int(epoch.item()) == 1 and int(theirs[0].item()) == 1 and int(mine[0].item()) == 1 and int(mine[1].item()) == 0
+  mine[1] = 2                                                    # "rank 1" has reached epoch 2
+  check(lib.lewi_ep_barrier(st(), peers, ptr(mine), ptr(epoch), 0, 2, 1000), "barrier")
+  assert _lib.last_status() == 0 and int(epoch.item()) == 2
+  # and ordinary work still runs on the same context
+  assert float((torch.ones(8, device=cuda) * 2).sum()) == 16.0
+
+
 def test_receive_buffer_too_small_is_reported_not_overrun(cuda):
   """A plan that needs more rows than the buffers hold raises LEWI_STATUS_EP_OVERFLOW; rows past the end are dropped."""
   from lewi_surge_b200 import _lib, layer
