@@ -243,8 +243,6 @@ def main():
   ap.add_argument("--ep-sync", choices=["flags", "nccl"], default="flags", help="how the exchange orders the ranks")
   ap.add_argument("--ep-dw-down-first", action="store_true", help="A/B switch: order of the two weight-gradient GEMMs")
   ap.add_argument("--ep-threads", default="0,0", help="CTA size of the exchange kernels: forward,backward (0: largest)")
-  ap.add_argument("--ep-exchange-sms", type=int, default=None,
-                  help="SMs the exchange kernels own during a pass (0: thin exchange CTAs beside every GEMM CTA)")
   ap.add_argument("--ep-phases", type=int, default=None, help="ranges of local experts the exchange is pipelined over")
   ap.add_argument("--preload-s", type=float, default=2.0,
                   help="seconds of untimed replays right before the timed window (clocks and power settle)")
@@ -288,7 +286,7 @@ def main():
       runner = ep.ExpertParallelP2P(w, c["k"], c["E"], c["T"], c["d"], dist.group.WORLD, capacity=args.ep_capacity,
                                     phases=args.ep_phases, sync=args.ep_sync,
                                     exchange_threads=tuple(int(v) for v in args.ep_threads.split(",")),
-                                    dw_down_last=not args.ep_dw_down_first, exchange_sms=args.ep_exchange_sms)
+                                    dw_down_last=not args.ep_dw_down_first)
     else:
       runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
     step_fn = lambda: runner.step(x, dout)
@@ -612,8 +610,7 @@ def ep_parity_check(args, c, rank, world, device, torch, dist, tokens=1024):
   w = layer.MoEWeights(torch.from_numpy(full["w_router"]).to(device), bf(full["w_gate"][lo:hi]), bf(full["w_up"][lo:hi]),
                        bf(full["w_down"][lo:hi]), bf(full["ws_gate"]), bf(full["ws_up"]), bf(full["ws_down"]),
                        torch.from_numpy(bias).to(device) if bias is not None else None)
-  runner = ep.ExpertParallelP2P(w, k, E, tokens, d, dist.group.WORLD, phases=args.ep_phases, sync=args.ep_sync,
-                                exchange_sms=args.ep_exchange_sms)
+  runner = ep.ExpertParallelP2P(w, k, E, tokens, d, dist.group.WORLD, phases=args.ep_phases, sync=args.ep_sync)
   sl = slice(rank * tokens, (rank + 1) * tokens)
   out, g = runner.step(bf(full["x"][sl]), bf(full["dout"][sl]))
   status = _lib.last_status()

@@ -418,9 +418,9 @@ int lewi_ep_plan(void* stream, const int32_t* counts_all, int G, int E, int me, 
  * (me << 28 | slot, i32) to peers_ret[owner][row] (optional).  Only the rows of local experts (e mod E/G) in
  * [el_lo, el_hi) are moved: launching once per range of local experts lets the owners start on the first
  * range while the next one is still in flight.  M = T*k < 2^28.  The kernel is one small CTA per SM that
- * fits beside a resident grouped-GEMM CTA, so it overlaps GEMMs running on another stream (or, after
- * lewi_set_exchange_sms(n), n CTAs that own their SMs).  threads = CTA size (a multiple of 32 up to 256, or up to
- * 1024 for the SM-owning form; 0 = the largest): fewer warps keep fewer remote stores in flight per SM. */
+ * fits beside a resident grouped-GEMM CTA, so it overlaps GEMMs running on another stream.  threads = CTA size
+ * (a multiple of 32 up to 256; 0 = 256): fewer warps keep fewer remote stores in flight per SM, which slows the
+ * transfer and disturbs a GEMM on the same SM less. */
 int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const int32_t* flat_expert,
                       const int32_t* offsets, const int32_t* dst_base, const float* slot_w,
                       void* const* peers_rows_host, void* const* peers_w_host, void* const* peers_ret_host, int me,
@@ -448,13 +448,6 @@ int lewi_ep_zero_pad(void* stream, void* buf, int32_t* ret, const int32_t* valid
  * the GEMMs; 0 (default): a GEMM CTA has its SM to itself, which measured faster when nothing needs to overlap.
  * Host-side switch read at launch time; not thread-safe against concurrent launches. */
 int lewi_set_sm_sharing(int on);
-
-/* n > 0 (even, at most half of the GPU): the grouped-GEMM kernels launched from now on leave n SMs free, and
- * lewi_ep_push_rows / lewi_ep_return_rows run as n "fat" CTAs (pairs of up to 1024 threads) that each take a whole
- * SM, instead of one thin CTA beside every GEMM CTA: the exchange then costs the GEMMs n of the GPU's SMs but none of
- * the issue slots and memory pipes on the SMs they keep.  0 (default): thin exchange CTAs, GEMM grids cover the GPU.
- * Host-side switch read at launch time; not thread-safe against concurrent launches. */
-int lewi_set_exchange_sms(int n);
 
 /* All-gather of a small table by peer stores: src i32 [n] goes to elements [dst_offset, dst_offset+n) of every
  * peer's buffer (used for the expert histograms: dst_offset = me*E).  Follow it with lewi_ep_barrier. */

@@ -73,7 +73,6 @@ SIGNATURES = {
     "lewi_ep_return_rows": (c_int, [P, P, P, P, P, c_int, c_int, P, P, c_int, c_int, c_int, c_int64, c_int64, c_int]),
     "lewi_ep_zero_pad": (c_int, [P, P, P, P, P, c_int, c_int, c_int64]),
     "lewi_set_sm_sharing": (c_int, [c_int]),
-    "lewi_set_exchange_sms": (c_int, [c_int]),
     "lewi_ep_put_i32": (c_int, [P, P, P, c_int64, c_int, c_int]),
     "lewi_ep_barrier": (c_int, [P, P, P, P, c_int, c_int, c_int64]),
     "lewi_set_cta_pair": (c_int, [c_int]),

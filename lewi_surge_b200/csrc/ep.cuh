@@ -8,14 +8,13 @@
 // Dispatch is then one gather kernel whose stores go straight into the owners' buffers, together with a
 // return address per row (source rank and slot); the owners send expert outputs back the same way, with
 // stores into the source's slot-ordered buffer, where the combine is a sum over k consecutive rows.
-// Stores only cross NVLink (a store holds no register while in flight, a load does).  The two bulk kernels come
-// in two shapes that overlap a range's transfer with the GEMMs of another range in different ways:
-//   thin   one CTA of <= 256 threads and at most 40 registers per SM, no shared memory: it fits on an SM beside a
-//          resident grouped-GEMM CTA (which then shares its issue slots and memory pipes with it);
-//   fat    a few CTA pairs of 1024 threads that each claim a whole SM (they ask for most of its shared memory, so
-//          no GEMM CTA can join them), while the GEMM grids leave exactly that many SMs free.
-// Ordering between ranks is either a stream-ordered collective issued by the host code or the flag barrier
-// below.  Plain loads/stores only (no multimem, no TMA).
+// Stores only cross NVLink (a store holds no register while in flight, a load does), and the kernels
+// are "thin": one CTA of 256 threads and at most 40 registers per SM, no shared memory, so that a CTA of
+// these fits on an SM beside a resident grouped-GEMM CTA whichever of the two arrives first; transfers of one
+// range of experts then overlap the GEMMs of another.  (Giving the exchange 16-32 SMs of its own, with the GEMM
+// grids shrunk by as many, was measured slower in every arrangement tried.)  Ordering between ranks is either a
+// stream-ordered collective issued by the host code or the flag barrier below.  Plain loads/stores only (no
+// multimem, no TMA).
 #pragma once
 
 #include "common.cuh"
@@ -107,38 +106,9 @@ __device__ __forceinline__ unsigned long long ep_timer_ns() {
   return t;
 }
 
-constexpr int kEpThreads = 256;      // thin: 8 warps x 40 registers, what is left beside a GEMM CTA (12 warps measured no faster)
-constexpr int kEpFatThreads = 512;   // fat: the CTA has its SM to itself; 16 warps x 4 rows of 2 KB in flight
-constexpr int kEpFatSmem = 160 * 1024;   // dynamic shared memory a fat CTA asks for (unused): keeps GEMM CTAs off its SM
+constexpr int kEpThreads = 256;      // 8 warps x 40 registers: what is left beside a GEMM CTA (12 warps measured no faster)
 constexpr int kEpChunk = 4;          // 16-byte vectors per lane and pass
 constexpr int kEpSlotBits = 28;      // return address = source rank << 28 | slot
-
-// ROWS rows at once (null source = no row): all loads of a pass are issued before the first store, so a warp keeps
-// ROWS x kEpChunk x 512 bytes in flight.
-template <int ROWS>
-__device__ __forceinline__ void ep_copy_rows(const __nv_bfloat16* const (&src)[ROWS], __nv_bfloat16* const (&dst)[ROWS],
-                                             int nvec, int lane) {
-  for (int c0 = 0; c0 < nvec; c0 += kEpChunk * kWarp) {
-    uint4 v[ROWS][kEpChunk];
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-#pragma unroll
-      for (int c = 0; c < kEpChunk; ++c) {
-        const int vi = c0 + lane + c * kWarp;
-        v[r][c] = make_uint4(0, 0, 0, 0);
-        if (src[r] != nullptr && vi < nvec) v[r][c] = ld_nc_v4(reinterpret_cast<const uint4*>(src[r]) + vi);
-      }
-    }
-#pragma unroll
-    for (int r = 0; r < ROWS; ++r) {
-#pragma unroll
-      for (int c = 0; c < kEpChunk; ++c) {
-        const int vi = c0 + lane + c * kWarp;
-        if (src[r] != nullptr && vi < nvec) st_v4(reinterpret_cast<uint4*>(dst[r]) + vi, v[r][c]);
-      }
-    }
-  }
-}
 
 __device__ __forceinline__ void ep_copy_row(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst,
                                             int nvec, int lane) {
@@ -167,8 +137,7 @@ __device__ __forceinline__ void ep_copy_row(const __nv_bfloat16* __restrict__ sr
 // then the whole warp copies the 32 rows one after the other.  Consecutive rows of a batch go to consecutive
 // destinations, starting at this rank's right-hand neighbour, so at any moment every rank is sending to all the
 // others and no destination's ingress port is everybody's target.
-template <bool FAT>
-__global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6) ep_push_rows_kernel(
+__global__ void __launch_bounds__(kEpThreads, 6) ep_push_rows_kernel(
     const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ order, const int32_t* __restrict__ flat_expert,
     const int32_t* __restrict__ offsets, const int32_t* __restrict__ dst_base, const float* __restrict__ slot_w,
     PeerPtrs peer_rows, PeerPtrs peer_w, PeerPtrs peer_ret, long long m, int k, int d, int El, int G,
@@ -211,28 +180,12 @@ __global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6)
         }
       }
     }
-    if constexpr (FAT) {
-      for (int i = 0; i < kWarp; i += 4) {
-        const __nv_bfloat16* src[4];
-        __nv_bfloat16* dst[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int r = __shfl_sync(0xffffffffu, my_r, i + q);
-          const long long tok = __shfl_sync(0xffffffffu, my_tok, i + q);
-          const long long row = __shfl_sync(0xffffffffu, my_row, i + q);
-          src[q] = r < 0 ? nullptr : x + tok * d;
-          dst[q] = r < 0 ? nullptr : reinterpret_cast<__nv_bfloat16*>(peer_rows.p[r]) + row * d;
-        }
-        ep_copy_rows<4>(src, dst, nvec, lane);
-      }
-    } else {
-      for (int i = 0; i < kWarp; ++i) {
-        const int r = __shfl_sync(0xffffffffu, my_r, i);
-        const long long tok = __shfl_sync(0xffffffffu, my_tok, i);
-        const long long row = __shfl_sync(0xffffffffu, my_row, i);
-        if (r < 0) continue;
-        ep_copy_row(x + tok * d, reinterpret_cast<__nv_bfloat16*>(peer_rows.p[r]) + row * d, nvec, lane);
-      }
+    for (int i = 0; i < kWarp; ++i) {
+      const int r = __shfl_sync(0xffffffffu, my_r, i);
+      const long long tok = __shfl_sync(0xffffffffu, my_tok, i);
+      const long long row = __shfl_sync(0xffffffffu, my_row, i);
+      if (r < 0) continue;
+      ep_copy_row(x + tok * d, reinterpret_cast<__nv_bfloat16*>(peer_rows.p[r]) + row * d, nvec, lane);
     }
   }
 }
@@ -241,8 +194,7 @@ __global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6)
 // `slot` of the source rank's slot-ordered buffer, and (optionally) its `parts` routing-weight gradient
 // pieces to the source's [slots, parts] buffer.  Padding rows carry the return address -1.  Same batching as
 // the push kernel: a lane reads one row's return address (and sends its pieces), the warp then copies 32 rows.
-template <bool FAT>
-__global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6) ep_return_rows_kernel(
+__global__ void __launch_bounds__(kEpThreads, 6) ep_return_rows_kernel(
     const __nv_bfloat16* __restrict__ rows, const float* __restrict__ pieces, const int32_t* __restrict__ ret,
     const int32_t* __restrict__ pad_offsets, int el_lo, int el_hi, PeerPtrs peer_slot_rows, PeerPtrs peer_slot_pieces,
     int d, int parts, int G, long long m_slots, long long rmax_pad) {
@@ -271,26 +223,11 @@ __global__ void __launch_bounds__(FAT ? kEpFatThreads : kEpThreads, FAT ? 1 : 6)
       }
     }
     if (rows == nullptr) continue;
-    if constexpr (FAT) {
-      for (int i = 0; i < kWarp; i += 4) {
-        const __nv_bfloat16* from[4];
-        __nv_bfloat16* to[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int src = __shfl_sync(0xffffffffu, my_src, i + q);
-          const long long slot = __shfl_sync(0xffffffffu, my_slot, i + q);
-          from[q] = src < 0 ? nullptr : rows + (base + i + q) * d;
-          to[q] = src < 0 ? nullptr : reinterpret_cast<__nv_bfloat16*>(peer_slot_rows.p[src]) + slot * d;
-        }
-        ep_copy_rows<4>(from, to, nvec, lane);
-      }
-    } else {
-      for (int i = 0; i < kWarp; ++i) {
-        const int src = __shfl_sync(0xffffffffu, my_src, i);
-        const long long slot = __shfl_sync(0xffffffffu, my_slot, i);
-        if (src < 0) continue;
-        ep_copy_row(rows + (base + i) * d, reinterpret_cast<__nv_bfloat16*>(peer_slot_rows.p[src]) + slot * d, nvec, lane);
-      }
+    for (int i = 0; i < kWarp; ++i) {
+      const int src = __shfl_sync(0xffffffffu, my_src, i);
+      const long long slot = __shfl_sync(0xffffffffu, my_slot, i);
+      if (src < 0) continue;
+      ep_copy_row(rows + (base + i) * d, reinterpret_cast<__nv_bfloat16*>(peer_slot_rows.p[src]) + slot * d, nvec, lane);
     }
   }
 }

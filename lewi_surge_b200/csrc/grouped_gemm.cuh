@@ -898,12 +898,6 @@ inline bool& sm_sharing() {
 }
 constexpr size_t SMEM_EXCLUSIVE_PAD = 1024;
 
-// SMs the GEMM grids leave free for "fat" exchange CTAs of another stream (0: the grids cover the GPU).
-inline int& reserved_sms() {
-  static int n = 0;
-  return n;
-}
-
 template <int MAJOR, int EPI, bool PAIR>
 inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, Args a,
                   long long max_tiles, const CUtensorMap& tc, const CUtensorMap& td) {
@@ -928,8 +922,7 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
   a.idesc = ptx::instr_desc_bf16(PAIR ? 2 * BM : BM, BN, a_mn ? 1 : 0, b_mn ? 1 : 0);
   if (max_tiles <= 0) return LEWI_OK;
   const size_t smem = SMEM_BYTES + (sm_sharing() ? 0 : SMEM_EXCLUSIVE_PAD);
-  long long grid = num_sms() - reserved_sms();
-  if (grid < 2) grid = 2;
+  long long grid = num_sms();
   if constexpr (PAIR) {
     grid &= ~1LL;
     if (grid > 2 * max_tiles) grid = 2 * max_tiles;

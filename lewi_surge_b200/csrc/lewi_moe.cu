@@ -797,39 +797,6 @@ inline void prefer_shared_carveout(const void* kern, bool* done) {
   done[dev] = true;
 }
 
-// "Fat" exchange kernels: CTA pairs (clusters of two, so that they take whole SM pairs and leave the GEMM kernels'
-// CTA pairs intact) of up to 1024 threads that claim their SM through a large, unused shared-memory request.
-inline int ep_fat_ctas() { return gg::reserved_sms() & ~1; }
-
-inline bool fat_launch_config(const void* kern, int ctas, int threads, cudaStream_t st, cudaLaunchConfig_t& cfg,
-                              cudaLaunchAttribute* attr) {
-  static bool set[64][2] = {{false}};
-  static const void* seen[2] = {nullptr, nullptr};
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
-  int slot = seen[0] == kern ? 0 : (seen[1] == kern ? 1 : (seen[0] == nullptr ? 0 : 1));
-  seen[slot] = kern;
-  if (!set[dev][slot]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kEpFatSmem) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return false;
-    }
-    set[dev][slot] = true;
-  }
-  cfg = cudaLaunchConfig_t{};
-  cfg.gridDim = dim3((unsigned)ctas);
-  cfg.blockDim = dim3((unsigned)threads);
-  cfg.dynamicSmemBytes = kEpFatSmem;
-  cfg.stream = st;
-  attr[0].id = cudaLaunchAttributeClusterDimension;
-  attr[0].val.clusterDim.x = 2;
-  attr[0].val.clusterDim.y = 1;
-  attr[0].val.clusterDim.z = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = 1;
-  return true;
-}
-
 inline bool fill_peers(PeerPtrs& pp, void* const* host, int G, bool required) {
   for (int i = 0; i < kMaxPeers; ++i) pp.p[i] = nullptr;
   if (host == nullptr) return !required;
@@ -866,32 +833,18 @@ int lewi_ep_push_rows(void* stream, const void* x, const int32_t* order, const i
   if (G <= 0 || G > kMaxPeers || E <= 0 || E % G != 0 || me < 0 || me >= G || d % 8 != 0) return LEWI_ERR_ARG;
   if (el_lo < 0 || el_hi > E / G || el_lo > el_hi) return LEWI_ERR_ARG;
   if (M >= (1ll << kEpSlotBits)) return LEWI_ERR_LIMIT;
-  const int fat_ctas = ep_fat_ctas();
-  if (threads == 0) threads = fat_ctas > 0 ? kEpFatThreads : kEpThreads;
-  if (threads < 32 || threads > (fat_ctas > 0 ? kEpFatThreads : kEpThreads) || threads % 32 != 0) return LEWI_ERR_ARG;
+  if (threads == 0) threads = kEpThreads;
+  if (threads < 32 || threads > kEpThreads || threads % 32 != 0) return LEWI_ERR_ARG;
   PeerPtrs rows, w, ret;
   if (!fill_peers(rows, peers_rows_host, G, true)) return LEWI_ERR_ARG;
   if (!fill_peers(w, peers_w_host, G, slot_w != nullptr)) return LEWI_ERR_ARG;
   if (!fill_peers(ret, peers_ret_host, G, false)) return LEWI_ERR_ARG;
   if (M == 0 || el_lo == el_hi) return LEWI_OK;
-  const __nv_bfloat16* xb = reinterpret_cast<const __nv_bfloat16*>(x);
-  if (fat_ctas > 0) {
-    cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
-    if (!fat_launch_config(reinterpret_cast<const void*>(ep_push_rows_kernel<true>), fat_ctas, threads, as_stream(stream), cfg,
-                           attr))
-      return LEWI_ERR_CUDA;
-    if (cudaLaunchKernelEx(&cfg, ep_push_rows_kernel<true>, xb, order, flat_expert, offsets, dst_base, slot_w, rows, w, ret,
-                           (long long)M, k, d, E / G, G, (long long)rmax_pad, (long long)T, el_lo, el_hi, me) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return LEWI_ERR_CUDA;
-    }
-  } else {
-    static bool carve[64] = {false};
-    prefer_shared_carveout(reinterpret_cast<const void*>(ep_push_rows_kernel<false>), carve);
-    ep_push_rows_kernel<false><<<num_sms(), threads, 0, as_stream(stream)>>>(
-        xb, order, flat_expert, offsets, dst_base, slot_w, rows, w, ret, M, k, d, E / G, G, rmax_pad, T, el_lo, el_hi, me);
-  }
+  static bool carve[64] = {false};
+  prefer_shared_carveout(reinterpret_cast<const void*>(ep_push_rows_kernel), carve);
+  ep_push_rows_kernel<<<num_sms(), threads, 0, as_stream(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(x), order, flat_expert, offsets, dst_base, slot_w, rows, w, ret, M, k, d, E / G,
+      G, rmax_pad, T, el_lo, el_hi, me);
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
 }
@@ -903,31 +856,17 @@ int lewi_ep_return_rows(void* stream, const void* rows, const float* pieces, con
   if (!ret || !pad_offsets || (!rows && !pieces) || d <= 0 || d % 8 != 0 || G <= 0 || G > kMaxPeers || M < 0)
     return LEWI_ERR_ARG;
   if (el_lo < 0 || el_lo > el_hi || (pieces && parts <= 0)) return LEWI_ERR_ARG;
-  const int fat_ctas = ep_fat_ctas();
-  if (threads == 0) threads = fat_ctas > 0 ? kEpFatThreads : kEpThreads;
-  if (threads < 32 || threads > (fat_ctas > 0 ? kEpFatThreads : kEpThreads) || threads % 32 != 0) return LEWI_ERR_ARG;
+  if (threads == 0) threads = kEpThreads;
+  if (threads < 32 || threads > kEpThreads || threads % 32 != 0) return LEWI_ERR_ARG;
   PeerPtrs pr, pp;
   if (!fill_peers(pr, peers_slot_rows_host, G, rows != nullptr)) return LEWI_ERR_ARG;
   if (!fill_peers(pp, peers_slot_pieces_host, G, pieces != nullptr)) return LEWI_ERR_ARG;
   if (el_lo == el_hi) return LEWI_OK;
-  const __nv_bfloat16* rb = reinterpret_cast<const __nv_bfloat16*>(rows);
-  if (fat_ctas > 0) {
-    cudaLaunchConfig_t cfg;
-    cudaLaunchAttribute attr[1];
-    if (!fat_launch_config(reinterpret_cast<const void*>(ep_return_rows_kernel<true>), fat_ctas, threads, as_stream(stream), cfg,
-                           attr))
-      return LEWI_ERR_CUDA;
-    if (cudaLaunchKernelEx(&cfg, ep_return_rows_kernel<true>, rb, pieces, ret, pad_offsets, el_lo, el_hi, pr, pp, d, parts, G,
-                           (long long)M, (long long)rmax_pad) != cudaSuccess) {
-      (void)cudaGetLastError();
-      return LEWI_ERR_CUDA;
-    }
-  } else {
-    static bool carve[64] = {false};
-    prefer_shared_carveout(reinterpret_cast<const void*>(ep_return_rows_kernel<false>), carve);
-    ep_return_rows_kernel<false><<<num_sms(), threads, 0, as_stream(stream)>>>(rb, pieces, ret, pad_offsets, el_lo, el_hi, pr, pp,
-                                                                                d, parts, G, M, rmax_pad);
-  }
+  static bool carve[64] = {false};
+  prefer_shared_carveout(reinterpret_cast<const void*>(ep_return_rows_kernel), carve);
+  ep_return_rows_kernel<<<num_sms(), threads, 0, as_stream(stream)>>>(
+      reinterpret_cast<const __nv_bfloat16*>(rows), pieces, ret, pad_offsets, el_lo, el_hi, pr, pp, d, parts, G, M,
+      rmax_pad);
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
 }
@@ -974,11 +913,6 @@ int lewi_set_sm_sharing(int on) {
   return LEWI_OK;
 }
 
-int lewi_set_exchange_sms(int n) {
-  if (n < 0 || n > num_sms() / 2) return LEWI_ERR_ARG;
-  gg::reserved_sms() = n & ~1;
-  return LEWI_OK;
-}
 
 // ------------------------------------------------------------------------------------------------ sequence mixing
 

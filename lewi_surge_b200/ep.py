@@ -309,10 +309,9 @@ class ExpertParallelP2P:
   """
 
   BARRIER_TIMEOUT_MS = 4000
-  DEFAULT_EXCHANGE_SMS = 0    # thin exchange CTAs beside the GEMM CTAs; > 0 gives the exchange that many SMs of its own
 
   def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None, phases=None, sync="flags",
-               exchange_threads=(0, 0), dw_down_last=True, exchange_sms=None):
+               exchange_threads=(0, 0), dw_down_last=True):
     from . import _lib, layer, ops
     self.lib, self.layer, self.ops, self._lib = _lib.load(), layer, ops, _lib
     self.w, self.k, self.e, self.d, self.t = w, k, num_experts, d, tokens
@@ -326,9 +325,6 @@ class ExpertParallelP2P:
       raise ValueError("sync must be 'flags' or 'nccl'")
     self.sync = sync
     self.fwd_threads, self.bwd_threads = (int(v) for v in exchange_threads)   # CTA size of the exchange kernels (0: largest)
-    # SMs the exchange kernels own while a pass runs (the GEMM grids leave them free); 0 = thin exchange CTAs that
-    # share every SM with a GEMM CTA
-    self.exchange_sms = int(exchange_sms) if exchange_sms is not None else (0 if self.world == 1 else self.DEFAULT_EXCHANGE_SMS)
     self.dw_down_last = bool(dw_down_last)
     self.el = num_experts // self.world
     self.f = w.w_gate.shape[2]
@@ -420,11 +416,8 @@ class ExpertParallelP2P:
     return lo, hi, self.pad_offsets[lo:hi + 1], None, None
 
   def _overlap_mode(self, on):
-    """How the exchange kernels of a pass coexist with its GEMMs: on their own SMs, or thin beside every GEMM CTA."""
-    if self.exchange_sms > 0:
-      self._lib.check(self.lib.lewi_set_exchange_sms(self.exchange_sms if on else 0), "lewi_set_exchange_sms")
-    else:
-      self.lib.lewi_set_sm_sharing(1 if on else 0)
+    """While a pass is queued the GEMM CTAs leave room on their SMs for one thin exchange CTA each."""
+    self.lib.lewi_set_sm_sharing(1 if on else 0)
 
   def forward(self, x):
     self._overlap_mode(True)

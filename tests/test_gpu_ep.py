@@ -46,11 +46,8 @@ def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
     if impl.startswith("p2p"):
       # "p2p": one exchange per pass; "p2p-phased": pipelined over ranges of local experts; "p2p-nccl": ranks
       # ordered by a one-element all-reduce instead of the flag barrier
-      # "p2p-fat": the exchange kernels own 16 SMs and the GEMM grids leave them free; the others run thin exchange
-      # CTAs beside every GEMM CTA
-      phases = {"p2p": 1, "p2p-phased": 4, "p2p-nccl": 2, "p2p-fat": 4}[impl]
-      lay = ep.ExpertParallelP2P(w, k, e, t, d, phases=phases, sync="nccl" if impl == "p2p-nccl" else "flags",
-                                 exchange_sms=16 if impl == "p2p-fat" else 0)
+      phases = {"p2p": 1, "p2p-phased": 4, "p2p-nccl": 2}[impl]
+      lay = ep.ExpertParallelP2P(w, k, e, t, d, phases=phases, sync="nccl" if impl == "p2p-nccl" else "flags")
     else:
       lay = ep.ExpertParallelLayer(w, k, e)
     sl = slice(rank * t, (rank + 1) * t)
@@ -69,13 +66,13 @@ def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("impl", ["p2p", "p2p-phased", "p2p-fat"])
+@pytest.mark.parametrize("impl", ["p2p", "p2p-phased"])
 def test_peer_memory_layer_on_one_gpu(cuda, tmp_path, impl):
   """World size 1: the push / return kernels, the plan and the barrier run against this GPU's own buffers."""
   _check(cuda, tmp_path, (512, 256, 16, 128, 128, 4), 1, impl)
 
 
-@pytest.mark.parametrize("impl", ["nccl", "p2p", "p2p-phased", "p2p-nccl", "p2p-fat"])
+@pytest.mark.parametrize("impl", ["nccl", "p2p", "p2p-phased", "p2p-nccl"])
 @pytest.mark.parametrize("cfg", [(512, 256, 16, 128, 128, 4), (1024, 1024, 64, 512, 512, 6)])
 def test_expert_parallel_matches_single_gpu(cuda, tmp_path, cfg, impl):
   world = min(torch.cuda.device_count(), 4)
