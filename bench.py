@@ -244,6 +244,12 @@ def main():
   ap.add_argument("--ep-dw-down-first", action="store_true", help="A/B switch: order of the two weight-gradient GEMMs")
   ap.add_argument("--ep-threads", default="0,0", help="CTA size of the exchange kernels: forward,backward (0: largest)")
   ap.add_argument("--ep-phases", type=int, default=None, help="ranges of local experts the exchange is pipelined over")
+  ap.add_argument("--ep-range-weights", default=None,
+                  help="relative sizes of the ranges, e.g. 1,3,3,1 (default: --ep-phases equal ranges)")
+  ap.add_argument("--ep-separate-return", action="store_true",
+                  help="A/B switch: rows go back with a transfer kernel of their own instead of the GEMM epilogue")
+  ap.add_argument("--ep-dw-per-range", action="store_true",
+                  help="A/B switch: weight-gradient GEMMs range by range instead of once after the last range")
   ap.add_argument("--preload-s", type=float, default=2.0,
                   help="seconds of untimed replays right before the timed window (clocks and power settle)")
   ap.add_argument("--single-cta", action="store_true", help="A/B switch: force the cta_group::1 GEMM kernels")
@@ -286,7 +292,8 @@ def main():
       runner = ep.ExpertParallelP2P(w, c["k"], c["E"], c["T"], c["d"], dist.group.WORLD, capacity=args.ep_capacity,
                                     phases=args.ep_phases, sync=args.ep_sync,
                                     exchange_threads=tuple(int(v) for v in args.ep_threads.split(",")),
-                                    dw_down_last=not args.ep_dw_down_first)
+                                    dw_down_last=not args.ep_dw_down_first, dw_deferred=not args.ep_dw_per_range,
+                                    range_weights=ep_range_weights(args), fused_return=not args.ep_separate_return)
     else:
       runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
     step_fn = lambda: runner.step(x, dout)
@@ -594,6 +601,10 @@ def measured_traffic(config, kernel, tokens):
     return None
 
 
+def ep_range_weights(args):
+  return [float(v) for v in args.ep_range_weights.split(",")] if args.ep_range_weights else None
+
+
 def ep_parity_check(args, c, rank, world, device, torch, dist, tokens=1024):
   """One small expert-parallel step (`tokens` per rank, the workload's widths) checked against the CPU oracle on the
   concatenated batch: out and dx of every rank, the owners' expert weight gradients.  Runs before the timed region;
@@ -610,7 +621,9 @@ def ep_parity_check(args, c, rank, world, device, torch, dist, tokens=1024):
   w = layer.MoEWeights(torch.from_numpy(full["w_router"]).to(device), bf(full["w_gate"][lo:hi]), bf(full["w_up"][lo:hi]),
                        bf(full["w_down"][lo:hi]), bf(full["ws_gate"]), bf(full["ws_up"]), bf(full["ws_down"]),
                        torch.from_numpy(bias).to(device) if bias is not None else None)
-  runner = ep.ExpertParallelP2P(w, k, E, tokens, d, dist.group.WORLD, phases=args.ep_phases, sync=args.ep_sync)
+  runner = ep.ExpertParallelP2P(w, k, E, tokens, d, dist.group.WORLD, phases=args.ep_phases, sync=args.ep_sync,
+                                dw_deferred=not args.ep_dw_per_range, range_weights=ep_range_weights(args),
+                                fused_return=not args.ep_separate_return)
   sl = slice(rank * tokens, (rank + 1) * tokens)
   out, g = runner.step(bf(full["x"][sl]), bf(full["dout"][sl]))
   status = _lib.last_status()

@@ -438,6 +438,66 @@ int lewi_ep_return_rows(void* stream, const void* rows, const float* pieces, con
                         void* const* peers_slot_pieces_host, int d, int parts, int G, int64_t M, int64_t rmax_pad,
                         int threads);
 
+/* The same way back fused into the GEMM that makes the rows: lewi_grouped_gemm_nn (down projection) and
+ * lewi_grouped_gemm_dx with an epilogue that stores row r of the bf16 product to row `slot` of out_ptrs[source]
+ * ([out_rows, N] bf16 each: this GPU's buffer or a peer's) for ret[r] = source << 28 | slot, and nowhere for
+ * ret[r] < 0; ret is indexed like the GEMM's rows.  A tile's rows leave while the tensor cores work on the next
+ * tile, the product is never written to local memory, and no separate transfer kernel runs.  out_ptrs_host: host
+ * array of `ranks` (<= 8) device pointers.  Other arguments as in the GEMM they extend.  There is no reference
+ * counterpart (the reference never ran expert-parallel). */
+int lewi_grouped_gemm_nn_return(void* stream, const void* a, const void* b, const int32_t* ret,
+                                void* const* out_ptrs_host, int ranks, int64_t out_rows, const int32_t* block_expert,
+                                const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows, int K, int N, int E);
+int lewi_grouped_gemm_dx_return(void* stream, const void* dgu, const void* w_gate, const void* w_up, const int32_t* ret,
+                                void* const* out_ptrs_host, int ranks, int64_t out_rows, const int32_t* block_expert,
+                                const int32_t* n_blocks, const int32_t* pad_offsets, int64_t rows, int d, int f, int E);
+
+/* ---- A token travels once per destination rank instead of once per (token, expert) slot.
+ * top-6 over 2 / 4 / 8 ranks: 0.99 / 2.5 / 3.9 rows per token cross NVLink instead of 3 / 4.5 / 5.25.  The owner copies
+ * a received ("unique") row to the padded rows of its local experts, runs the grouped GEMMs, adds up the token's local
+ * expert outputs and returns ONE partial row; the source adds the partial rows of the ranks it sent the token to
+ * (lewi_gather_reduce over comb).  The exchange stays pipelined over ranges of local experts (bounds_host
+ * [n_ranges+1], 0 = first, E/G = last, n_ranges <= 8): a row is pushed with the first range it is needed for and its
+ * partial row returns after the last.  No reference counterpart.
+ *
+ * lewi_ep_unique_tables: from topk_idx [T,k] (global expert ids): info [T,G] (-1 = token not sent to that rank, else
+ * first range | last range << 8), uidx [T,G] (rank of the token among those sent to the rank, token order; -1),
+ * comb [T,G] (r*T + uidx: row of this rank's [G*T,d] return buffer; -1), ucount [G] (tokens sent to each rank).
+ * workspace: lewi_ep_unique_workspace_bytes(T, G). */
+int64_t lewi_ep_unique_workspace_bytes(int64_t T, int G);
+int lewi_ep_unique_tables(void* stream, const int32_t* topk_idx, int64_t T, int k, int E, int G,
+                          const int32_t* bounds_host, int n_ranges, int32_t* info, int32_t* uidx, int32_t* comb,
+                          int32_t* ucount, void* workspace, int64_t workspace_bytes);
+/* ucount_all [G,G] (row = source rank, gathered with lewi_ep_put_i32) -> usrc_base [G]: first row of THIS rank's unique
+ * rows in every owner's buffer; utotal [1]: unique rows this rank receives (more than umax: LEWI_STATUS_EP_OVERFLOW). */
+int lewi_ep_unique_plan(void* stream, const int32_t* ucount_all, int G, int me, int64_t umax, int32_t* usrc_base,
+                        int32_t* utotal);
+/* Stores into the owners' tables what they need besides the rows: per padded row the routing weight (w f32
+ * [rmax_pad]), the slot's return address (ret, as lewi_ep_push_rows) and its unique row (rowu i32 [rmax_pad]); per
+ * unique row its padded rows (urows i32 [umax,k], -1 padded), last range (umeta i32 [umax]) and return address
+ * (uret i32 [umax] = source << 28 | row of the source's return buffer).  pos / offsets / dst_base as in
+ * lewi_ep_push_rows (pos = sorted position of a slot). */
+int lewi_ep_unique_meta(void* stream, const int32_t* topk_idx, const float* topk_w, const int32_t* pos,
+                        const int32_t* offsets, const int32_t* dst_base, const int32_t* info, const int32_t* uidx,
+                        const int32_t* usrc_base, void* const* peers_w_host, void* const* peers_ret_host,
+                        void* const* peers_rowu_host, void* const* peers_urows_host, void* const* peers_umeta_host,
+                        void* const* peers_uret_host, int me, int64_t T, int k, int E, int G, int64_t rmax_pad,
+                        int64_t umax);
+/* Rows x[t] of the tokens whose first range on the destination is `group` (negative: every token) go to row
+ * usrc_base[r] + uidx[t,r] of peers_ux[r] ([umax,d] bf16).  Thin kernel, threads as in lewi_ep_push_rows. */
+int lewi_ep_push_unique(void* stream, const void* x, const int32_t* info, const int32_t* uidx, const int32_t* usrc_base,
+                        void* const* peers_ux_host, int me, int64_t T, int d, int G, int group, int64_t umax,
+                        int threads);
+/* Owner, local memory: out[row] = ux[rowu[row]] (zero row where rowu[row] < 0) for the padded rows of local experts
+ * [el_lo, el_hi). */
+int lewi_ep_local_rows(void* stream, const void* ux, const int32_t* rowu, const int32_t* pad_offsets, int el_lo, int el_hi,
+                       void* out, int d, int64_t rmax_pad, int64_t umax);
+/* Owner: for every unique row u < utotal[0] whose last range is `group` (negative: all), the f32 sum of rows[urows[u,:]]
+ * goes as bf16 to row (uret[u] & slot mask) of peers_out[uret[u] >> 28] ([out_rows,d] bf16).  Thin kernel. */
+int lewi_ep_combine_return(void* stream, const void* rows, const int32_t* urows, const int32_t* umeta,
+                           const int32_t* uret, const int32_t* utotal, int group, void* const* peers_out_host, int k,
+                           int d, int G, int64_t rmax_pad, int64_t out_rows, int threads);
+
 /* Zero rows [valid_end[el], pad_offsets[el+1]) of buf [rmax_pad,d] bf16 for every local expert and, with
  * ret (i32 [rmax_pad], optional), mark them as having no return address. */
 int lewi_ep_zero_pad(void* stream, void* buf, int32_t* ret, const int32_t* valid_end, const int32_t* pad_offsets,

@@ -50,6 +50,16 @@ SIGNATURES = {
     "lewi_grouped_gemm_gateup_swiglu": (c_int, [P, P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dh_dswiglu": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dx": (c_int, [P, P, P, P, P, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_ep_unique_workspace_bytes": (c_int64, [c_int64, c_int]),
+    "lewi_ep_unique_tables": (c_int, [P, P, c_int64, c_int, c_int, c_int, P, c_int, P, P, P, P, P, c_int64]),
+    "lewi_ep_unique_plan": (c_int, [P, P, c_int, c_int, c_int64, P, P]),
+    "lewi_ep_unique_meta": (c_int, [P, P, P, P, P, P, P, P, P, P, P, P, P, P, P, c_int, c_int64, c_int, c_int, c_int,
+                                    c_int64, c_int64]),
+    "lewi_ep_push_unique": (c_int, [P, P, P, P, P, P, c_int, c_int64, c_int, c_int, c_int, c_int64, c_int]),
+    "lewi_ep_local_rows": (c_int, [P, P, P, P, c_int, c_int, P, c_int, c_int64, c_int64]),
+    "lewi_ep_combine_return": (c_int, [P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_int64, c_int64, c_int]),
+    "lewi_grouped_gemm_nn_return": (c_int, [P, P, P, P, P, c_int, c_int64, P, P, P, c_int64, c_int, c_int, c_int]),
+    "lewi_grouped_gemm_dx_return": (c_int, [P, P, P, P, P, P, c_int, c_int64, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_causal_conv1d_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int]),
     "lewi_causal_conv1d_fwd": (c_int, [P, P, P, P, c_int, c_int, c_int, c_int]),
     "lewi_causal_conv1d_bwd": (c_int, [P, P, P, P, P, P, c_int, P, c_int64, c_int, c_int, c_int, c_int]),

@@ -54,7 +54,9 @@ constexpr int EPI_BAR_BYTES = 64;        // one mbarrier per epilogue warp (TMA 
 constexpr size_t SMEM_BYTES = (size_t)DATA_BYTES + 256 /*barriers*/ + PAIR_PREFIX_BYTES + EPI_BAR_BYTES;
 
 enum Major { NN = 0, NT = 1, TN = 2 };
-enum Epi { PLAIN = 0, SWIGLU = 1, DSWIGLU = 2, TNOUT = 3 };
+enum Epi { PLAIN = 0, SWIGLU = 1, DSWIGLU = 2, TNOUT = 3, SCATTER = 4 };
+constexpr int kRetSlotBits = 28;   // return address of a row = rank << 28 | row in that rank's buffer
+constexpr int kRetRanks = 8;
 
 struct Args {
   void* out;                    // PLAIN: [rows,N]; SWIGLU: h [rows,f]; DSWIGLU: dgu [rows,2f]; TNOUT: [E,Ma,Nb(/2)]
@@ -87,6 +89,12 @@ struct Args {
                                 // row's slot); SWIGLU stores h * scale, DSWIGLU multiplies dh by it
   float* dw_partial;            // DSWIGLU: optional [rows, dw_parts] f32, sum over this warp's columns of
   int dw_parts;                 //   dh_unscaled * silu(g) * u  (= pieces of the routing-weight gradient)
+  // SCATTER: the bf16 product [rows, N] is not stored as a tensor: row r goes to row (ret[r] & slot mask) of
+  // ret_out[ret[r] >> kRetSlotBits], a [ret_slots, N] buffer in this GPU's or a peer's memory; negative: not stored
+  const int32_t* ret;
+  void* ret_out[kRetRanks];
+  long long ret_slots;
+  int ret_ranks;
   uint64_t desc_hi_a, desc_hi_b;
   uint32_t kstep_a, kstep_b;    // bytes to advance the descriptor start per 16-wide k step
   uint32_t idesc;
@@ -704,6 +712,54 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (a.dw_partial != nullptr && lane < rows_valid) {
           const int part = (t.n0 / BN) * 2 + col_half;
           if (part < a.dw_parts) a.dw_partial[(wrow0 + lane) * a.dw_parts + part] = dw_acc;
+        }
+      } else if constexpr (EPI == SCATTER) {
+        // Every lane looks up where its row goes; the warp then fills a 64-column staging tile and stores it row by
+        // row, 8 lanes per 128-byte row piece and 4 rows per instruction, with plain 16-byte stores (the destination
+        // may be a peer's memory: the rows travel while the tensor cores work on the next tile).
+        if (rows_valid > 0) {
+          unsigned long long my_dst = 0;
+          if (lane < rows_valid) {
+            const int code = a.ret[wrow0 + lane];
+            if (code >= 0) {
+              const int rank = code >> kRetSlotBits;
+              const long long slot = code & ((1 << kRetSlotBits) - 1);
+              if (rank < a.ret_ranks && slot < a.ret_slots)
+                my_dst = reinterpret_cast<unsigned long long>(a.ret_out[rank]) + (unsigned long long)slot * a.N * 2;
+              else
+                raise_status(LEWI_STATUS_BAD_INDEX);
+            }
+          }
+#pragma unroll 1
+          for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
+            const int n = t.n0 + c * 32;
+            if (n >= n_end) break;  // uniform across the warp
+            uint32_t r[32];
+            float v[32];
+            if (has_acc) {
+              ptx::tmem_ld_32x32(t_addr + c * 32, r);
+              ptx::tmem_ld_wait();
+            }
+#pragma unroll
+            for (int q = 0; q < 32; ++q) v[q] = has_acc ? __uint_as_float(r[q]) : 0.f;
+            uint8_t* buf = stage + ((c >> 1) & 1) * TILE_BYTES;
+            tile_put_bf16x32(buf, lane, (c & 1) * 4, v);
+            if ((c & 1) == 1 || n + 32 >= n_end) {
+              __syncwarp();
+              const int nb = n - (c & 1) * 32;   // first column of the staging tile
+              const int piece = lane & 7;
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const int row = i * 4 + (lane >> 3);
+                const unsigned long long dst = __shfl_sync(0xffffffffu, my_dst, row);
+                if (dst != 0 && nb + piece * 8 < a.N) {
+                  const uint4 val = *reinterpret_cast<const uint4*>(buf + row * 128 + ((piece ^ (row & 7)) << 4));
+                  st_v4(reinterpret_cast<void*>(dst + (unsigned long long)(nb + piece * 8) * 2), val);
+                }
+              }
+              __syncwarp();
+            }
+          }
         }
       } else {  // TNOUT
         // straight to the output ([E, Ma, N] through tm_c, or its two column halves through tm_c / tm_d), or one part

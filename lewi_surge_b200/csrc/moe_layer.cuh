@@ -181,7 +181,7 @@ __global__ void __launch_bounds__(256) shared_gate_bwd_kernel(const __nv_bfloat1
 
 // Per-device events that tie the side stream to the main one (created once, never destroyed).
 struct Events {
-  cudaEvent_t fork_fwd, join_fwd, fork_bwd, join_bwd;
+  cudaEvent_t fork_fwd, join_fwd, fork_bwd, join_bwd, dh_done;
   bool ok;
 };
 
@@ -195,7 +195,8 @@ inline Events* events() {
     e.ok = cudaEventCreateWithFlags(&e.fork_fwd, cudaEventDisableTiming) == cudaSuccess &&
            cudaEventCreateWithFlags(&e.join_fwd, cudaEventDisableTiming) == cudaSuccess &&
            cudaEventCreateWithFlags(&e.fork_bwd, cudaEventDisableTiming) == cudaSuccess &&
-           cudaEventCreateWithFlags(&e.join_bwd, cudaEventDisableTiming) == cudaSuccess;
+           cudaEventCreateWithFlags(&e.join_bwd, cudaEventDisableTiming) == cudaSuccess &&
+           cudaEventCreateWithFlags(&e.dh_done, cudaEventDisableTiming) == cudaSuccess;
     made[dev] = true;
   }
   return ev[dev].ok ? &ev[dev] : nullptr;

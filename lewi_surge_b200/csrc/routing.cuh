@@ -48,68 +48,120 @@ __device__ __forceinline__ void warp_histogram(const int* s_e, int begin, int en
   }
 }
 
-// ER = experts held per lane (E <= 32*ER).
-template <int ER>
-__device__ __forceinline__ void warp_softmax_topk(const float* __restrict__ row, int E, int k, int lane,
-                                                  int& out_idx, float& out_w, float (&p)[ER]) {
-  float l[ER];
-  float mx = -INFINITY;
+// ER = experts held per lane (E <= 32*ER); NT = tokens a warp works on at once.  The soft-max and the k rounds of
+// arg-max are chains of dependent shuffles; NT independent chains side by side keep the warp's issue slots busy
+// while one of them waits.  Token i of the group is rows[i] (null: no such token); its results are the same bits
+// whatever NT is.
+template <int ER, int NT>
+__device__ __forceinline__ void warp_softmax_topk(const float* const (&rows)[NT], int E, int k, int lane,
+                                                  int (&out_idx)[NT], float (&out_w)[NT], float (&p)[NT][ER]) {
+  float l[NT][ER];
+  float mx[NT], sum[NT];
 #pragma unroll
-  for (int r = 0; r < ER; ++r) {
-    int e = lane + r * kWarp;
-    l[r] = (e < E) ? row[e] : -INFINITY;
-    mx = fmaxf(mx, l[r]);
-  }
-  mx = warp_max(mx);
-  float sum = 0.f;
-#pragma unroll
-  for (int r = 0; r < ER; ++r) {
-    int e = lane + r * kWarp;
-    p[r] = (e < E) ? expf(l[r] - mx) : 0.f;
-    sum += p[r];
-  }
-  sum = warp_sum(sum);
-  float inv = 1.0f / sum;
-#pragma unroll
-  for (int r = 0; r < ER; ++r) p[r] *= inv;
-
-  // k rounds of warp arg-max on (logit descending, index ascending).
-  unsigned long long key[ER];
-#pragma unroll
-  for (int r = 0; r < ER; ++r) {
-    int e = lane + r * kWarp;
-    key[r] = (e < E) ? ((unsigned long long)float_order_key(l[r]) << 32) | (unsigned)(0xFFFFFFFFu - (unsigned)e) : 0ull;
-  }
-  float vsum = 0.f;
-  float my_v = 0.f;
-  int my_idx = 0;
-  for (int j = 0; j < k; ++j) {
-    unsigned long long best = 0ull;
-    float best_p = 0.f;
+  for (int i = 0; i < NT; ++i) {
 #pragma unroll
     for (int r = 0; r < ER; ++r) {
-      if (key[r] > best) {
-        best = key[r];
-        best_p = p[r];
-      }
-    }
-    unsigned long long win = warp_max_u64(best);
-    int e_win = (int)(0xFFFFFFFFu - (unsigned)(win & 0xFFFFFFFFull));
-    int owner = e_win & (kWarp - 1);
-    float v = __shfl_sync(0xffffffffu, best_p, owner);
-    if (lane == owner) {
-#pragma unroll
-      for (int r = 0; r < ER; ++r)
-        if (key[r] == win) key[r] = 0ull;
-    }
-    vsum += v;
-    if (lane == j) {
-      my_v = v;
-      my_idx = e_win;
+      const int e = lane + r * kWarp;
+      l[i][r] = (e < E && rows[i] != nullptr) ? rows[i][e] : -INFINITY;
     }
   }
-  out_idx = my_idx;
-  out_w = my_v / vsum;
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    mx[i] = -INFINITY;
+#pragma unroll
+    for (int r = 0; r < ER; ++r) mx[i] = fmaxf(mx[i], l[i][r]);
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+    for (int i = 0; i < NT; ++i) mx[i] = fmaxf(mx[i], __shfl_xor_sync(0xffffffffu, mx[i], o));
+  }
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    sum[i] = 0.f;
+#pragma unroll
+    for (int r = 0; r < ER; ++r) {
+      const int e = lane + r * kWarp;
+      p[i][r] = (e < E && rows[i] != nullptr) ? expf(l[i][r] - mx[i]) : 0.f;
+      sum[i] += p[i][r];
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+    for (int i = 0; i < NT; ++i) sum[i] += __shfl_xor_sync(0xffffffffu, sum[i], o);
+  }
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    const float inv = 1.0f / sum[i];
+#pragma unroll
+    for (int r = 0; r < ER; ++r) p[i][r] *= inv;
+  }
+
+  // k rounds of warp arg-max on (logit descending, index ascending).
+  unsigned long long key[NT][ER];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+#pragma unroll
+    for (int r = 0; r < ER; ++r) {
+      const int e = lane + r * kWarp;
+      key[i][r] = (e < E && rows[i] != nullptr)
+                      ? ((unsigned long long)float_order_key(l[i][r]) << 32) | (unsigned)(0xFFFFFFFFu - (unsigned)e)
+                      : 0ull;
+    }
+  }
+  float vsum[NT], my_v[NT];
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    vsum[i] = 0.f;
+    my_v[i] = 0.f;
+    out_idx[i] = 0;
+  }
+  for (int j = 0; j < k; ++j) {
+    unsigned long long best[NT];
+    float best_p[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      best[i] = 0ull;
+      best_p[i] = 0.f;
+#pragma unroll
+      for (int r = 0; r < ER; ++r) {
+        if (key[i][r] > best[i]) {
+          best[i] = key[i][r];
+          best_p[i] = p[i][r];
+        }
+      }
+    }
+    unsigned long long win[NT];
+#pragma unroll
+    for (int i = 0; i < NT; ++i) win[i] = best[i];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, win[i], o);
+        win[i] = other > win[i] ? other : win[i];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < NT; ++i) {
+      const int e_win = (int)(0xFFFFFFFFu - (unsigned)(win[i] & 0xFFFFFFFFull));
+      const int owner = e_win & (kWarp - 1);
+      const float v = __shfl_sync(0xffffffffu, best_p[i], owner);
+      if (lane == owner) {
+#pragma unroll
+        for (int r = 0; r < ER; ++r)
+          if (key[i][r] == win[i]) key[i][r] = 0ull;
+      }
+      vsum[i] += v;
+      if (lane == j) {
+        my_v[i] = v;
+        out_idx[i] = e_win;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < NT; ++i) out_w[i] = my_v[i] / vsum[i];
 }
 
 struct RouteChunkArgs {
@@ -149,18 +201,31 @@ __global__ void __launch_bounds__(kRouteThreads) route_chunk_kernel(RouteChunkAr
     for (int r = 0; r < ER; ++r) pacc[r] = 0.f;
     const int n_tok = n_slots / a.k;
     const long long tok0 = slot0 / a.k;
-    for (int t = warp; t < n_tok; t += nwarps) {
-      float p[ER];
-      int idx;
-      float w;
-      warp_softmax_topk<ER>(a.logits + (tok0 + t) * a.E, a.E, a.k, lane, idx, w, p);
+    // a warp takes NT of its tokens (warp, warp + nwarps, ...) at a time; fewer when a lane holds many experts
+    constexpr int NT = ER <= 4 ? 4 : (ER <= 8 ? 2 : 1);
+    for (int t0 = warp; t0 < n_tok; t0 += nwarps * NT) {
+      const float* rows[NT];
+      float p[NT][ER];
+      int idx[NT];
+      float w[NT];
 #pragma unroll
-      for (int r = 0; r < ER; ++r) pacc[r] += p[r];
-      if (lane < a.k) {
-        long long s = (tok0 + t) * a.k + lane;
-        a.topk_idx[s] = idx;
-        a.topk_w[s] = w;
-        s_e[t * a.k + lane] = idx;
+      for (int i = 0; i < NT; ++i) {
+        const int t = t0 + i * nwarps;
+        rows[i] = t < n_tok ? a.logits + (tok0 + t) * a.E : nullptr;
+      }
+      warp_softmax_topk<ER, NT>(rows, a.E, a.k, lane, idx, w, p);
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        const int t = t0 + i * nwarps;
+        if (t >= n_tok) continue;
+#pragma unroll
+        for (int r = 0; r < ER; ++r) pacc[r] += p[i][r];
+        if (lane < a.k) {
+          const long long s = (tok0 + t) * a.k + lane;
+          a.topk_idx[s] = idx[i];
+          a.topk_w[s] = w[i];
+          s_e[t * a.k + lane] = idx[i];
+        }
       }
     }
     if (a.chunk_probs != nullptr) {

@@ -219,6 +219,25 @@ class ExpertParallelLayer:
 # ======================================================================================================
 
 
+def range_bounds(num_local_experts, phases, weights=None):
+  """Boundaries of the ranges of local experts one pass works through: `phases` ranges of equal size, or sizes in the
+  proportion of `weights` (a short first range lets the GEMMs start early, a short last one shortens the tail in which
+  only the exchange runs).  Every range gets at least one expert; ranges that would be empty are dropped."""
+  if weights is None:
+    weights = [1.0] * phases
+  weights = [float(v) for v in weights]
+  if not weights or min(weights) <= 0:
+    raise ValueError("range weights must be positive")
+  total, acc, bounds = sum(weights), 0.0, [0]
+  for v in weights:
+    acc += v
+    b = min(num_local_experts, max(bounds[-1] + 1, int(round(num_local_experts * acc / total))))
+    if b > bounds[-1]:
+      bounds.append(b)
+  bounds[-1] = num_local_experts
+  return bounds
+
+
 class _DevBuf:
   """Device memory from lewi_ep_alloc that exposes itself to torch through __cuda_array_interface__."""
 
@@ -288,8 +307,10 @@ class ExpertParallelP2P:
   Every rank routes its own tokens and shares its expert histogram (4*E bytes, stored into every peer's table);
   `lewi_ep_plan` turns the histograms into row offsets on every owner.  Rows are then pushed straight into the
   owners' padded buffers together with their return address (`lewi_ep_push_rows`), the owners run the grouped
-  GEMMs in place and push every output row back into the source's slot-ordered buffer
-  (`lewi_ep_return_rows`), where the combine is a sum over k consecutive rows.  The backward pass moves the
+  GEMMs in place and every output row goes back into the source's slot-ordered buffer, where the combine is a sum
+  over k consecutive rows: by default straight from the epilogue of the down-projection (and dx) GEMM
+  (`lewi_grouped_gemm_nn_return`, `lewi_grouped_gemm_dx_return`: a tile's rows travel while the next tile is being
+  multiplied), or with `fused_return=False` by a transfer kernel of its own (`lewi_ep_return_rows`).  The backward pass moves the
   upstream gradient rows, dx and the routing-weight gradient pieces the same way.
 
   The local experts are worked on in `phases` ranges.  The exchange kernels run on their own stream and are small
@@ -311,7 +332,8 @@ class ExpertParallelP2P:
   BARRIER_TIMEOUT_MS = 4000
 
   def __init__(self, w, k, num_experts, tokens, d, group=None, capacity=None, phases=None, sync="flags",
-               exchange_threads=(0, 0), dw_down_last=True):
+               exchange_threads=(0, 0), dw_down_last=True, range_weights=None, dw_deferred=True,
+               fused_return=True, unique_push=False, combined_return=None):
     from . import _lib, layer, ops
     self.lib, self.layer, self.ops, self._lib = _lib.load(), layer, ops, _lib
     self.w, self.k, self.e, self.d, self.t = w, k, num_experts, d, tokens
@@ -332,7 +354,21 @@ class ExpertParallelP2P:
     self.m = tokens * k
     want = int(phases) if phases is not None else (1 if self.world == 1 else 4)
     self.phases = max(1, min(want, self.el))
-    self.bounds = [self.el * p // self.phases for p in range(self.phases + 1)]
+    self.bounds = range_bounds(self.el, self.phases, range_weights)
+    self.phases = len(self.bounds) - 1
+    # weight gradients of all ranges as one pair of launches after the last range's dx (or range by range)
+    self.dw_deferred = bool(dw_deferred)
+    # A token travels once per destination rank (and is copied to its experts' padded rows by the owner) instead of
+    # once per slot; with combined_return the owner also adds up the token's local expert outputs and returns one
+    # partial row per token.  Otherwise rows return per slot: as the epilogue of the GEMM that makes them (down
+    # projection, dx), or by a transfer kernel of its own.
+    self.unique_push = bool(unique_push)
+    self.combined_return = self.unique_push if combined_return is None else bool(combined_return)
+    if self.combined_return and not self.unique_push:
+      raise ValueError("combined_return needs unique_push")
+    self.fused_return = bool(fused_return) and not self.combined_return
+    if self.phases > 8:
+      raise ValueError("at most 8 ranges")
     cap = float(capacity) if capacity is not None else float(self.world)
     rows = int(self.m * cap)
     self.rmax = (rows + self.el * (BLOCK - 1)) // BLOCK * BLOCK
@@ -356,8 +392,35 @@ class ExpertParallelP2P:
     self.counts_all = self.s_counts.local.tensor((self.world * num_experts,), torch.int32)
     self.flags = self.s_flags.local.tensor((self.world,), torch.int32)
     # local to the owner
-    self.ys = torch.empty((self.rmax, d), dtype=bf, device=self.dev)
-    self.dxs = torch.empty((self.rmax, d), dtype=bf, device=self.dev)
+    if not self.fused_return:
+      self.ys = torch.empty((self.rmax, d), dtype=bf, device=self.dev)
+      self.dxs = torch.empty((self.rmax, d), dtype=bf, device=self.dev)
+    if self.unique_push:
+      import ctypes
+      G, T = self.world, tokens
+      self.umax = max(G * T, 1)   # every token of every rank may come here: nothing is dropped
+      self.s_ux = sb(self.umax * d * 2)
+      self.s_rowu, self.s_urows = sb(self.rmax * 4), sb(self.umax * k * 4)
+      self.s_umeta, self.s_uret = sb(self.umax * 4), sb(self.umax * 4)
+      self.s_ucounts = sb(G * G * 4)
+      self.ux = self.s_ux.local.tensor((self.umax, d), bf)
+      self.rowu = self.s_rowu.local.tensor((self.rmax,), torch.int32)
+      self.urows = self.s_urows.local.tensor((self.umax, k), torch.int32)
+      self.umeta = self.s_umeta.local.tensor((self.umax,), torch.int32)
+      self.uret = self.s_uret.local.tensor((self.umax,), torch.int32)
+      self.ucount_all = self.s_ucounts.local.tensor((G * G,), torch.int32)
+      self.info = torch.zeros((max(T, 1), G), **i32)
+      self.uidx = torch.zeros((max(T, 1), G), **i32)
+      self.comb = torch.zeros((max(T, 1), G), **i32)
+      self.ucount, self.usrc_base, self.utotal = torch.zeros(G, **i32), torch.zeros(G, **i32), torch.zeros(1, **i32)
+      self.uws = torch.zeros(max(int(self.lib.lewi_ep_unique_workspace_bytes(T, G)), 4) // 4, **i32)
+      self.c_bounds = (ctypes.c_int32 * len(self.bounds))(*self.bounds)
+      self.rowu.fill_(-1)
+      self.ucount_all.zero_()
+      if self.combined_return:
+        self.s_yrecv, self.s_dxrecv = sb(self.umax * d * 2), sb(self.umax * d * 2)
+        self.y_recv = self.s_yrecv.local.tensor((self.umax, d), bf)
+        self.dx_recv = self.s_dxrecv.local.tensor((self.umax, d), bf)
     self.dwp = torch.zeros((self.rmax, self.parts), dtype=f32, device=self.dev)
     self.dst_base = torch.zeros(num_experts, **i32)
     self.pad_offsets = torch.zeros(self.el + 1, **i32)
@@ -389,12 +452,14 @@ class ExpertParallelP2P:
     """Releases the peer mappings and this rank's exchange buffers.  Collective: every rank calls it."""
     torch.cuda.synchronize(self.dev)
     dist.barrier(group=self.group)
-    for name in ("s_x", "s_w", "s_ret", "s_dy", "s_yslot", "s_dxslot", "s_dwslot", "s_counts", "s_flags"):
+    for name in ("s_x", "s_w", "s_ret", "s_dy", "s_yslot", "s_dxslot", "s_dwslot", "s_counts", "s_flags", "s_ux", "s_rowu",
+                 "s_urows", "s_umeta", "s_uret", "s_ucounts", "s_yrecv", "s_dxrecv"):
       buf = getattr(self, name, None)
       if buf is not None:
         buf.close()
         setattr(self, name, None)
-    for view in ("recv_x", "recv_w", "ret", "recv_dy", "y_slot", "dx_slot", "dw_slot", "counts_all", "flags"):
+    for view in ("recv_x", "recv_w", "ret", "recv_dy", "y_slot", "dx_slot", "dw_slot", "counts_all", "flags", "ux", "rowu",
+                 "urows", "umeta", "uret", "ucount_all", "y_recv", "dx_recv"):
       setattr(self, view, None)   # these pointed into the freed buffers
     dist.barrier(group=self.group)
 
@@ -426,11 +491,12 @@ class ExpertParallelP2P:
     finally:
       self._overlap_mode(False)
 
-  def _pipeline(self, push, gemms, give_back, first=None):
+  def _pipeline(self, push, gemms, give_back, first=None, last=None):
     """Issue order of one pass.  On the exchange stream: push 0, push 1, then for every range p >= 1 push p+1 followed
     by the return of range p-1, last the return of the final range and a barrier.  On the caller's stream: the GEMMs of
     range p once its rows have arrived.  So while range p is being multiplied, range p+1 is arriving and range p-1 is
-    on its way back.  Returns with the caller's stream waiting for the final barrier."""
+    on its way back.  `first` runs on the caller's stream while the first rows are in flight, `last` while the final
+    range is on its way back.  Returns with the caller's stream waiting for the final barrier."""
     L, P = self.layer, self.phases
     main, comm = torch.cuda.current_stream(self.dev), self.comm
     arrived, done = {}, {}
@@ -466,6 +532,8 @@ class ExpertParallelP2P:
       self._sync_ranks()   # everything is back at its source
       L._mark("ep_barrier")
       returned = comm.record_event()
+    if last is not None:
+      last()
     main.wait_event(returned)
     L._mark("step_begin")
 
@@ -484,6 +552,12 @@ class ExpertParallelP2P:
     with torch.cuda.stream(comm):
       comm.wait_event(routed)
       L._mark("side_begin")
+      if self.unique_push:
+        check(lib.lewi_ep_unique_tables(st(), ptr(tb.topk_idx), t, k, self.e, G, self.c_bounds, self.phases,
+                                        ptr(self.info), ptr(self.uidx), ptr(self.comb), ptr(self.ucount), ptr(self.uws),
+                                        self.uws.numel() * 4), "lewi_ep_unique_tables")
+        check(lib.lewi_ep_put_i32(st(), ptr(self.ucount), self.s_ucounts.c_ptrs, self.rank * G, G, G), "lewi_ep_put_i32")
+        L._mark("ep_unique_tables")
       check(lib.lewi_ep_put_i32(st(), ptr(tb.counts), self.s_counts.c_ptrs, self.rank * self.e, self.e, G),
             "lewi_ep_put_i32")
       L._mark("ep_put_counts")
@@ -496,29 +570,62 @@ class ExpertParallelP2P:
       check(lib.lewi_ep_zero_pad(st(), ptr(self.recv_x), ptr(self.ret), ptr(self.valid_end), ptr(self.pad_offsets),
                                  self.el, d, self.rmax), "lewi_ep_zero_pad")
       L._mark("ep_zero_pad")
+      if self.unique_push:
+        check(lib.lewi_ep_unique_plan(st(), ptr(self.ucount_all), G, self.rank, self.umax, ptr(self.usrc_base),
+                                      ptr(self.utotal)), "lewi_ep_unique_plan")
+        check(lib.lewi_ep_zero_pad(st(), ptr(self.recv_x), ptr(self.rowu), ptr(self.valid_end), ptr(self.pad_offsets),
+                                   self.el, d, self.rmax), "lewi_ep_zero_pad")
+        check(lib.lewi_ep_unique_meta(st(), ptr(tb.topk_idx), ptr(tb.topk_w), ptr(tb.pos), ptr(tb.offsets),
+                                      ptr(self.dst_base), ptr(self.info), ptr(self.uidx), ptr(self.usrc_base),
+                                      self.s_w.c_ptrs, self.s_ret.c_ptrs, self.s_rowu.c_ptrs, self.s_urows.c_ptrs,
+                                      self.s_umeta.c_ptrs, self.s_uret.c_ptrs, self.rank, t, k, self.e, G, self.rmax,
+                                      self.umax), "lewi_ep_unique_meta")
+        L._mark("ep_unique_meta")
     gu = torch.empty((self.rmax, 2 * f), dtype=torch.bfloat16, device=self.dev)
     h = torch.empty((self.rmax, f), dtype=torch.bfloat16, device=self.dev)
     shared = []
 
     def push(p):
-      check(lib.lewi_ep_push_rows(st(), ptr(x), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
-                                  ptr(tb.topk_w), self.s_x.c_ptrs, self.s_w.c_ptrs, self.s_ret.c_ptrs, self.rank, self.m,
-                                  k, d, self.e, G, self.rmax, t, self.bounds[p], self.bounds[p + 1], self.fwd_threads),
-            "lewi_ep_push_rows")
+      if self.unique_push:
+        check(lib.lewi_ep_push_unique(st(), ptr(x), ptr(self.info), ptr(self.uidx), ptr(self.usrc_base), self.s_ux.c_ptrs,
+                                      self.rank, t, d, G, p if self.phases > 1 else -1, self.umax, self.fwd_threads),
+              "lewi_ep_push_unique")
+      else:
+        check(lib.lewi_ep_push_rows(st(), ptr(x), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
+                                    ptr(tb.topk_w), self.s_x.c_ptrs, self.s_w.c_ptrs, self.s_ret.c_ptrs, self.rank, self.m,
+                                    k, d, self.e, G, self.rmax, t, self.bounds[p], self.bounds[p + 1], self.fwd_threads),
+              "lewi_ep_push_rows")
       L._mark("ep_push_x")
 
     def gemms(p, mark_done):
       lo, hi, po, be, nb = self._range(p)
+      if self.unique_push:   # the received rows go to the padded rows of this range's experts
+        check(lib.lewi_ep_local_rows(st(), ptr(self.ux), ptr(self.rowu), ptr(self.pad_offsets), lo, hi, ptr(self.recv_x), d,
+                                     self.rmax, self.umax), "lewi_ep_local_rows")
+        L._mark("ep_local_rows_x")
       check(lib.lewi_grouped_gemm_gateup_swiglu_scaled(st(), ptr(self.recv_x), None, ptr(self.recv_w),
                                                        ptr(w.w_gate[lo:hi]), ptr(w.w_up[lo:hi]), ptr(gu), ptr(h), ptr(be),
                                                        ptr(nb), ptr(po), self.rmax, d, f, hi - lo),
             "lewi_grouped_gemm_gateup_swiglu")
       L._mark("gemm_gateup_swiglu")
-      ops.grouped_gemm_nn(h, w.w_down[lo:hi], be, nb, pad_offsets=po, out=self.ys)
+      if self.fused_return:
+        check(lib.lewi_grouped_gemm_nn_return(st(), ptr(h), ptr(w.w_down[lo:hi]), ptr(self.ret), self.s_yslot.c_ptrs, G,
+                                              self.m, ptr(be), ptr(nb), ptr(po), self.rmax, f, d, hi - lo),
+              "lewi_grouped_gemm_nn_return")
+      else:
+        ops.grouped_gemm_nn(h, w.w_down[lo:hi], be, nb, pad_offsets=po, out=self.ys)
       L._mark("gemm_down")
       mark_done()
 
     def give_back(p):
+      if self.fused_return:
+        return   # the rows left with the GEMM's epilogue
+      if self.combined_return:
+        check(lib.lewi_ep_combine_return(st(), ptr(self.ys), ptr(self.urows), ptr(self.umeta), ptr(self.uret),
+                                         ptr(self.utotal), p if self.phases > 1 else -1, self.s_yrecv.c_ptrs, k, d, G,
+                                         self.rmax, self.umax, self.fwd_threads), "lewi_ep_combine_return")
+        L._mark("ep_combine_return_y")
+        return
       check(lib.lewi_ep_return_rows(st(), ptr(self.ys), None, ptr(self.ret), ptr(self.pad_offsets), self.bounds[p],
                                     self.bounds[p + 1], self.s_yslot.c_ptrs, None, d, self.parts, G, self.m, self.rmax,
                                     self.fwd_threads), "lewi_ep_return_rows")
@@ -533,7 +640,10 @@ class ExpertParallelP2P:
       L._mark("shared_down")
 
     self._pipeline(push, gemms, give_back, first=shared_expert)
-    out = ops.gather_reduce(self.y_slot, self.slot_ids, None, x.dtype, add0=shared[2] if shared else None)
+    if self.combined_return:   # one partial row per rank the token went to
+      out = ops.gather_reduce(self.y_recv, self.comb[:t], None, x.dtype, add0=shared[2] if shared else None)
+    else:
+      out = ops.gather_reduce(self.y_slot, self.slot_ids, None, x.dtype, add0=shared[2] if shared else None)
     L._mark("combine_reduce")
     return out, dict(x=x, logits=logits, tb=tb, gu=gu, h=h, shared=tuple(shared) or None)
 
@@ -556,9 +666,10 @@ class ExpertParallelP2P:
     with torch.cuda.stream(comm):
       comm.wait_event(ready)
       L._mark("side_begin")
-      check(lib.lewi_ep_zero_pad(st(), ptr(self.recv_dy), None, ptr(self.valid_end), ptr(self.pad_offsets), self.el, d,
-                                 self.rmax), "lewi_ep_zero_pad")
-      L._mark("ep_zero_pad")
+      if not self.unique_push:   # (the owner's local copy writes the zero rows itself)
+        check(lib.lewi_ep_zero_pad(st(), ptr(self.recv_dy), None, ptr(self.valid_end), ptr(self.pad_offsets), self.el, d,
+                                   self.rmax), "lewi_ep_zero_pad")
+        L._mark("ep_zero_pad")
     grads = {}
     dxsh = []
 
@@ -581,23 +692,40 @@ class ExpertParallelP2P:
     grads["dw_gate"], grads["dw_up"] = torch.empty_like(w.w_gate), torch.empty_like(w.w_up)
 
     def push(p):
-      check(lib.lewi_ep_push_rows(st(), ptr(dout), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
-                                  None, self.s_dy.c_ptrs, None, None, self.rank, self.m, k, d, self.e, G, self.rmax, t,
-                                  self.bounds[p], self.bounds[p + 1], self.bwd_threads), "lewi_ep_push_rows")
+      if self.unique_push:
+        check(lib.lewi_ep_push_unique(st(), ptr(dout), ptr(self.info), ptr(self.uidx), ptr(self.usrc_base),
+                                      self.s_ux.c_ptrs, self.rank, t, d, G, p if self.phases > 1 else -1, self.umax,
+                                      self.bwd_threads), "lewi_ep_push_unique")
+      else:
+        check(lib.lewi_ep_push_rows(st(), ptr(dout), ptr(tb.order), ptr(tb.topk_idx), ptr(tb.offsets), ptr(self.dst_base),
+                                    None, self.s_dy.c_ptrs, None, None, self.rank, self.m, k, d, self.e, G, self.rmax, t,
+                                    self.bounds[p], self.bounds[p + 1], self.bwd_threads), "lewi_ep_push_rows")
       L._mark("ep_push_dout")
 
     def gemms(p, mark_done):
       lo, hi, po, be, nb = self._range(p)
+      if self.unique_push:
+        check(lib.lewi_ep_local_rows(st(), ptr(self.ux), ptr(self.rowu), ptr(self.pad_offsets), lo, hi, ptr(self.recv_dy),
+                                     d, self.rmax, self.umax), "lewi_ep_local_rows")
+        L._mark("ep_local_rows_dout")
       check(lib.lewi_grouped_gemm_dh_dswiglu_scaled(st(), ptr(self.recv_dy), None, ptr(self.recv_w),
                                                     ptr(self.dwp), ptr(w.w_down[lo:hi]), ptr(c["gu"]), ptr(dgu), ptr(be),
                                                     ptr(nb), ptr(po), self.rmax, d, f, hi - lo),
             "lewi_grouped_gemm_dh_dswiglu")
       L._mark("gemm_dh_dswiglu")
-      check(lib.lewi_grouped_gemm_dx(st(), ptr(dgu), ptr(w.w_gate[lo:hi]), ptr(w.w_up[lo:hi]), ptr(self.dxs), ptr(be),
-                                     ptr(nb), ptr(po), self.rmax, d, f, hi - lo), "lewi_grouped_gemm_dx")
+      if self.fused_return:
+        check(lib.lewi_grouped_gemm_dx_return(st(), ptr(dgu), ptr(w.w_gate[lo:hi]), ptr(w.w_up[lo:hi]), ptr(self.ret),
+                                              self.s_dxslot.c_ptrs, G, self.m, ptr(be), ptr(nb), ptr(po), self.rmax, d, f,
+                                              hi - lo), "lewi_grouped_gemm_dx_return")
+      else:
+        check(lib.lewi_grouped_gemm_dx(st(), ptr(dgu), ptr(w.w_gate[lo:hi]), ptr(w.w_up[lo:hi]), ptr(self.dxs), ptr(be),
+                                       ptr(nb), ptr(po), self.rmax, d, f, hi - lo), "lewi_grouped_gemm_dx")
       L._mark("gemm_dx")
-      mark_done()   # the weight gradients below are of no interest to the other ranks
+      mark_done()   # the weight gradients are of no interest to the other ranks
+      if not self.dw_deferred:
+        weight_grads(lo, hi, po)
 
+    def weight_grads(lo, hi, po):
       def dw_down():
         ops.grouped_gemm_tn(c["h"], self.recv_dy, po, hi - lo, out=grads["dw_down"][lo:hi])
         L._mark("gemm_dw_down")
@@ -607,18 +735,32 @@ class ExpertParallelP2P:
                             split=True)
         L._mark("gemm_dw_gateup")
 
-      # The return of this range's dx starts now and shares the SMs with whatever comes next.  dW_down (few tiles,
-      # long contraction) was measured 3x slower beside it, dW_gate|up 1.1x: the robust one goes first.
+      # A return of dx rows shares the SMs with these.  dW_down (few tiles, long contraction) was measured 3x slower
+      # beside it, dW_gate|up 1.1x: the robust one goes first.
       for gemm in ((dw_gateup, dw_down) if self.dw_down_last else (dw_down, dw_gateup)):
         gemm()
 
-    def give_back(p):
-      check(lib.lewi_ep_return_rows(st(), ptr(self.dxs), ptr(self.dwp), ptr(self.ret), ptr(self.pad_offsets),
-                                    self.bounds[p], self.bounds[p + 1], self.s_dxslot.c_ptrs, self.s_dwslot.c_ptrs, d,
-                                    self.parts, G, self.m, self.rmax, self.bwd_threads), "lewi_ep_return_rows")
-      L._mark("ep_return_dx")
+    def all_weight_grads():
+      # One pair of launches over every local expert: each has enough tiles to fill the GPU (a range of a few experts
+      # does not), and they run while the last range's dx rows travel home.
+      if self.dw_deferred:
+        weight_grads(0, self.el, self.pad_offsets)
 
-    self._pipeline(push, gemms, give_back, first=shared_expert)
+    def give_back(p):
+      # fused: the dx rows left with the GEMM's epilogue; only the routing-weight gradient pieces remain
+      rows_too = not (self.fused_return or self.combined_return)
+      check(lib.lewi_ep_return_rows(st(), ptr(self.dxs) if rows_too else None, ptr(self.dwp), ptr(self.ret),
+                                    ptr(self.pad_offsets), self.bounds[p], self.bounds[p + 1],
+                                    self.s_dxslot.c_ptrs if rows_too else None, self.s_dwslot.c_ptrs, d,
+                                    self.parts, G, self.m, self.rmax, self.bwd_threads), "lewi_ep_return_rows")
+      L._mark("ep_return_dx" if rows_too else "ep_return_dw")
+      if self.combined_return:
+        check(lib.lewi_ep_combine_return(st(), ptr(self.dxs), ptr(self.urows), ptr(self.umeta), ptr(self.uret),
+                                         ptr(self.utotal), p if self.phases > 1 else -1, self.s_dxrecv.c_ptrs, k, d, G,
+                                         self.rmax, self.umax, self.bwd_threads), "lewi_ep_combine_return")
+        L._mark("ep_combine_return_dx")
+
+    self._pipeline(push, gemms, give_back, first=shared_expert, last=all_weight_grads)
     _, dlb, dw = L.router_topk_bwd(c["logits"], tb.topk_idx, None, want_f32=False, want_bf16=True, dw_partial=self.dw_slot,
                                    pad_pos=self.slot_ids)
     L._mark("router_topk_bwd")
@@ -627,8 +769,11 @@ class ExpertParallelP2P:
     L._mark("router_dx")
     grads["dw_router"] = ops.grouped_gemm_tn(x, dlb, None, 1, out_dtype=torch.float32)[0]
     L._mark("router_dw")
-    grads["dx"] = ops.gather_reduce(self.dx_slot, self.slot_ids, None, x.dtype, add0=dxsh[0] if dxsh else None,
-                                    add1=dx_r)
+    if self.combined_return:
+      grads["dx"] = ops.gather_reduce(self.dx_recv, self.comb[:t], None, x.dtype, add0=dxsh[0] if dxsh else None, add1=dx_r)
+    else:
+      grads["dx"] = ops.gather_reduce(self.dx_slot, self.slot_ids, None, x.dtype, add0=dxsh[0] if dxsh else None,
+                                      add1=dx_r)
     L._mark("combine_bwd_reduce")
     return grads
 

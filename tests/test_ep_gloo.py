@@ -83,3 +83,18 @@ def test_plan_split_sizes():
   p1 = ep.make_plan(counts, 1, 2)
   assert p0.send_splits == [3, 7] and p0.recv_splits == [3, 5] and p0.n_recv == 8
   assert p1.send_splits == [5, 7] and p1.recv_splits == [7, 7]
+
+
+def test_range_bounds_cover_all_local_experts():
+  from lewi_surge_b200 import ep
+  assert ep.range_bounds(16, 4) == [0, 4, 8, 12, 16]
+  assert ep.range_bounds(16, 4, [1, 3, 3, 1]) == [0, 2, 8, 14, 16]
+  assert ep.range_bounds(64, 1) == [0, 64]
+  # more ranges than experts: one expert each, the empty ranges are dropped
+  assert ep.range_bounds(2, 4, [1, 1, 1, 1]) == [0, 1, 2]
+  for el in (1, 3, 16, 64):
+    for w in ([1, 1], [1, 5, 1], [2, 1, 1, 1, 3]):
+      b = ep.range_bounds(el, len(w), w)
+      assert b[0] == 0 and b[-1] == el and all(x < y for x, y in zip(b, b[1:]))
+  with pytest.raises(ValueError):
+    ep.range_bounds(8, 2, [1, 0])
