@@ -246,8 +246,11 @@ def main():
   ap.add_argument("--ep-phases", type=int, default=None, help="ranges of local experts the exchange is pipelined over")
   ap.add_argument("--ep-range-weights", default=None,
                   help="relative sizes of the ranges, e.g. 1,3,3,1 (default: --ep-phases equal ranges)")
-  ap.add_argument("--ep-separate-return", action="store_true",
-                  help="A/B switch: rows go back with a transfer kernel of their own instead of the GEMM epilogue")
+  ap.add_argument("--ep-push", choices=["slots", "unique"], default=None,
+                  help="rows travel once per (token, expert) slot, or once per (token, destination rank)")
+  ap.add_argument("--ep-return", choices=["fused", "kernel", "combined"], default=None,
+                  help="rows come back per slot from the GEMM epilogues, per slot by a transfer kernel, or as one partial "
+                       "row per token and rank (needs --ep-push unique)")
   ap.add_argument("--ep-dw-per-range", action="store_true",
                   help="A/B switch: weight-gradient GEMMs range by range instead of once after the last range")
   ap.add_argument("--preload-s", type=float, default=2.0,
@@ -293,7 +296,7 @@ def main():
                                     phases=args.ep_phases, sync=args.ep_sync,
                                     exchange_threads=tuple(int(v) for v in args.ep_threads.split(",")),
                                     dw_down_last=not args.ep_dw_down_first, dw_deferred=not args.ep_dw_per_range,
-                                    range_weights=ep_range_weights(args), fused_return=not args.ep_separate_return)
+                                    range_weights=ep_range_weights(args), **ep_exchange_mode(args))
     else:
       runner = ep.ExpertParallelLayer(w, c["k"], c["E"], dist.group.WORLD)
     step_fn = lambda: runner.step(x, dout)
@@ -605,6 +608,17 @@ def ep_range_weights(args):
   return [float(v) for v in args.ep_range_weights.split(",")] if args.ep_range_weights else None
 
 
+def ep_exchange_mode(args):
+  """Keyword arguments of ExpertParallelP2P for --ep-push / --ep-return (unset: the class defaults)."""
+  kw = {}
+  if args.ep_push is not None:
+    kw["unique_push"] = args.ep_push == "unique"
+  if args.ep_return is not None:
+    kw["fused_return"] = args.ep_return == "fused"
+    kw["combined_return"] = args.ep_return == "combined"
+  return kw
+
+
 def ep_parity_check(args, c, rank, world, device, torch, dist, tokens=1024):
   """One small expert-parallel step (`tokens` per rank, the workload's widths) checked against the CPU oracle on the
   concatenated batch: out and dx of every rank, the owners' expert weight gradients.  Runs before the timed region;
@@ -623,7 +637,7 @@ def ep_parity_check(args, c, rank, world, device, torch, dist, tokens=1024):
                        torch.from_numpy(bias).to(device) if bias is not None else None)
   runner = ep.ExpertParallelP2P(w, k, E, tokens, d, dist.group.WORLD, phases=args.ep_phases, sync=args.ep_sync,
                                 dw_deferred=not args.ep_dw_per_range, range_weights=ep_range_weights(args),
-                                fused_return=not args.ep_separate_return)
+                                **ep_exchange_mode(args))
   sl = slice(rank * tokens, (rank + 1) * tokens)
   out, g = runner.step(bf(full["x"][sl]), bf(full["dout"][sl]))
   status = _lib.last_status()

@@ -544,8 +544,50 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         if (rows_valid > 0 && t.n0 + col_half * 128 < n_end) dsw_load(t.n0 + col_half * 128);
       }
 
+      // What the epilogue needs per row besides the accumulator is fetched now, while the tensor cores still work on
+      // the tile: the row's scale (a dependent pair of loads under SWIGLU / DSWIGLU), rank-one factor or destination.
+      [[maybe_unused]] float row_sc = 1.0f, row_r1 = 0.f;
+      [[maybe_unused]] unsigned long long my_dst = 0;
+      if (lane < rows_valid) {
+        if constexpr (EPI == PLAIN) {
+          if (a.row_scale != nullptr) row_sc = a.row_scale[wrow0 + lane];
+          if (a.r1_row != nullptr) row_r1 = a.r1_row[wrow0 + lane];
+        } else if constexpr (EPI == SWIGLU || EPI == DSWIGLU) {
+          if (a.scale_src != nullptr) {
+            const long long gi = a.scale_idx != nullptr ? (long long)a.scale_idx[wrow0 + lane] : wrow0 + lane;
+            row_sc = gi >= 0 ? a.scale_src[gi] : 0.f;
+          }
+        } else if constexpr (EPI == SCATTER) {
+          const int code = a.ret[wrow0 + lane];
+          if (code >= 0) {
+            const int rank = code >> kRetSlotBits;
+            const long long slot = code & ((1 << kRetSlotBits) - 1);
+            if (rank < a.ret_ranks && slot < a.ret_slots)
+              my_dst = reinterpret_cast<unsigned long long>(a.ret_out[rank]) + (unsigned long long)slot * a.N * 2;
+            else
+              raise_status(LEWI_STATUS_BAD_INDEX);
+          }
+        }
+      } else if constexpr (EPI == SWIGLU || EPI == DSWIGLU) {
+        if (a.scale_src != nullptr) row_sc = 0.f;
+      }
+
       uint32_t acc = 0;
+      bool acc_held = false;
+      // The accumulator goes back to the MMA warp as soon as this warp has read its last piece of it, before that
+      // piece is converted and stored.
+      auto release_acc = [&]() {
+        if (!acc_held) return;
+        acc_held = false;
+        ptx::tc_fence_before();
+        __syncwarp();
+        if (lane == 0) {
+          if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(acc), 0));
+          else ptx::mbar_arrive(tempty_bar(acc));
+        }
+      };
       if (has_acc) {
+        acc_held = true;
         acc = acc_it & 1u;
         const uint32_t acc_ph = (acc_it >> 1) & 1u;
         const bool got = ptx::mbar_wait(tfull_bar(acc), acc_ph, abort_flag);
@@ -558,10 +600,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       if constexpr (EPI == PLAIN) {
         // out [rows, N] through tm_c: bf16 tiles of 64 columns or f32 tiles of 32 columns
         if (rows_valid > 0) {
-          const long long grow = wrow0 + lane;
-          const bool live = lane < rows_valid;
-          const float sc = (a.row_scale != nullptr && live) ? a.row_scale[grow] : 1.0f;
-          const float r1 = (a.r1_row != nullptr && live) ? a.r1_row[grow] : 0.f;
+          const float sc = row_sc, r1 = row_r1;
           uint8_t* buf = nullptr;
 #pragma unroll 1
           for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
@@ -573,6 +612,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (has_acc) {
               ptx::tmem_ld_32x32(t_addr + c * 32, r);
               ptx::tmem_ld_wait();
+              if (c == col_half * 4 + 3 || n + 32 >= n_end) release_acc();
             }
 #pragma unroll
             for (int q = 0; q < 32; ++q) v[q] = has_acc ? __uint_as_float(r[q]) * sc : 0.f;
@@ -601,14 +641,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         const int f = a.N;
         const int n64 = t.n0 + col_half * 64;
         if (rows_valid > 0 && n64 < n_end) {
-          float hsc = 1.0f;
-          if (a.scale_src != nullptr) {
-            hsc = 0.f;
-            if (lane < rows_valid) {
-              const long long gi = a.scale_idx != nullptr ? (long long)a.scale_idx[wrow0 + lane] : wrow0 + lane;
-              if (gi >= 0) hsc = a.scale_src[gi];
-            }
-          }
+          const float hsc = row_sc;
           if (lane == 0) ptx::bulk_wait_read();   // the previous tile's three stores have read the staging tiles
           __syncwarp();
           uint8_t* buf_g = stage;
@@ -651,14 +684,8 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         }
       } else if constexpr (EPI == DSWIGLU) {
         const int f = a.N;
-        float dsc = 1.0f, dw_acc = 0.f;
-        if (a.scale_src != nullptr) {
-          dsc = 0.f;
-          if (lane < rows_valid) {
-            const long long gi = a.scale_idx != nullptr ? (long long)a.scale_idx[wrow0 + lane] : wrow0 + lane;
-            if (gi >= 0) dsc = a.scale_src[gi];
-          }
-        }
+        const float dsc = row_sc;
+        float dw_acc = 0.f;
         uint8_t* my_g = stage + lane * 128;   // this lane's row of the swizzled g tile; the u tile is 4 KB further
 #pragma unroll 1
         for (int hf = 0; hf < 2 && ok; ++hf) {
@@ -718,18 +745,6 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
         // row, 8 lanes per 128-byte row piece and 4 rows per instruction, with plain 16-byte stores (the destination
         // may be a peer's memory: the rows travel while the tensor cores work on the next tile).
         if (rows_valid > 0) {
-          unsigned long long my_dst = 0;
-          if (lane < rows_valid) {
-            const int code = a.ret[wrow0 + lane];
-            if (code >= 0) {
-              const int rank = code >> kRetSlotBits;
-              const long long slot = code & ((1 << kRetSlotBits) - 1);
-              if (rank < a.ret_ranks && slot < a.ret_slots)
-                my_dst = reinterpret_cast<unsigned long long>(a.ret_out[rank]) + (unsigned long long)slot * a.N * 2;
-              else
-                raise_status(LEWI_STATUS_BAD_INDEX);
-            }
-          }
 #pragma unroll 1
           for (int c = col_half * 4; c < col_half * 4 + 4; ++c) {
             const int n = t.n0 + c * 32;
@@ -739,6 +754,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (has_acc) {
               ptx::tmem_ld_32x32(t_addr + c * 32, r);
               ptx::tmem_ld_wait();
+              if (c == col_half * 4 + 3 || n + 32 >= n_end) release_acc();
             }
 #pragma unroll
             for (int q = 0; q < 32; ++q) v[q] = has_acc ? __uint_as_float(r[q]) : 0.f;
@@ -778,6 +794,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
             if (has_acc) {
               ptx::tmem_ld_32x32(t_addr + c * 32, r);
               ptx::tmem_ld_wait();
+              if (c == col_half * 4 + 3 || n + 32 >= n_end) release_acc();
             }
 #pragma unroll
             for (int q = 0; q < 32; ++q) v[q] = has_acc ? __uint_as_float(r[q]) : 0.f;
@@ -798,12 +815,7 @@ grouped_gemm_kernel(const __grid_constant__ CUtensorMap tm_a, const __grid_const
       }
 
       if (has_acc) {
-        ptx::tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          if constexpr (PAIR) ptx::mbar_arrive_cluster(ptx::map_to_cta(tempty_bar(acc), 0));
-          else ptx::mbar_arrive(tempty_bar(acc));
-        }
+        release_acc();   // (warps without rows or columns of this tile have not read it)
         ++acc_it;
       }
     }
