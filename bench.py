@@ -585,6 +585,9 @@ def main():
       "roofline": roofline, "cpu_baseline": cpu_baseline, "ep_parity": ep_parity,
       "summary": summary, "kernels": table,
   }
+  if world > 1 and args.ep_impl == "p2p":
+    # rank 0's share of the exchange: rows that left for other ranks, counted per slot and once per destination rank
+    line["exchange"] = runner.exchange_summary(runner.last_topk_idx)
   print(json.dumps(line), flush=True)
   if world > 1:
     dist.destroy_process_group()

@@ -182,7 +182,6 @@ __global__ void __launch_bounds__(256) conv_dw_reduce_kernel(const float* __rest
 
 constexpr int kGdnChunk = 64;
 constexpr int kGdnThreads = 256;
-constexpr int kGdnVBlock = 32;
 constexpr int kGdnMaxDim = 128;
 
 __device__ __forceinline__ float gdn_round_bf16(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
@@ -195,11 +194,11 @@ struct GdnDims {
 inline size_t gdn_prep_smem_bytes(int K, int V) {
   const int C = kGdnChunk, KP = K + 1, VP = V + 1;
   const int QP = KP > VP ? (KP > C + 1 ? KP : C + 1) : (VP > C + 1 ? VP : C + 1);
-  return (size_t)(2 * C * KP + C * QP + C * (C + 1) + 2 * C) * 4;
+  return (size_t)(C * KP + C * QP + C * (C + 1) + 3 * C) * 4;
 }
-inline size_t gdn_scan_smem_bytes(int K) {
+inline size_t gdn_scan_smem_bytes(int K, int vb) {
   const int C = kGdnChunk, KP = K + 1;
-  return (size_t)(K * kGdnVBlock + 3 * C * KP + C * kGdnVBlock + C * (C + 1) + C) * 4;
+  return (size_t)(K * vb + 3 * C * KP + C * vb + C * (C + 1) + 3 * C) * 4;
 }
 
 __host__ __device__ inline long long gdn_chunk_ws_bytes(int K, int V) {
@@ -215,29 +214,53 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_prep_kernel(const __nv_
   extern __shared__ float gdn_smem[];
   constexpr int C = kGdnChunk;
   const int K = D.K, V = D.V, KP = K + 1, VP = V + 1;
+  // k * beta (rounded to bf16) is recomputed from k wherever it is needed instead of being kept: with one array less
+  // two CTAs fit on an SM, and the phases in which few threads work (prefix sum, substitution) overlap another CTA.
   float* sK = gdn_smem;                 // [C][KP]   k
-  float* sKB = sK + C * KP;             // [C][KP]   k * beta (bf16-rounded), later k_beta * exp(gcs)
-  float* sQ = sKB + C * KP;             // [C][QP]   scaled q, later A while it is built, later v * beta
+  float* sQ = sK + C * KP;              // [C][QP]   scaled q, later A while it is built, later v * beta
   const int QP = max(max(KP, VP), C + 1);   // the area also holds A [C][C+1] during the substitution
   float* sS = sQ + C * QP;              // [C][C+1]  S, then A
   float* sG = sS + C * (C + 1);         // [C] gcs
   float* sB = sG + C;                   // [C] beta
+  float* sE = sB + C;                   // [C] exp(gcs)
   const int n = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x;
   const long long tok0 = (long long)n * C;
   const float scale = gdn_round_bf16(rsqrtf((float)K));
   // loads (tokens past the end of the sequence are zero rows with g = 0, beta = 0)
-  for (int i = tid; i < C * K; i += kGdnThreads) {
-    const int r = i / K, c = i - r * K;
-    const long long t = tok0 + r;
-    float kv = 0.f, qv = 0.f;
-    if (t < D.S) {
-      const long long off = (((long long)b * D.S + t) * D.H + h) * K + c;
-      kv = __bfloat162float(k[off]);
-      qv = gdn_round_bf16(__bfloat162float(q[off]) * scale);
+  if ((K & 7) == 0) {   // 16-byte pieces of the bf16 rows
+    const int kv8 = K / 8;
+    for (int i = tid; i < C * kv8; i += kGdnThreads) {
+      const int r = i / kv8, c = (i - r * kv8) * 8;
+      const long long t = tok0 + r;
+      uint4 kq[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+      if (t < D.S) {
+        const long long off = (((long long)b * D.S + t) * D.H + h) * K + c;
+        kq[0] = *reinterpret_cast<const uint4*>(k + off);
+        kq[1] = *reinterpret_cast<const uint4*>(q + off);
+      }
+      float kf[8], qf[8];
+      lewi::Elem<__nv_bfloat16>::unpack(kq[0], kf);
+      lewi::Elem<__nv_bfloat16>::unpack(kq[1], qf);
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        sK[r * KP + c + x] = kf[x];
+        sQ[r * QP + c + x] = gdn_round_bf16(qf[x] * scale);
+      }
     }
-    sK[r * KP + c] = kv;
-    sQ[r * QP + c] = qv;
+  } else {
+    for (int i = tid; i < C * K; i += kGdnThreads) {
+      const int r = i / K, c = i - r * K;
+      const long long t = tok0 + r;
+      float kv = 0.f, qv = 0.f;
+      if (t < D.S) {
+        const long long off = (((long long)b * D.S + t) * D.H + h) * K + c;
+        kv = __bfloat162float(k[off]);
+        qv = gdn_round_bf16(__bfloat162float(q[off]) * scale);
+      }
+      sK[r * KP + c] = kv;
+      sQ[r * QP + c] = qv;
+    }
   }
   if (tid < C) {
     const long long t = tok0 + tid;
@@ -252,32 +275,59 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_prep_kernel(const __nv_
       sG[i] = run;
     }
   }
-  for (int i = tid; i < C * K; i += kGdnThreads) {
-    const int r = i / K, c = i - r * K;
-    sKB[r * KP + c] = gdn_round_bf16(sK[r * KP + c] * sB[r]);
-  }
   __syncthreads();
+  if (tid < C) sE[tid] = __expf(sG[tid]);
   uint8_t* my_ws = ws + (((long long)b * D.N + n) * D.H + h) * gdn_chunk_ws_bytes(K, V);
   __nv_bfloat16* u_out = reinterpret_cast<__nv_bfloat16*>(my_ws);
   __nv_bfloat16* w_out = u_out + C * V;
   float* attn_out = reinterpret_cast<float*>(w_out + C * K);
   float* gcs_out = attn_out + C * C;
-  // S (strictly lower) and the in-chunk attention (lower, diagonal included)
-  for (int i = tid; i < C * C; i += kGdnThreads) {
-    const int r = i / C, c = i - r * C;
-    float s_acc = 0.f, a_acc = 0.f;
-    if (c <= r) {
-      for (int x = 0; x < K; ++x) {
-        const float kc = sK[c * KP + x];
-        s_acc = fmaf(sKB[r * KP + x], kc, s_acc);
-        a_acc = fmaf(sQ[r * QP + x], kc, a_acc);
+  // S (strictly lower) and the in-chunk attention (lower, diagonal included).  Register tiles: a thread owns rows
+  // 4*tr .. 4*tr+3 and columns tc, tc+16, tc+32, tc+48 (neighbouring lanes read neighbouring rows of k: no bank
+  // conflicts with the odd row stride), 32 fused multiply-adds per 12 shared-memory loads; sums run over x ascending.
+  {
+    const int tr = tid >> 4, tc = tid & 15;
+    float s_acc[4][4], a_acc[4][4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        s_acc[i][j] = 0.f;
+        a_acc[i][j] = 0.f;
       }
-      const float dec = __expf(sG[r] - sG[c]);
-      s_acc = c < r ? gdn_round_bf16(s_acc) * dec : 0.f;
-      a_acc = gdn_round_bf16(a_acc) * dec;
+    if (tc <= tr * 4 + 3) {   // otherwise every element of the tile lies above the diagonal
+      const float b4[4] = {sB[tr * 4], sB[tr * 4 + 1], sB[tr * 4 + 2], sB[tr * 4 + 3]};
+      for (int x = 0; x < K; ++x) {
+        float kb[4], qq[4], kc[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          kb[i] = gdn_round_bf16(sK[(tr * 4 + i) * KP + x] * b4[i]);
+          qq[i] = sQ[(tr * 4 + i) * QP + x];
+          kc[i] = sK[(tc + 16 * i) * KP + x];
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            s_acc[i][j] = fmaf(kb[i], kc[j], s_acc[i][j]);
+            a_acc[i][j] = fmaf(qq[i], kc[j], a_acc[i][j]);
+          }
+      }
     }
-    sS[r * (C + 1) + c] = s_acc;
-    attn_out[i] = a_acc;
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int r = tr * 4 + i, c = tc + 16 * j;
+        float sv = 0.f, av = 0.f;
+        if (c <= r) {
+          const float dec = __expf(sG[r] - sG[c]);
+          sv = c < r ? gdn_round_bf16(s_acc[i][j]) * dec : 0.f;
+          av = gdn_round_bf16(a_acc[i][j]) * dec;
+        }
+        sS[r * (C + 1) + c] = sv;
+        attn_out[r * C + c] = av;
+      }
   }
   if (tid < C) gcs_out[tid] = sG[tid];
   __syncthreads();
@@ -286,11 +336,17 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_prep_kernel(const __nv_
   float* sA = sQ;   // [C][C+1]
   __syncthreads();
   if (tid < C) {
+    // the column stays in registers (both loops unrolled); terms with j < c multiply an exact zero, so the sum equals
+    // the one that starts at j = c
     const int c = tid;
+    float colv[C];
+#pragma unroll
     for (int i = 0; i < C; ++i) {
       float acc = i == c ? 1.f : 0.f;
-      for (int j = c; j < i; ++j) acc = fmaf(-sS[i * (C + 1) + j], sA[j * (C + 1) + c], acc);   // A[j,c] = 0 for j < c
-      sA[i * (C + 1) + c] = i < c ? 0.f : acc;
+#pragma unroll
+      for (int j = 0; j < i; ++j) acc = fmaf(-sS[i * (C + 1) + j], colv[j], acc);
+      colv[i] = i < c ? 0.f : acc;
+      sA[i * (C + 1) + c] = colv[i];
     }
   }
   __syncthreads();
@@ -300,33 +356,77 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_prep_kernel(const __nv_
     sS[r * (C + 1) + c] = sA[r * (C + 1) + c];
   }
   __syncthreads();
-  for (int i = tid; i < C * V; i += kGdnThreads) {
-    const int r = i / V, c = i - r * V;
-    const long long t = tok0 + r;
-    float vv = 0.f;
-    if (t < D.S) vv = __bfloat162float(v[(((long long)b * D.S + t) * D.H + h) * V + c]);
-    sQ[r * QP + c] = gdn_round_bf16(vv * sB[r]);
-  }
-  for (int i = tid; i < C * K; i += kGdnThreads) {
-    const int r = i / K, c = i - r * K;
-    sKB[r * KP + c] *= __expf(sG[r]);
+  if ((V & 7) == 0) {
+    const int vv8 = V / 8;
+    for (int i = tid; i < C * vv8; i += kGdnThreads) {
+      const int r = i / vv8, c = (i - r * vv8) * 8;
+      const long long t = tok0 + r;
+      uint4 raw = make_uint4(0, 0, 0, 0);
+      if (t < D.S) raw = *reinterpret_cast<const uint4*>(v + (((long long)b * D.S + t) * D.H + h) * V + c);
+      float vf[8];
+      lewi::Elem<__nv_bfloat16>::unpack(raw, vf);
+      const float br = sB[r];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) sQ[r * QP + c + x] = gdn_round_bf16(vf[x] * br);
+    }
+  } else {
+    for (int i = tid; i < C * V; i += kGdnThreads) {
+      const int r = i / V, c = i - r * V;
+      const long long t = tok0 + r;
+      float vv = 0.f;
+      if (t < D.S) vv = __bfloat162float(v[(((long long)b * D.S + t) * D.H + h) * V + c]);
+      sQ[r * QP + c] = gdn_round_bf16(vv * sB[r]);
+    }
   }
   __syncthreads();
-  // u = A v_beta, w = A (k_beta exp(gcs)); A is lower triangular
-  for (int i = tid; i < C * V; i += kGdnThreads) {
-    const int r = i / V, c = i - r * V;
-    float acc = 0.f;
-    for (int j = 0; j <= r; ++j) acc = fmaf(sS[r * (C + 1) + j], sQ[j * QP + c], acc);
-    u_out[i] = __float2bfloat16_rn(acc);
-  }
-  for (int i = tid; i < C * K; i += kGdnThreads) {
-    const int r = i / K, c = i - r * K;
-    float acc = 0.f;
-    for (int j = 0; j <= r; ++j) acc = fmaf(sS[r * (C + 1) + j], sKB[j * KP + c], acc);
-    w_out[i] = __float2bfloat16_rn(acc);
+  // u = A v_beta, w = A (k_beta exp(gcs)); A is lower triangular with exact zeros above the diagonal, so a tile of
+  // four rows sums j up to its last row.  A thread owns rows 4*tr .. 4*tr+3 and columns tc + 16*i of a 128-column
+  // block: 32 fused multiply-adds per 12 shared-memory loads, sums over j ascending.
+  {
+    const int tr = tid >> 4, tc = tid & 15;
+    for (int pass = 0; pass < 2; ++pass) {
+      const float* src = pass == 0 ? sQ : sK;           // v_beta, then k (made k_beta exp(gcs) below)
+      const int ld = pass == 0 ? QP : KP, width = pass == 0 ? V : K;
+      __nv_bfloat16* dst = pass == 0 ? u_out : w_out;
+      for (int cb = 0; cb < width; cb += 128) {
+        float acc[4][8];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) acc[i][c] = 0.f;
+        for (int j = 0; j <= tr * 4 + 3; ++j) {
+          float av[4], xv[8];
+#pragma unroll
+          for (int i = 0; i < 4; ++i) av[i] = sS[(tr * 4 + i) * (C + 1) + j];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int col = cb + tc + 16 * c;
+            xv[c] = col < width ? src[j * ld + col] : 0.f;
+          }
+          if (pass == 1) {
+            const float bj = sB[j], ej = sE[j];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) xv[c] = gdn_round_bf16(xv[c] * bj) * ej;
+          }
+#pragma unroll
+          for (int i = 0; i < 4; ++i)
+#pragma unroll
+            for (int c = 0; c < 8; ++c) acc[i][c] = fmaf(av[i], xv[c], acc[i][c]);
+        }
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            const int col = cb + tc + 16 * c;
+            if (col < width) dst[(tr * 4 + i) * width + col] = __float2bfloat16_rn(acc[i][c]);
+          }
+      }
+    }
   }
 }
 
+// VB = state columns per CTA: 32 (more CTAs) or 64 (half as many CTAs, twice the multiply-adds per shared-memory load).
+template <int VB>
 __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_scan_kernel(const __nv_bfloat16* __restrict__ q,
                                                                      const __nv_bfloat16* __restrict__ k,
                                                                      const uint8_t* __restrict__ ws,
@@ -334,7 +434,10 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_scan_kernel(const __nv_
                                                                      __nv_bfloat16* __restrict__ o,
                                                                      float* __restrict__ h_final, GdnDims D) {
   extern __shared__ float gdn_smem[];
-  constexpr int C = kGdnChunk, VB = kGdnVBlock;
+  constexpr int C = kGdnChunk;
+  constexpr int CG = VB / 4;                 // groups of 4 adjacent columns
+  constexpr int RG = kGdnThreads / CG;       // row groups
+  constexpr int RPT = C / RG;                // chunk rows per thread
   const int K = D.K, V = D.V, KP = K + 1;
   float* sH = gdn_smem;               // [K][VB]      this CTA's columns of the state
   float* sQ = sH + K * VB;            // [C][KP]      q exp(gcs)
@@ -343,10 +446,11 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_scan_kernel(const __nv_
   float* sVn = sW + C * KP;           // [C][VB]      u, then v_new
   float* sAt = sVn + C * VB;          // [C][C+1]     in-chunk attention
   float* sG = sAt + C * (C + 1);      // [C]
+  float* sEq = sG + C;                // [C] exp(gcs)
+  float* sEk = sEq + C;               // [C] exp(gcs_last - gcs)
   const int vb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int tid = threadIdx.x;
   const int v0 = vb * VB;
-  const int col = tid % VB, grp = tid / VB;      // 8 groups of 32 columns
   const float scale = gdn_round_bf16(rsqrtf((float)K));
   for (int i = tid; i < K * VB; i += kGdnThreads) {
     const int r = i / VB, c = i - r * VB;
@@ -360,21 +464,52 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_scan_kernel(const __nv_
     const float* attn_in = reinterpret_cast<const float*>(w_in + C * K);
     const float* gcs_in = attn_in + C * C;
     __syncthreads();   // the previous chunk is done with every buffer
-    if (tid < C) sG[tid] = gcs_in[tid];
+    if (tid < C) {
+      const float gc = gcs_in[tid], gl = gcs_in[C - 1];
+      sG[tid] = gc;
+      sEq[tid] = __expf(gc);        // q rows carry exp(gcs)
+      sEk[tid] = __expf(gl - gc);   // k rows carry exp(gcs_last - gcs)
+    }
     __syncthreads();
     const float g_last = sG[C - 1];
-    for (int i = tid; i < C * K; i += kGdnThreads) {
-      const int r = i / K, c = i - r * K;
-      const long long t = tok0 + r;
-      float kv = 0.f, qv = 0.f;
-      if (t < D.S) {
-        const long long off = (((long long)b * D.S + t) * D.H + h) * K + c;
-        kv = __bfloat162float(k[off]);
-        qv = gdn_round_bf16(__bfloat162float(q[off]) * scale);
+    if ((K & 7) == 0) {   // 16-byte pieces of the bf16 rows
+      const int kv8 = K / 8;
+      for (int i = tid; i < C * kv8; i += kGdnThreads) {
+        const int r = i / kv8, c = (i - r * kv8) * 8;
+        const long long t = tok0 + r;
+        uint4 kq[2] = {make_uint4(0, 0, 0, 0), make_uint4(0, 0, 0, 0)};
+        if (t < D.S) {
+          const long long off = (((long long)b * D.S + t) * D.H + h) * K + c;
+          kq[0] = *reinterpret_cast<const uint4*>(k + off);
+          kq[1] = *reinterpret_cast<const uint4*>(q + off);
+        }
+        const uint4 wv = *reinterpret_cast<const uint4*>(w_in + r * K + c);
+        float kf[8], qf[8], wf[8];
+        lewi::Elem<__nv_bfloat16>::unpack(kq[0], kf);
+        lewi::Elem<__nv_bfloat16>::unpack(kq[1], qf);
+        lewi::Elem<__nv_bfloat16>::unpack(wv, wf);
+        const float eq = sEq[r], ek = sEk[r];
+#pragma unroll
+        for (int x = 0; x < 8; ++x) {
+          sQ[r * KP + c + x] = gdn_round_bf16(qf[x] * scale) * eq;
+          sK[r * KP + c + x] = kf[x] * ek;
+          sW[r * KP + c + x] = wf[x];
+        }
       }
-      sQ[r * KP + c] = qv * __expf(sG[r]);
-      sK[r * KP + c] = kv * __expf(g_last - sG[r]);
-      sW[r * KP + c] = __bfloat162float(w_in[i]);
+    } else {
+      for (int i = tid; i < C * K; i += kGdnThreads) {
+        const int r = i / K, c = i - r * K;
+        const long long t = tok0 + r;
+        float kv = 0.f, qv = 0.f;
+        if (t < D.S) {
+          const long long off = (((long long)b * D.S + t) * D.H + h) * K + c;
+          kv = __bfloat162float(k[off]);
+          qv = gdn_round_bf16(__bfloat162float(q[off]) * scale);
+        }
+        sQ[r * KP + c] = qv * sEq[r];
+        sK[r * KP + c] = kv * sEk[r];
+        sW[r * KP + c] = __bfloat162float(w_in[i]);
+      }
     }
     for (int i = tid; i < C * VB; i += kGdnThreads) {
       const int r = i / VB, c = i - r * VB;
@@ -385,50 +520,88 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_chunk_scan_kernel(const __nv_
       sAt[r * (C + 1) + c] = attn_in[i];
     }
     __syncthreads();
-    // v_new = u - w h   (thread: column `col`, rows grp*8 .. +7)
-    float vn[8], acc_o[8];
+    // Register tiles: a thread owns 4 adjacent state columns (c0..c0+3) and RPT adjacent rows of the chunk's 64; of the
+    // state's K rows it owns rows rg, rg+RG, ...  Every sum runs over its index in ascending order.
+    const int c0 = (tid % CG) * 4, rg = tid / CG;
+    const int r0 = rg * RPT;
+    float vn[RPT][4], acc_o[RPT][4];
 #pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      vn[x] = 0.f;
-      acc_o[x] = 0.f;
-    }
+    for (int x = 0; x < RPT; ++x)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        vn[x][c] = 0.f;
+        acc_o[x][c] = 0.f;
+      }
+    // w h and (q exp(gcs)) h with the OLD state
     for (int kk = 0; kk < K; ++kk) {
-      const float hv = sH[kk * VB + col];
+      const float4 hv = *reinterpret_cast<const float4*>(&sH[kk * VB + c0]);
+      const float h4[4] = {hv.x, hv.y, hv.z, hv.w};
 #pragma unroll
-      for (int x = 0; x < 8; ++x) {
-        const int r = grp * 8 + x;
-        vn[x] = fmaf(sW[r * KP + kk], hv, vn[x]);
-        acc_o[x] = fmaf(sQ[r * KP + kk], hv, acc_o[x]);      // (q exp(gcs)) h with the OLD state
+      for (int x = 0; x < RPT; ++x) {
+        const float wv = sW[(r0 + x) * KP + kk], qv = sQ[(r0 + x) * KP + kk];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          vn[x][c] = fmaf(wv, h4[c], vn[x][c]);
+          acc_o[x][c] = fmaf(qv, h4[c], acc_o[x][c]);
+        }
       }
     }
-    __syncthreads();   // every thread has read u from sVn
+    // v_new = u - w h, written over u (a thread reads and writes only its own elements)
 #pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      const int r = grp * 8 + x;
-      vn[x] = sVn[r * VB + col] - vn[x];
+    for (int x = 0; x < RPT; ++x) {
+      float4* cell = reinterpret_cast<float4*>(&sVn[(r0 + x) * VB + c0]);
+      const float4 u4 = *cell;
+      *cell = make_float4(u4.x - vn[x][0], u4.y - vn[x][1], u4.z - vn[x][2], u4.w - vn[x][3]);
     }
-    __syncthreads();
-#pragma unroll
-    for (int x = 0; x < 8; ++x) sVn[(grp * 8 + x) * VB + col] = vn[x];
     __syncthreads();
     // o = (q exp(gcs)) h + attn v_new
     for (int j = 0; j < C; ++j) {
-      const float vj = sVn[j * VB + col];
+      const float4 vj = *reinterpret_cast<const float4*>(&sVn[j * VB + c0]);
+      const float v4[4] = {vj.x, vj.y, vj.z, vj.w};
 #pragma unroll
-      for (int x = 0; x < 8; ++x) acc_o[x] = fmaf(sAt[(grp * 8 + x) * (C + 1) + j], vj, acc_o[x]);
+      for (int x = 0; x < RPT; ++x) {
+        const float av = sAt[(r0 + x) * (C + 1) + j];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) acc_o[x][c] = fmaf(av, v4[c], acc_o[x][c]);
+      }
     }
 #pragma unroll
-    for (int x = 0; x < 8; ++x) {
-      const long long t = tok0 + grp * 8 + x;
-      if (t < D.S && v0 + col < V) o[(((long long)b * D.S + t) * D.H + h) * V + v0 + col] = __float2bfloat16_rn(acc_o[x]);
+    for (int x = 0; x < RPT; ++x) {
+      const long long t = tok0 + r0 + x;
+      if (t >= D.S) continue;
+      __nv_bfloat16* dst = o + (((long long)b * D.S + t) * D.H + h) * V + v0 + c0;
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        if (v0 + c0 + c < V) dst[c] = __float2bfloat16_rn(acc_o[x][c]);
     }
-    // h <- h exp(gcs_last) + (k exp(gcs_last - gcs))^T v_new   (thread: column `col`, state rows grp + 8*x)
+    // h <- h exp(gcs_last) + (k exp(gcs_last - gcs))^T v_new: state rows rg, rg + RG, ... of this thread's 4 columns
     const float dec = __expf(g_last);
-    for (int r0 = grp; r0 < K; r0 += kGdnThreads / VB) {
-      float acc = sH[r0 * VB + col] * dec;
-      for (int i = 0; i < C; ++i) acc = fmaf(sK[i * KP + r0], sVn[i * VB + col], acc);
-      sH[r0 * VB + col] = acc;   // every element of the state has one owner in this phase; others read it after the
-                                 // barrier at the top of the next chunk
+    for (int kr0 = rg; kr0 < K; kr0 += 4 * RG) {
+      float acc[4][4];
+#pragma unroll
+      for (int y = 0; y < 4; ++y) {
+        const int kr = kr0 + y * RG;
+        const float4 hv = kr < K ? *reinterpret_cast<const float4*>(&sH[kr * VB + c0]) : make_float4(0.f, 0.f, 0.f, 0.f);
+        acc[y][0] = hv.x * dec; acc[y][1] = hv.y * dec; acc[y][2] = hv.z * dec; acc[y][3] = hv.w * dec;
+      }
+      for (int i = 0; i < C; ++i) {
+        const float4 vi = *reinterpret_cast<const float4*>(&sVn[i * VB + c0]);
+        const float v4[4] = {vi.x, vi.y, vi.z, vi.w};
+#pragma unroll
+        for (int y = 0; y < 4; ++y) {
+          const int kr = kr0 + y * RG;
+          const float kv = kr < K ? sK[i * KP + kr] : 0.f;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) acc[y][c] = fmaf(kv, v4[c], acc[y][c]);
+        }
+      }
+      // every element of the state has one owner in this phase; others read it after the barrier at the top of the
+      // next chunk
+#pragma unroll
+      for (int y = 0; y < 4; ++y) {
+        const int kr = kr0 + y * RG;
+        if (kr < K) *reinterpret_cast<float4*>(&sH[kr * VB + c0]) = make_float4(acc[y][0], acc[y][1], acc[y][2], acc[y][3]);
+      }
     }
   }
   __syncthreads();

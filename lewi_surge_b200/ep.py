@@ -310,8 +310,15 @@ class ExpertParallelP2P:
   GEMMs in place and every output row goes back into the source's slot-ordered buffer, where the combine is a sum
   over k consecutive rows: by default straight from the epilogue of the down-projection (and dx) GEMM
   (`lewi_grouped_gemm_nn_return`, `lewi_grouped_gemm_dx_return`: a tile's rows travel while the next tile is being
-  multiplied), or with `fused_return=False` by a transfer kernel of its own (`lewi_ep_return_rows`).  The backward pass moves the
-  upstream gradient rows, dx and the routing-weight gradient pieces the same way.
+  multiplied), or with `fused_return=False` by a transfer kernel of its own (`lewi_ep_return_rows`).  The backward
+  pass moves the upstream gradient rows, dx and the routing-weight gradient pieces the same way; the weight
+  gradients of all ranges are one pair of GEMM launches after the last range (`dw_deferred`).
+
+  `unique_push=True` sends a token once per destination RANK instead of once per slot (top-6 over 8 ranks: 3.9
+  instead of 5.25 rows per token on the links): the owner copies the row to the padded rows of its experts
+  (`lewi_ep_local_rows`) before a range's GEMMs.  With `combined_return=True` the owner also adds up a token's local
+  expert outputs and returns one partial row per token (`lewi_ep_combine_return`); the source adds the partial rows
+  of the ranks it used.  Both are off by default: at 2 GPUs they measured slower than the slot-wise exchange.
 
   The local experts are worked on in `phases` ranges.  The exchange kernels run on their own stream and are small
   enough to share an SM with a grouped-GEMM CTA, so the rows of range p+1 arrive, and the outputs of range p-1
@@ -547,6 +554,7 @@ class ExpertParallelP2P:
     L._mark("router_logits")
     self.last_logits = logits
     tb = L.router_topk(logits, k)
+    self.last_topk_idx = tb.topk_idx
     L._mark("router_topk")
     routed = main.record_event()
     with torch.cuda.stream(comm):
@@ -780,3 +788,20 @@ class ExpertParallelP2P:
   def step(self, x, dout):
     out, cache = self.forward(x)
     return out, self.backward(dout, cache)
+
+  def exchange_summary(self, topk_idx):
+    """Rows this rank sends to OTHER ranks per pass for the routing `topk_idx` [T,k] (global expert ids), counted both
+    ways: once per (token, expert) slot and once per (token, destination rank); and the mode this layer runs in.
+    Synchronises (reads a few numbers back)."""
+    ranks = (topk_idx // self.el).to(torch.int64)
+    away = ranks != self.rank
+    per_rank = torch.zeros((topk_idx.shape[0], self.world), dtype=torch.bool, device=topk_idx.device)
+    per_rank.scatter_(1, ranks, True)
+    per_rank[:, self.rank] = False
+    slots, unique = int(away.sum().item()), int(per_rank.sum().item())
+    row_bytes = 2 * self.d
+    return dict(push="unique" if self.unique_push else "slots",
+                back="combined" if self.combined_return else ("fused" if self.fused_return else "kernel"),
+                ranges=self.phases, rows_sent_per_slot=slots, rows_sent_once_per_rank=unique,
+                push_bytes_per_pass=(unique if self.unique_push else slots) * row_bytes,
+                return_bytes_per_pass=(unique if self.combined_return else slots) * row_bytes)

@@ -57,3 +57,31 @@ def test_work_table_adds_up_to_the_layer():
   assert all(work[n][0] == "nvlink" and work[n][1] == 0 for n in ("ep_push_x", "ep_return_dx"))   # one GPU: nothing leaves
   w8 = bench.kernel_work(c, world=8)
   assert w8["ep_push_x"][1] == c["T"] * c["k"] * 2 * c["d"] * 7 / 8
+
+
+def test_exchange_flags_map_to_layer_arguments():
+  import argparse
+  import bench
+  ns = lambda **kw: argparse.Namespace(ep_push=None, ep_return=None, ep_range_weights=None, **kw)
+  assert bench.ep_exchange_mode(ns()) == {}
+  a = ns()
+  a.ep_push, a.ep_return = "unique", "combined"
+  assert bench.ep_exchange_mode(a) == {"unique_push": True, "fused_return": False, "combined_return": True}
+  a.ep_push, a.ep_return = "slots", "kernel"
+  assert bench.ep_exchange_mode(a) == {"unique_push": False, "fused_return": False, "combined_return": False}
+  a.ep_range_weights = "1,3,3,1"
+  assert bench.ep_range_weights(a) == [1.0, 3.0, 3.0, 1.0] and bench.ep_range_weights(ns()) is None
+
+
+def test_exchange_summary_counts_rows_both_ways():
+  import types
+  import torch
+  from lewi_surge_b200 import ep
+  me = types.SimpleNamespace(el=4, rank=1, world=4, d=8, unique_push=True, combined_return=False, fused_return=True,
+                             phases=2)
+  idx = torch.tensor([[0, 1, 5, 6], [4, 5, 6, 7], [12, 13, 0, 8]])
+  got = ep.ExpertParallelP2P.exchange_summary(me, idx)
+  # token 0: experts 0,1 on rank 0 (one row once per rank, two per slot); token 1 stays home; token 2: ranks 3,3,0,2
+  assert got["rows_sent_per_slot"] == 6 and got["rows_sent_once_per_rank"] == 4
+  assert got["push_bytes_per_pass"] == 4 * 16 and got["return_bytes_per_pass"] == 6 * 16
+  assert (got["push"], got["back"]) == ("unique", "fused")

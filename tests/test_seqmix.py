@@ -104,7 +104,8 @@ def test_gdn_kernel_matches_the_reference_outputs(cuda, case):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("b,s,h,kd,vd", [(1, 64, 1, 16, 32), (2, 300, 3, 128, 128), (1, 1000, 2, 64, 96), (1, 4096, 4, 128, 128)])
+@pytest.mark.parametrize("b,s,h,kd,vd", [(1, 64, 1, 16, 32), (2, 300, 3, 128, 128), (1, 1000, 2, 64, 96), (1, 4096, 4, 128, 128),
+                                            (4, 200, 12, 64, 128), (6, 130, 16, 128, 64)])  # the last two: 64 state columns per scan CTA
 def test_gdn_kernel_against_the_oracle(cuda, b, s, h, kd, vd):
   """Shapes up to the reference model's (head dimensions 128, modal/../conv_wrapper sizes), ragged tails, an initial
   state; compared with the chunked oracle and, for the short cases, the float64 recurrence."""
