@@ -251,6 +251,9 @@ def main():
   ap.add_argument("--ep-return", choices=["fused", "kernel", "combined"], default=None,
                   help="rows come back per slot from the GEMM epilogues, per slot by a transfer kernel, or as one partial "
                        "row per token and rank (needs --ep-push unique)")
+  ap.add_argument("--ep-return-sms", default=None,
+                  help="SMs given to the GEMMs whose epilogues send rows home; the next range's first GEMM runs beside "
+                       "them on the rest (0: one GEMM at a time on all SMs); N or FWD,BWD")
   ap.add_argument("--ep-dw-per-range", action="store_true",
                   help="A/B switch: weight-gradient GEMMs range by range instead of once after the last range")
   ap.add_argument("--preload-s", type=float, default=2.0,
@@ -619,6 +622,8 @@ def ep_exchange_mode(args):
   if args.ep_return is not None:
     kw["fused_return"] = args.ep_return == "fused"
     kw["combined_return"] = args.ep_return == "combined"
+  if args.ep_return_sms is not None:
+    kw["return_sms"] = tuple(int(v) for v in str(args.ep_return_sms).split(","))[:2]
   return kw
 
 

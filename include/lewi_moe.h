@@ -509,6 +509,13 @@ int lewi_ep_zero_pad(void* stream, void* buf, int32_t* ret, const int32_t* valid
  * Host-side switch read at launch time; not thread-safe against concurrent launches. */
 int lewi_set_sm_sharing(int on);
 
+/* n >= 2: the grouped-GEMM launches that follow use at most n CTAs (an odd n counts as n-1 for the CTA-pair kernels);
+ * 0 (default): one CTA per SM.  With limits that add up to the SM count, two GEMMs launched on different streams run
+ * side by side, each on its share of the GPU: the expert-parallel layer gives the GEMM whose epilogue sends rows to
+ * peers (and therefore runs at the speed of the links) a part of the SMs and the next range's first GEMM the rest.
+ * Host-side switch read at launch time; not thread-safe against concurrent launches. */
+int lewi_set_gemm_cta_limit(int n);
+
 /* All-gather of a small table by peer stores: src i32 [n] goes to elements [dst_offset, dst_offset+n) of every
  * peer's buffer (used for the expert histograms: dst_offset = me*E).  Follow it with lewi_ep_barrier. */
 int lewi_ep_put_i32(void* stream, const int32_t* src, void* const* peers_dst_host, int64_t dst_offset, int n, int G);

@@ -966,6 +966,13 @@ inline bool& sm_sharing() {
 }
 constexpr size_t SMEM_EXCLUSIVE_PAD = 1024;
 
+// Upper bound on the CTAs of the GEMM launches that follow (0: one per SM).  Two GEMMs launched on different streams
+// with limits that add up to the SM count run side by side, each on its share of the GPU.
+inline int& cta_limit() {
+  static int n = 0;
+  return n;
+}
+
 template <int MAJOR, int EPI, bool PAIR>
 inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb, const CUtensorMap& tb2, Args a,
                   long long max_tiles, const CUtensorMap& tc, const CUtensorMap& td) {
@@ -991,6 +998,7 @@ inline int launch(cudaStream_t st, const CUtensorMap& ta, const CUtensorMap& tb,
   if (max_tiles <= 0) return LEWI_OK;
   const size_t smem = SMEM_BYTES + (sm_sharing() ? 0 : SMEM_EXCLUSIVE_PAD);
   long long grid = num_sms();
+  if (cta_limit() > 0 && grid > cta_limit()) grid = cta_limit();
   if constexpr (PAIR) {
     grid &= ~1LL;
     if (grid > 2 * max_tiles) grid = 2 * max_tiles;

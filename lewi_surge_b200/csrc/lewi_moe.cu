@@ -1546,6 +1546,12 @@ int lewi_moe_bwd(void* stream, void* side_stream, const void* dout, const void* 
   return LEWI_OK;
 }
 
+int lewi_set_gemm_cta_limit(int n) {
+  if (n < 0 || n == 1) return LEWI_ERR_ARG;
+  gg::cta_limit() = n;
+  return LEWI_OK;
+}
+
 // A/B switch: 0 forces the single-CTA (cta_group::1) GEMM kernels, 1 (default) allows CTA pairs.
 int lewi_set_cta_pair(int on) {
   gg::pair_mode() = on != 0;

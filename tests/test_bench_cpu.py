@@ -62,7 +62,7 @@ def test_work_table_adds_up_to_the_layer():
 def test_exchange_flags_map_to_layer_arguments():
   import argparse
   import bench
-  ns = lambda **kw: argparse.Namespace(ep_push=None, ep_return=None, ep_range_weights=None, **kw)
+  ns = lambda **kw: argparse.Namespace(ep_push=None, ep_return=None, ep_range_weights=None, ep_return_sms=None, **kw)
   assert bench.ep_exchange_mode(ns()) == {}
   a = ns()
   a.ep_push, a.ep_return = "unique", "combined"

@@ -50,12 +50,14 @@ def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
       # others compute the weight gradients once at the end and send rows back from the GEMM epilogues
       # "p2p-unique": a token travels once per destination rank and one partial row per token comes back;
       # "p2p-unique-slots": once per rank on the way out, per slot from the GEMM epilogues on the way back
-      phases = {"p2p": 1, "p2p-phased": 4, "p2p-nccl": 2, "p2p-ranges": 3, "p2p-unique": 4, "p2p-unique-slots": 2}[impl]
+      # "p2p-split": the GEMMs that send rows home run on 48 SMs beside the next range's first GEMM
+      phases = {"p2p": 1, "p2p-phased": 4, "p2p-nccl": 2, "p2p-ranges": 3, "p2p-unique": 4, "p2p-unique-slots": 2,
+                "p2p-split": 4}[impl]
       lay = ep.ExpertParallelP2P(w, k, e, t, d, phases=phases, sync="nccl" if impl == "p2p-nccl" else "flags",
                                  range_weights=[1, 2, 1] if impl == "p2p-ranges" else None,
                                  dw_deferred=impl != "p2p-ranges", fused_return=impl != "p2p-ranges",
                                  unique_push=impl.startswith("p2p-unique"),
-                                 combined_return=impl == "p2p-unique")
+                                 combined_return=impl == "p2p-unique", return_sms=48 if impl == "p2p-split" else 0)
     else:
       lay = ep.ExpertParallelLayer(w, k, e)
     sl = slice(rank * t, (rank + 1) * t)
@@ -74,13 +76,13 @@ def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("impl", ["p2p", "p2p-phased", "p2p-ranges", "p2p-unique", "p2p-unique-slots"])
+@pytest.mark.parametrize("impl", ["p2p", "p2p-phased", "p2p-ranges", "p2p-unique", "p2p-unique-slots", "p2p-split"])
 def test_peer_memory_layer_on_one_gpu(cuda, tmp_path, impl):
   """World size 1: the push / return kernels, the plan and the barrier run against this GPU's own buffers."""
   _check(cuda, tmp_path, (512, 256, 16, 128, 128, 4), 1, impl)
 
 
-@pytest.mark.parametrize("impl", ["nccl", "p2p", "p2p-phased", "p2p-nccl", "p2p-ranges", "p2p-unique", "p2p-unique-slots"])
+@pytest.mark.parametrize("impl", ["nccl", "p2p", "p2p-phased", "p2p-nccl", "p2p-ranges", "p2p-unique", "p2p-unique-slots", "p2p-split"])
 @pytest.mark.parametrize("cfg", [(512, 256, 16, 128, 128, 4), (1024, 1024, 64, 512, 512, 6)])
 def test_expert_parallel_matches_single_gpu(cuda, tmp_path, cfg, impl):
   world = min(torch.cuda.device_count(), 4)
