@@ -1,4 +1,4 @@
-"""Whole MoE layer, forward and backward, against the float32 oracle (BASELINE tolerance 1e-2)."""
+"""Whole MoE layer, forward and backward, against the float32 oracle (tolerance 1e-2)."""
 import numpy as np
 import pytest
 import torch
@@ -66,19 +66,19 @@ def test_layer_small(cuda, t, d, e, f, fs, k):
 
 
 def test_layer_config1(cuda):
-  """BASELINE config 1: T=4096, d=1024, 64 experts x 512, top-6, shared 512, seed 0."""
+  """Benchmark config 1: T=4096, d=1024, 64 experts x 512, top-6, shared 512, seed 0."""
   inp, out, cache, grads, want, c, g = run_layer(cuda, 4096, 1024, 64, 512, 512, 6, seed=0)
   compare(out, cache, grads, want, c, g, 6)
 
 
 def test_layer_config2_full_size_against_the_oracle(cuda):
-  """BASELINE config 2 at its own size: T=32768, d=1024, 128 experts x 512, top-6, shared 512."""
+  """Benchmark config 2 at its own size: T=32768, d=1024, 128 experts x 512, top-6, shared 512."""
   inp, out, cache, grads, want, c, g = run_layer(cuda, 32768, 1024, 128, 512, 512, 6, seed=0)
   compare(out, cache, grads, want, c, g, 6)
 
 
 def test_layer_config3_full_size_skewed_routing(cuda):
-  """BASELINE config 3 at its own size: T=65536 with the Zipf(1.2) router bias; most experts are empty, a few own
+  """Benchmark config 3 at its own size: T=65536 with the Zipf(1.2) router bias; most experts are empty, a few own
   most rows (their weight-gradient contractions are cut into parts), every integer table is compared."""
   e = 128
   bias = O.zipf_bias(e, seed=0)
@@ -89,13 +89,13 @@ def test_layer_config3_full_size_skewed_routing(cuda):
 
 
 def test_layer_config4_shapes(cuda):
-  """BASELINE config 4's layer (d=2048, 256 experts x 768, top-8, shared 2048) on 4096 tokens."""
+  """Benchmark config 4's layer (d=2048, 256 experts x 768, top-8, shared 2048) on 4096 tokens."""
   inp, out, cache, grads, want, c, g = run_layer(cuda, 4096, 2048, 256, 768, 2048, 8, seed=4)
   compare(out, cache, grads, want, c, g, 8)
 
 
 def test_layer_config5_shapes(cuda):
-  """BASELINE config 5's per-GPU share: 16384 tokens of the long sequence, config-2 widths."""
+  """Benchmark config 5's per-GPU share: 16384 tokens of the long sequence, config-2 widths."""
   inp, out, cache, grads, want, c, g = run_layer(cuda, 16384, 1024, 128, 512, 512, 6, seed=5)
   compare(out, cache, grads, want, c, g, 6)
 
@@ -196,7 +196,7 @@ def test_layer_autograd_wrapper_and_determinism(cuda):
 
 
 def test_full_size_config2_properties(cuda):
-  """BASELINE config 2 (T=32768, 128 experts): properties that do not need the CPU oracle.
+  """Benchmark config 2 (T=32768, 128 experts): properties that do not need the CPU oracle.
 
   * scaling the upstream gradient by 2 scales every gradient by exactly 2 (all kernels are linear in it);
   * zero shared-expert weights leave the routed output unchanged when added back.
