@@ -100,26 +100,30 @@ class ClockSampler:
     self._stop = False
     self._thread = None
 
-  def _run(self):
+  def _open(self):
+    """NVML handle and the constant queries, before the timed region starts (the first sample must not wait for them)."""
+    import pynvml as nv
+    nv.nvmlInit()
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    idx = self.gpu_index
+    if vis:
+      try:
+        idx = int(vis.split(",")[self.gpu_index])
+      except (ValueError, IndexError):
+        idx = self.gpu_index
+    h = nv.nvmlDeviceGetHandleByIndex(idx)
+    self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
+    names = {
+        getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
+        getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
+        getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
+        getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
+    }
+    get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
+    return nv, h, names, get_reasons
+
+  def _run(self, nv, h, names, get_reasons):
     try:
-      import pynvml as nv
-      nv.nvmlInit()
-      vis = os.environ.get("CUDA_VISIBLE_DEVICES")
-      idx = self.gpu_index
-      if vis:
-        try:
-          idx = int(vis.split(",")[self.gpu_index])
-        except (ValueError, IndexError):
-          idx = self.gpu_index
-      h = nv.nvmlDeviceGetHandleByIndex(idx)
-      self.max_mhz = float(nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM))
-      names = {
-          getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8): "hw_slowdown",
-          getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40): "hw_thermal_slowdown",
-          getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20): "sw_thermal_slowdown",
-          getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4): "sw_power_cap",
-      }
-      get_reasons = getattr(nv, "nvmlDeviceGetCurrentClocksEventReasons", None) or nv.nvmlDeviceGetCurrentClocksThrottleReasons
       while not self._stop:
         self.samples.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
         r = int(get_reasons(h))
@@ -127,12 +131,16 @@ class ClockSampler:
           if r & bit:
             self.reasons.add(name)
         time.sleep(self.period)
-    except Exception:  # noqa: BLE001  (no NVML: the line reports no samples)
+    except Exception:  # noqa: BLE001  (NVML went away: the line reports the samples taken so far)
       pass
 
   def start(self):
     import threading
-    self._thread = threading.Thread(target=self._run, daemon=True)
+    try:
+      opened = self._open()
+    except Exception:  # noqa: BLE001  (no NVML: the line reports no samples)
+      return
+    self._thread = threading.Thread(target=self._run, args=opened, daemon=True)
     self._thread.start()
 
   def stop(self):
