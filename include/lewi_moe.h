@@ -301,11 +301,26 @@ int lewi_causal_conv1d_bwd(void* stream, const void* x, const void* w, const voi
  * h0 f32 [B,H,K,V] or null (zero state); h_final f32 [B,H,K,V] or null.  K <= 128 and a multiple of 8, V a
  * multiple of 8.  S need not be a multiple of 64 (the tail is padded with empty tokens, as the reference pads).
  * workspace: lewi_gdn_chunk_workspace_bytes(...) bytes (per-chunk u, w, in-chunk attention and cumulative decay).
- * Forward only: the reference differentiates this function through JAX autodiff; no backward kernel exists here. */
+ * The reference differentiates this function through JAX autodiff; lewi_gdn_chunk_bwd below is its gradient here. */
 int64_t lewi_gdn_chunk_workspace_bytes(int B, int S, int H, int K, int V);
 int lewi_gdn_chunk_fwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
                        const float* h0, void* o, float* h_final, void* workspace, int64_t workspace_bytes, int B,
                        int S, int H, int K, int V);
+
+/* Backward of lewi_gdn_chunk_fwd: gradients of q, k, v, beta (bf16, shapes of the inputs), g (f32 [B,S,H]) and,
+ * optionally, of the initial state (dh0 f32 [B,H,K,V], may be null) from d_o (bf16 [B,S,H,V]) and, optionally, the
+ * gradient of the final state (dh_final f32 [B,H,K,V], may be null).  fwd_workspace is the workspace lewi_gdn_chunk_fwd
+ * filled for the same inputs (it holds u, w, the in-chunk attention and the cumulative decay of every chunk); workspace
+ * is scratch of lewi_gdn_chunk_bwd_workspace_bytes (the state at the start of every chunk, which the first kernel
+ * recomputes, and per-column-block partial sums that are added in a fixed order: no atomics, reproducible).  The
+ * forward pass's roundings to bf16 are kept in the values and differentiated as the identity, which is what automatic
+ * differentiation of the reference's forward (modal/gdn_fast.py:37-113) does with its casts; the reference has no
+ * backward of its own to compare with.  K, V <= 128, multiples of 8. */
+int64_t lewi_gdn_chunk_bwd_workspace_bytes(int B, int S, int H, int K, int V);
+int lewi_gdn_chunk_bwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
+                       const float* h0, const void* d_o, const float* dh_final, const void* fwd_workspace,
+                       int64_t fwd_workspace_bytes, void* workspace, int64_t workspace_bytes, void* dq, void* dk, void* dv,
+                       float* dg, void* dbeta, float* dh0, int B, int S, int H, int K, int V);
 
 /* ------------------------------------------------------------------------------------------------
  * The whole layer in two calls.  lewi_moe_fwd / lewi_moe_bwd queue the complete launch sequence of the MoE layer of

@@ -59,6 +59,9 @@ SIGNATURES = {
     "lewi_ep_local_rows": (c_int, [P, P, P, P, c_int, c_int, P, c_int, c_int64, c_int64]),
     "lewi_ep_combine_return": (c_int, [P, P, P, P, P, P, c_int, P, c_int, c_int, c_int, c_int64, c_int64, c_int]),
     "lewi_set_gemm_cta_limit": (c_int, [c_int]),
+    "lewi_gdn_chunk_bwd_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int, c_int]),
+    "lewi_gdn_chunk_bwd": (c_int, [P, P, P, P, P, P, P, P, P, P, c_int64, P, c_int64, P, P, P, P, P, P, c_int, c_int, c_int,
+                                   c_int, c_int]),
     "lewi_grouped_gemm_nn_return": (c_int, [P, P, P, P, P, c_int, c_int64, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_grouped_gemm_dx_return": (c_int, [P, P, P, P, P, P, c_int, c_int64, P, P, P, c_int64, c_int, c_int, c_int]),
     "lewi_causal_conv1d_workspace_bytes": (c_int64, [c_int, c_int, c_int, c_int]),

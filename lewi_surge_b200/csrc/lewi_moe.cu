@@ -8,6 +8,7 @@
 #include "router_gemm.cuh"
 #include "routing.cuh"
 #include "seqmix.cuh"
+#include "seqmix_bwd.cuh"
 
 #include <cstring>
 #include <mutex>
@@ -1226,6 +1227,54 @@ int lewi_gdn_chunk_fwd(void* stream, const void* q, const void* k, const void* v
   else
     gdn_chunk_scan_kernel<32><<<grid, kGdnThreads, smem_b, st>>>(qb, kb, reinterpret_cast<const uint8_t*>(workspace), h0,
                                                               reinterpret_cast<__nv_bfloat16*>(o), h_final, D);
+  LEWI_CHECK_LAUNCH();
+  return LEWI_OK;
+}
+
+int64_t lewi_gdn_chunk_bwd_workspace_bytes(int B, int S, int H, int K, int V) {
+  if (B <= 0 || S <= 0 || H <= 0 || K <= 0 || V <= 0) return LEWI_ERR_ARG;
+  GdnDims D{B, S, H, K, V, (S + kGdnChunk - 1) / kGdnChunk};
+  return gdn_bwd_ws(D).total;
+}
+
+int lewi_gdn_chunk_bwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
+                       const float* h0, const void* d_o, const float* dh_final, const void* fwd_workspace,
+                       int64_t fwd_workspace_bytes, void* workspace, int64_t workspace_bytes, void* dq, void* dk, void* dv,
+                       float* dg, void* dbeta, float* dh0, int B, int S, int H, int K, int V) {
+  if (!q || !k || !v || !g || !beta || !d_o || !fwd_workspace || !workspace || !dq || !dk || !dv || !dg || !dbeta)
+    return LEWI_ERR_ARG;
+  if (B <= 0 || S <= 0 || H <= 0 || K <= 0 || V <= 0) return LEWI_ERR_ARG;
+  if (K > kGdnBwdMaxDim || V > kGdnBwdMaxDim) return LEWI_ERR_LIMIT;
+  if (K % 8 != 0 || V % 8 != 0) return LEWI_ERR_SHAPE;
+  if (fwd_workspace_bytes < lewi_gdn_chunk_workspace_bytes(B, S, H, K, V)) return LEWI_ERR_WORKSPACE;
+  if (workspace_bytes < lewi_gdn_chunk_bwd_workspace_bytes(B, S, H, K, V)) return LEWI_ERR_WORKSPACE;
+  GdnDims D{B, S, H, K, V, (S + kGdnChunk - 1) / kGdnChunk};
+  const size_t smem_a = gdn_bwd_scan_smem_bytes(K), smem_b = gdn_bwd_chunk_smem_bytes(K, V);
+  if (smem_a > 220 * 1024 || smem_b > 220 * 1024) return LEWI_ERR_LIMIT;
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return LEWI_ERR_CUDA;
+  if (!attr_set[dev]) {
+    if (cudaFuncSetAttribute(gdn_bwd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess ||
+        cudaFuncSetAttribute(gdn_bwd_chunk_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024) != cudaSuccess) {
+      (void)cudaGetLastError();
+      return LEWI_ERR_CUDA;
+    }
+    attr_set[dev] = true;
+  }
+  cudaStream_t st = as_stream(stream);
+  const __nv_bfloat16* qb = reinterpret_cast<const __nv_bfloat16*>(q);
+  const __nv_bfloat16* kb = reinterpret_cast<const __nv_bfloat16*>(k);
+  const uint8_t* fws = reinterpret_cast<const uint8_t*>(fwd_workspace);
+  uint8_t* bws = reinterpret_cast<uint8_t*>(workspace);
+  (void)g;   // the forward workspace holds the cumulative decay of every chunk
+  gdn_bwd_scan_kernel<<<dim3((unsigned)((V + kGdnBwdVB - 1) / kGdnBwdVB), (unsigned)H, (unsigned)B), kGdnThreads, smem_a, st>>>(
+      qb, kb, fws, h0, reinterpret_cast<const __nv_bfloat16*>(d_o), dh_final, bws, dh0, D);
+  LEWI_CHECK_LAUNCH();
+  gdn_bwd_chunk_kernel<<<dim3((unsigned)D.N, (unsigned)H, (unsigned)B), kGdnThreads, smem_b, st>>>(
+      qb, kb, reinterpret_cast<const __nv_bfloat16*>(v), reinterpret_cast<const __nv_bfloat16*>(beta), fws, bws,
+      reinterpret_cast<__nv_bfloat16*>(dq), reinterpret_cast<__nv_bfloat16*>(dk), reinterpret_cast<__nv_bfloat16*>(dv), dg,
+      reinterpret_cast<__nv_bfloat16*>(dbeta), D);
   LEWI_CHECK_LAUNCH();
   return LEWI_OK;
 }

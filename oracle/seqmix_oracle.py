@@ -7,7 +7,8 @@ from __future__ import annotations
 
 import numpy as np
 
-__all__ = ["causal_conv1d", "causal_conv1d_bwd", "recurrent_gated_delta_rule", "chunk_gated_delta_rule"]
+__all__ = ["causal_conv1d", "causal_conv1d_bwd", "recurrent_gated_delta_rule", "chunk_gated_delta_rule",
+           "chunk_gated_delta_rule_bwd"]
 
 
 def causal_conv1d(x, w):
@@ -117,3 +118,102 @@ def chunk_gated_delta_rule(q, k, v, g, beta, chunk_size=64, initial_state=None, 
     h = h * np.exp(gg[..., -1, None, None]) + k_i.swapaxes(-1, -2) @ v_new
   o = o.transpose(0, 1, 3, 2, 4).reshape(b, -1, hh, vd)[:, :s]
   return o.astype(f32), h.astype(f32)
+
+
+def chunk_gated_delta_rule_bwd(q, k, v, g, beta, do, dh_final=None, initial_state=None, chunk_size=64):
+  """Gradient of `chunk_gated_delta_rule` (the solve form) written out by hand, in float64.
+
+  The reference has no backward of its own: JAX differentiates `fast_chunk_gated_delta_rule` (modal/gdn_fast.py:37-113),
+  and a cast to bfloat16 differentiates as the identity.  So the forward values below carry the forward pass's
+  roundings and the derivative ignores them.  tests/test_seqmix.py pins this function against torch autograd of a
+  differentiable restatement of the forward (roundings straight-through), which in turn equals the forward oracle.
+  Returns (dq, dk, dv, dg, dbeta, dh0)."""
+  f = np.float64
+  b, s, hh, kd = np.shape(k)
+  c = chunk_size
+  q, k, v, beta = (_bf16(a).astype(f) for a in (q, k, v, beta))
+  g = np.asarray(g, np.float32).astype(f)
+  do = np.asarray(do, f)
+  scale = f(_bf16(np.float32(1.0) / np.sqrt(np.float32(kd))).reshape(-1)[0])
+  pad = (-s) % c
+  if pad:
+    padf = lambda a: np.pad(a, ((0, 0), (0, pad)) + ((0, 0),) * (a.ndim - 2))
+    q, k, v, g, beta, do = map(padf, (q, k, v, g, beta, do))
+  n = q.shape[1] // c
+  chunked = lambda a: a.reshape(b, n, c, hh, -1).transpose(0, 1, 3, 2, 4)      # [B,N,H,C,*]
+  qs = _bf16(chunked(q) * scale).astype(f)
+  k_c, v_c, do_c = chunked(k), chunked(v), chunked(do)
+  g_c = g.reshape(b, n, c, hh).transpose(0, 1, 3, 2)
+  beta_c = beta.reshape(b, n, c, hh).transpose(0, 1, 3, 2)
+  gcs = np.cumsum(g_c.astype(np.float32), -1, dtype=np.float32).astype(f)
+  strict = np.tril(np.ones((c, c), bool), -1)
+  incl = np.tril(np.ones((c, c), bool))
+  kb = _bf16(k_c * beta_c[..., None]).astype(f)
+  vb = _bf16(v_c * beta_c[..., None]).astype(f)
+  p_mat = _bf16(kb @ k_c.swapaxes(-1, -2)).astype(f)
+  d_mat = np.exp(np.where(incl, gcs[..., :, None] - gcs[..., None, :], 0.0))
+  s_mat = np.where(strict, p_mat * d_mat, 0.0)
+  a_mat = np.linalg.solve(np.eye(c) + s_mat, np.broadcast_to(np.eye(c), s_mat.shape).copy())
+  e_vec = np.exp(gcs)
+  kg = kb * e_vec[..., None]
+  u = _bf16(a_mat @ vb).astype(f)
+  w = _bf16(a_mat @ kg).astype(f)
+  attn = np.where(incl, _bf16(qs @ k_c.swapaxes(-1, -2)).astype(f) * d_mat, 0.0)
+  # the state at the start of every chunk
+  h = np.zeros((b, hh, kd, v.shape[-1]), f) if initial_state is None else np.asarray(initial_state, f).copy()
+  states = []
+  for i in range(n):
+    states.append(h)
+    vn = u[:, i] - w[:, i] @ h
+    k_dec = k_c[:, i] * np.exp(gcs[:, i, :, -1, None] - gcs[:, i])[..., None]
+    h = h * np.exp(gcs[:, i, :, -1])[..., None, None] + k_dec.swapaxes(-1, -2) @ vn
+  dh = np.zeros_like(h) if dh_final is None else np.asarray(dh_final, f).copy()
+  dqs, dk, dvb, dkb, dgcs = (np.zeros_like(a) for a in (qs, k_c, vb, kb, gcs))
+  for i in reversed(range(n)):
+    h_in, gg = states[i], gcs[:, i]
+    gl, e_i = gg[..., -1], e_vec[:, i]
+    vn = u[:, i] - w[:, i] @ h_in
+    e_dk = np.exp(gl[..., None] - gg)
+    k_dec = k_c[:, i] * e_dk[..., None]
+    q_e = qs[:, i] * e_i[..., None]
+    d_o = do_c[:, i]
+    # the recurrence
+    dvn = attn[:, i].swapaxes(-1, -2) @ d_o + k_dec @ dh
+    dattn = np.where(incl, d_o @ vn.swapaxes(-1, -2), 0.0)
+    dq_e = d_o @ h_in.swapaxes(-1, -2)
+    dk_dec = vn @ dh.swapaxes(-1, -2)
+    dh_in = q_e.swapaxes(-1, -2) @ d_o + dh * np.exp(gl)[..., None, None] - w[:, i].swapaxes(-1, -2) @ dvn
+    dgc = (dq_e * q_e).sum(-1) - (dk_dec * k_dec).sum(-1)
+    dgc[..., -1] += (dh * h_in).sum((-1, -2)) * np.exp(gl) + (dk_dec * k_dec).sum((-1, -2))
+    dqs[:, i] += dq_e * e_i[..., None]
+    dk[:, i] += dk_dec * e_dk[..., None]
+    dw = -dvn @ h_in.swapaxes(-1, -2)
+    # the in-chunk attention
+    gmat = dattn * attn[:, i]
+    dgc += gmat.sum(-1) - gmat.sum(-2)
+    d_qk = dattn * d_mat[:, i]
+    dqs[:, i] += d_qk @ k_c[:, i]
+    dk[:, i] += d_qk.swapaxes(-1, -2) @ qs[:, i]
+    # u = A vb, w = A kg
+    a_i = a_mat[:, i]
+    d_a = dvn @ vb[:, i].swapaxes(-1, -2) + dw @ kg[:, i].swapaxes(-1, -2)
+    dvb[:, i] += a_i.swapaxes(-1, -2) @ dvn
+    dkg = a_i.swapaxes(-1, -2) @ dw
+    dkb[:, i] += dkg * e_i[..., None]
+    dgc += (dkg * kg[:, i]).sum(-1)
+    # A = (I + S)^-1, S = strict(P D)
+    d_s = np.where(strict, -(a_i.swapaxes(-1, -2) @ d_a @ a_i.swapaxes(-1, -2)), 0.0)
+    gmat = d_s * s_mat[:, i]
+    dgc += gmat.sum(-1) - gmat.sum(-2)
+    d_p = d_s * d_mat[:, i]
+    dkb[:, i] += d_p @ k_c[:, i]
+    dk[:, i] += d_p.swapaxes(-1, -2) @ kb[:, i]
+    dgcs[:, i] = dgc
+    dh = dh_in
+  dk += dkb * beta_c[..., None]
+  dbeta = (dkb * k_c).sum(-1) + (dvb * v_c).sum(-1)
+  dv = dvb * beta_c[..., None]
+  dg = np.flip(np.cumsum(np.flip(dgcs, -1), -1), -1)
+  rows = lambda a: a.transpose(0, 1, 3, 2, 4).reshape(b, n * c, hh, -1)[:, :s]
+  vecs = lambda a: a.transpose(0, 1, 3, 2).reshape(b, n * c, hh)[:, :s]
+  return rows(dqs * scale), rows(dk), rows(dv), vecs(dg), vecs(dbeta), dh

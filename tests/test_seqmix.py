@@ -128,3 +128,110 @@ def test_gdn_kernel_against_the_oracle(cuda, b, s, h, kd, vd):
     assert O.rel_err(to_np(o), o_rec) <= 2e-2 and O.rel_err(to_np(hf), h_rec) <= 2e-2
   o2, _ = seqmix.chunk_gated_delta_rule(dev(q), dev(k), dev(v), dev(g, torch.float32), dev(beta), initial_state=dev(h0, torch.float32))
   assert torch.equal(o, o2)
+
+
+def _round_bf16_straight_through(x):
+  return x + (x.to(torch.bfloat16).to(x.dtype) - x).detach()
+
+
+def _torch_chunked_delta_rule(q, k, v, g, beta, h0, c=64):
+  """Differentiable restatement (float64) of the chunked forward with its bf16 roundings as straight-through casts:
+  what automatic differentiation of the reference's forward computes."""
+  rb = _round_bf16_straight_through
+  b, s, hh, kd = k.shape
+  vd = v.shape[-1]
+  dt = q.dtype
+  scale = torch.tensor(1.0 / np.sqrt(np.float32(kd)), dtype=torch.float32).to(torch.bfloat16).to(dt)
+  q = rb(q * scale)
+  pad = (-s) % c
+  if pad:
+    q, k, v = (torch.cat([a, torch.zeros(b, pad, *a.shape[2:], dtype=dt)], 1) for a in (q, k, v))
+    g, beta = (torch.cat([a, torch.zeros(b, pad, hh, dtype=dt)], 1) for a in (g, beta))
+  n = q.shape[1] // c
+  ch = lambda a: a.reshape(b, n, c, hh, -1).permute(0, 1, 3, 2, 4)
+  qc, kc, vc = ch(q), ch(k), ch(v)
+  gcs = torch.cumsum(g.reshape(b, n, c, hh).permute(0, 1, 3, 2), -1)
+  bc = beta.reshape(b, n, c, hh).permute(0, 1, 3, 2)
+  strict = torch.tril(torch.ones(c, c, dtype=torch.bool), -1)
+  incl = torch.tril(torch.ones(c, c, dtype=torch.bool))
+  kb = rb(kc * bc[..., None])
+  dec = gcs[..., :, None] - gcs[..., None, :]
+  zero = torch.zeros_like(dec)
+  s_mat = torch.where(strict, rb(kb @ kc.transpose(-1, -2)) * torch.exp(torch.where(strict, dec, zero)), zero)
+  eye = torch.eye(c, dtype=dt)
+  a_mat = torch.linalg.solve(eye + s_mat, eye.expand_as(s_mat))
+  u = rb(a_mat @ rb(vc * bc[..., None]))
+  w = rb(a_mat @ (kb * torch.exp(gcs)[..., None]))
+  h = h0
+  outs = []
+  for i in range(n):
+    gg = gcs[:, i]
+    vn = u[:, i] - w[:, i] @ h
+    gd = gg[..., :, None] - gg[..., None, :]
+    attn = torch.where(incl, rb(qc[:, i] @ kc[:, i].transpose(-1, -2)) * torch.exp(torch.where(incl, gd, zero[:, i])), zero[:, i])
+    outs.append((qc[:, i] * torch.exp(gg)[..., None]) @ h + attn @ vn)
+    ki = kc[:, i] * torch.exp(gg[..., -1, None] - gg)[..., None]
+    h = h * torch.exp(gg[..., -1, None, None]) + ki.transpose(-1, -2) @ vn
+  return torch.stack(outs, 1).permute(0, 1, 3, 2, 4).reshape(b, -1, hh, vd)[:, :s], h
+
+
+def _gdn_inputs(b, s, h, kd, vd, seed):
+  rng = np.random.default_rng(seed)
+  n = lambda *shape: rng.standard_normal(shape).astype(np.float32)
+  return dict(q=O.bf16_round(n(b, s, h, kd)), k=O.bf16_round(n(b, s, h, kd) / np.sqrt(kd) * 2), v=O.bf16_round(n(b, s, h, vd)),
+              g=-np.abs(n(b, s, h)) * 0.3, beta=O.bf16_round(1 / (1 + np.exp(-n(b, s, h)))), h0=n(b, h, kd, vd) * 0.1,
+              do=O.bf16_round(n(b, s, h, vd)), dhf=n(b, h, kd, vd) * 0.1)
+
+
+@pytest.mark.parametrize("b,s,h,kd,vd", [(2, 150, 2, 16, 24), (1, 64, 1, 32, 16)])
+def test_oracle_backward_of_the_chunked_delta_rule_matches_autograd(b, s, h, kd, vd):
+  """The hand-written gradient against torch autograd of the differentiable restatement, whose forward equals the
+  forward oracle (which the reference's outputs pin)."""
+  i = _gdn_inputs(b, s, h, kd, vd, seed=3)
+  t = {n: torch.tensor(i[n], dtype=torch.float64, requires_grad=True) for n in ("q", "k", "v", "g", "beta", "h0")}
+  o, hf = _torch_chunked_delta_rule(t["q"], t["k"], t["v"], t["g"], t["beta"], t["h0"])
+  want_o, want_h = O.chunk_gated_delta_rule(i["q"], i["k"], i["v"], i["g"], i["beta"], initial_state=i["h0"])
+  # float64 here, float32 in the oracle: a product that lands on the other side of a bf16 rounding boundary moves one
+  # element by 2^-9 of its value; anything wrong with the restatement would show as an error of order one
+  assert O.rel_err(o.detach().numpy(), want_o) <= 1e-3 and O.rel_err(hf.detach().numpy(), want_h) <= 1e-3
+  ((o * torch.tensor(i["do"], dtype=torch.float64)).sum() + (hf * torch.tensor(i["dhf"], dtype=torch.float64)).sum()).backward()
+  got = O.chunk_gated_delta_rule_bwd(i["q"], i["k"], i["v"], i["g"], i["beta"], i["do"], i["dhf"], i["h0"])
+  for name, a in zip(("q", "k", "v", "g", "beta", "h0"), got):
+    assert O.rel_err(a, t[name].grad.numpy()) <= 1e-3, name
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("b,s,h,kd,vd,state", [(1, 64, 1, 16, 32, False), (2, 300, 2, 128, 128, True), (1, 200, 3, 64, 96, True),
+                                                  (1, 130, 2, 128, 64, False), (2, 1000, 2, 32, 128, True)])
+def test_gdn_backward_kernels_against_the_oracle(cuda, b, s, h, kd, vd, state):
+  """Gradients of q, k, v, g, beta and the initial state through torch.autograd, ragged tails, with and without a
+  state; bf16 gradients within bf16 rounding of the float64 oracle, float32 ones much closer; reproducible."""
+  from lewi_surge_b200 import seqmix, _lib
+  i = _gdn_inputs(b, s, h, kd, vd, seed=s + vd)
+  dev = lambda a, dt=torch.bfloat16: to_dev(a, dt, cuda)
+
+  def run():
+    t = dict(q=dev(i["q"]), k=dev(i["k"]), v=dev(i["v"]), g=dev(i["g"], torch.float32), beta=dev(i["beta"]))
+    if state:
+      t["h0"] = dev(i["h0"], torch.float32)
+    for x in t.values():
+      x.requires_grad_(True)
+    o, hf = seqmix.chunk_gated_delta_rule(t["q"], t["k"], t["v"], t["g"], t["beta"], initial_state=t.get("h0"))
+    loss = (o.float() * dev(i["do"], torch.float32)).sum()
+    if state:
+      loss = loss + (hf.float() * dev(i["dhf"], torch.float32)).sum()
+    loss.backward()
+    return {n: x.grad for n, x in t.items()}
+
+  _lib.last_status()
+  got = run()
+  assert _lib.last_status() == 0
+  want = O.chunk_gated_delta_rule_bwd(i["q"], i["k"], i["v"], i["g"], i["beta"], i["do"], i["dhf"] if state else None,
+                                      i["h0"] if state else None)
+  for name, w in zip(("q", "k", "v", "g", "beta", "h0"), want):
+    if name == "h0" and not state:
+      continue
+    assert got[name].dtype == (torch.float32 if name in ("g", "h0") else torch.bfloat16)
+    assert O.rel_err(to_np(got[name]), w) <= (2e-3 if name in ("g", "h0") else 1e-2), name
+  again = run()
+  assert all(torch.equal(got[n], again[n]) for n in got)
