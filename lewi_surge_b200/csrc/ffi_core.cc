@@ -94,4 +94,34 @@ int moe_bwd(void* stream, const MoeDims& D, const void* dout, const void* x, con
                       nullptr, aux_grad, wgrad_dtype, D.T, D.d, D.E, D.f, D.k, D.fs);
 }
 
+int64_t causal_conv1d_scratch_bytes(int b, int t, int c, int k) { return lewi_causal_conv1d_workspace_bytes(b, t, c, k); }
+
+int causal_conv1d_fwd(void* stream, const void* x, const void* w, void* y, int b, int t, int c, int k) {
+  return lewi_causal_conv1d_fwd(stream, x, w, y, b, t, c, k);
+}
+
+int causal_conv1d_bwd(void* stream, const void* x, const void* w, const void* g, void* dx, float* dw, void* scratch,
+                      int64_t scratch_bytes, int b, int t, int c, int k) {
+  return lewi_causal_conv1d_bwd(stream, x, w, g, dx, dw, LEWI_F32, scratch, scratch_bytes, b, t, c, k);
+}
+
+int64_t gdn_chunk_fwd_scratch_bytes(int b, int s, int h, int k, int v) { return lewi_gdn_chunk_workspace_bytes(b, s, h, k, v); }
+int64_t gdn_chunk_bwd_scratch_bytes(int b, int s, int h, int k, int v) {
+  return lewi_gdn_chunk_bwd_workspace_bytes(b, s, h, k, v);
+}
+
+int gdn_chunk_fwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
+                  const float* h0, void* o, float* h_final, void* saved, int64_t saved_bytes, int b, int s, int h, int kd,
+                  int vd) {
+  return lewi_gdn_chunk_fwd(stream, q, k, v, g, beta, h0, o, h_final, saved, saved_bytes, b, s, h, kd, vd);
+}
+
+int gdn_chunk_bwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
+                  const float* h0, const void* d_o, const float* dh_final, const void* saved, int64_t saved_bytes,
+                  void* scratch, int64_t scratch_bytes, void* dq, void* dk, void* dv, float* dg, void* dbeta, float* dh0,
+                  int b, int s, int h, int kd, int vd) {
+  return lewi_gdn_chunk_bwd(stream, q, k, v, g, beta, h0, d_o, dh_final, saved, saved_bytes, scratch, scratch_bytes, dq, dk,
+                            dv, dg, dbeta, dh0, b, s, h, kd, vd);
+}
+
 }  // namespace lewi_ffi

@@ -53,4 +53,20 @@ int moe_bwd(void* stream, const MoeDims& D, const void* dout, const void* x, con
             void* dx, float* dw_router, float* d_router_bias, void* dw_gate, void* dw_up, void* dw_down, void* dws_gate,
             void* dws_up, void* dws_down, float* dw_sg, float aux_grad, int wgrad_dtype);
 
+// Sequence mixing beside the layer: the causal depthwise convolution and the chunked gated delta rule, each with its
+// gradient.  Scratch sizes come from the library; XLA allocates them as extra results.
+int64_t causal_conv1d_scratch_bytes(int b, int t, int c, int k);
+int causal_conv1d_fwd(void* stream, const void* x, const void* w, void* y, int b, int t, int c, int k);
+int causal_conv1d_bwd(void* stream, const void* x, const void* w, const void* g, void* dx, float* dw, void* scratch,
+                      int64_t scratch_bytes, int b, int t, int c, int k);
+int64_t gdn_chunk_fwd_scratch_bytes(int b, int s, int h, int k, int v);
+int64_t gdn_chunk_bwd_scratch_bytes(int b, int s, int h, int k, int v);
+int gdn_chunk_fwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
+                  const float* h0, void* o, float* h_final, void* saved, int64_t saved_bytes, int b, int s, int h, int kd,
+                  int vd);
+int gdn_chunk_bwd(void* stream, const void* q, const void* k, const void* v, const float* g, const void* beta,
+                  const float* h0, const void* d_o, const float* dh_final, const void* saved, int64_t saved_bytes,
+                  void* scratch, int64_t scratch_bytes, void* dq, void* dk, void* dv, float* dg, void* dbeta, float* dh0,
+                  int b, int s, int h, int kd, int vd);
+
 }  // namespace lewi_ffi

@@ -161,6 +161,58 @@ ffi::Error MoeBwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> dout, ffi::Buffer<
                "lewi_moe_bwd");
 }
 
+// causal_conv1d(x [B,T,C] bf16, w [K,1,C] bf16) -> y [B,T,C]  (modal/fast_conv.py:14-31)
+ffi::Error CausalConvFwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> x, ffi::Buffer<ffi::BF16> w,
+                         ffi::ResultBuffer<ffi::BF16> y) {
+  const auto xd = x.dimensions();
+  return Check(lewi_ffi::causal_conv1d_fwd(stream, x.typed_data(), w.typed_data(), y->typed_data(), (int)xd[0], (int)xd[1],
+                                           (int)xd[2], (int)w.dimensions()[0]),
+               "lewi_causal_conv1d_fwd");
+}
+
+// its gradient: (x, w, g) -> dx [B,T,C] bf16, dw [K,1,C] f32; scratch u8
+ffi::Error CausalConvBwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> x, ffi::Buffer<ffi::BF16> w, ffi::Buffer<ffi::BF16> g,
+                         ffi::ResultBuffer<ffi::BF16> dx, ffi::ResultBuffer<ffi::F32> dw,
+                         ffi::ResultBuffer<ffi::U8> scratch) {
+  const auto xd = x.dimensions();
+  return Check(lewi_ffi::causal_conv1d_bwd(stream, x.typed_data(), w.typed_data(), g.typed_data(), dx->typed_data(),
+                                           dw->typed_data(), scratch->typed_data(), (int64_t)scratch->element_count(),
+                                           (int)xd[0], (int)xd[1], (int)xd[2], (int)w.dimensions()[0]),
+               "lewi_causal_conv1d_bwd");
+}
+
+// chunk_gated_delta_rule(q, k [B,S,H,K], v [B,S,H,V] bf16, g f32 [B,S,H], beta bf16 [B,S,H], h0 f32 [B,H,K,V] or empty)
+// -> o bf16 [B,S,H,V], h_final f32 [B,H,K,V], saved u8 (kept for the gradient)   (modal/gdn_fast.py:37-113)
+ffi::Error GdnChunkFwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> q, ffi::Buffer<ffi::BF16> k, ffi::Buffer<ffi::BF16> v,
+                       ffi::Buffer<ffi::F32> g, ffi::Buffer<ffi::BF16> beta, ffi::Buffer<ffi::F32> h0,
+                       ffi::ResultBuffer<ffi::BF16> o, ffi::ResultBuffer<ffi::F32> h_final,
+                       ffi::ResultBuffer<ffi::U8> saved, bool has_state) {
+  const auto kd = k.dimensions();
+  return Check(lewi_ffi::gdn_chunk_fwd(stream, q.typed_data(), k.typed_data(), v.typed_data(), g.typed_data(),
+                                       beta.typed_data(), has_state ? h0.typed_data() : nullptr, o->typed_data(),
+                                       h_final->typed_data(), saved->typed_data(), (int64_t)saved->element_count(),
+                                       (int)kd[0], (int)kd[1], (int)kd[2], (int)kd[3], (int)v.dimensions()[3]),
+               "lewi_gdn_chunk_fwd");
+}
+
+// its gradient: (q, k, v, g, beta, h0, do, dh_final or empty, saved) -> dq, dk, dv bf16, dg f32, dbeta bf16, dh0 f32; scratch u8
+ffi::Error GdnChunkBwd(cudaStream_t stream, ffi::Buffer<ffi::BF16> q, ffi::Buffer<ffi::BF16> k, ffi::Buffer<ffi::BF16> v,
+                       ffi::Buffer<ffi::F32> g, ffi::Buffer<ffi::BF16> beta, ffi::Buffer<ffi::F32> h0,
+                       ffi::Buffer<ffi::BF16> d_o, ffi::Buffer<ffi::F32> dh_final, ffi::Buffer<ffi::U8> saved,
+                       ffi::ResultBuffer<ffi::BF16> dq, ffi::ResultBuffer<ffi::BF16> dk, ffi::ResultBuffer<ffi::BF16> dv,
+                       ffi::ResultBuffer<ffi::F32> dg, ffi::ResultBuffer<ffi::BF16> dbeta, ffi::ResultBuffer<ffi::F32> dh0,
+                       ffi::ResultBuffer<ffi::U8> scratch, bool has_state, bool has_dstate) {
+  const auto kd = k.dimensions();
+  return Check(lewi_ffi::gdn_chunk_bwd(stream, q.typed_data(), k.typed_data(), v.typed_data(), g.typed_data(),
+                                       beta.typed_data(), has_state ? h0.typed_data() : nullptr, d_o.typed_data(),
+                                       has_dstate ? dh_final.typed_data() : nullptr, saved.typed_data(),
+                                       (int64_t)saved.element_count(), scratch->typed_data(),
+                                       (int64_t)scratch->element_count(), dq->typed_data(), dk->typed_data(),
+                                       dv->typed_data(), dg->typed_data(), dbeta->typed_data(), dh0->typed_data(),
+                                       (int)kd[0], (int)kd[1], (int)kd[2], (int)kd[3], (int)v.dimensions()[3]),
+               "lewi_gdn_chunk_bwd");
+}
+
 }  // namespace
 
 #define LEWI_STREAM ffi::Ffi::Bind().Ctx<ffi::PlatformStream<cudaStream_t>>()
@@ -196,3 +248,13 @@ XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_moe_bwd, MoeBwd,
                                   .Arg<B16>().Arg<B16>().Arg<F32B>().Arg<U8B>().Ret<B16>().Ret<F32B>().Ret<F32B>().Ret<B16>()
                                   .Ret<B16>().Ret<B16>().Ret<B16>().Ret<B16>().Ret<B16>().Ret<F32B>().Ret<U8B>()
                                   .Attr<int32_t>("k").Attr<bool>("has_bias").Attr<bool>("has_gate").Attr<float>("aux_grad"));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_causal_conv1d_fwd, CausalConvFwd, LEWI_STREAM.Arg<B16>().Arg<B16>().Ret<B16>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_causal_conv1d_bwd, CausalConvBwd,
+                              LEWI_STREAM.Arg<B16>().Arg<B16>().Arg<B16>().Ret<B16>().Ret<F32B>().Ret<U8B>());
+XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_gdn_chunk_fwd, GdnChunkFwd,
+                              LEWI_STREAM.Arg<B16>().Arg<B16>().Arg<B16>().Arg<F32B>().Arg<B16>().Arg<F32B>().Ret<B16>()
+                                  .Ret<F32B>().Ret<U8B>().Attr<bool>("has_state"));
+XLA_FFI_DEFINE_HANDLER_SYMBOL(lewi_ffi_gdn_chunk_bwd, GdnChunkBwd,
+                              LEWI_STREAM.Arg<B16>().Arg<B16>().Arg<B16>().Arg<F32B>().Arg<B16>().Arg<F32B>().Arg<B16>()
+                                  .Arg<F32B>().Arg<U8B>().Ret<B16>().Ret<B16>().Ret<B16>().Ret<F32B>().Ret<B16>().Ret<F32B>()
+                                  .Ret<U8B>().Attr<bool>("has_state").Attr<bool>("has_dstate"));

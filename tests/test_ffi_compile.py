@@ -24,7 +24,8 @@ def test_xla_free_core_compiles_and_links(tmp_path):
                        capture_output=True, text=True)
   assert res.returncode == 0, res.stderr
   syms = subprocess.run(["nm", "-D", "--defined-only", str(out)], capture_output=True, text=True).stdout
-  for name in ("sort_indices", "gather_rows", "ragged_dot_fwd", "ragged_dot_dlhs", "ragged_dot_drhs", "moe_fwd", "moe_bwd"):
+  for name in ("sort_indices", "gather_rows", "ragged_dot_fwd", "ragged_dot_dlhs", "ragged_dot_drhs", "moe_fwd", "moe_bwd",
+               "causal_conv1d_fwd", "causal_conv1d_bwd", "gdn_chunk_fwd", "gdn_chunk_bwd"):
     assert re.search(rf"lewi_ffi\d+{name}", syms), name
 
 
@@ -38,9 +39,9 @@ def test_handler_layer_type_checks_against_the_stand_in_header():
 def test_python_side_registers_the_handlers_the_cxx_side_defines():
   from lewi_surge_b200 import jax_ops
   src = open(os.path.join(CSRC, "ffi_xla.cc")).read()
-  defined = re.findall(r"XLA_FFI_DEFINE_HANDLER_SYMBOL\((lewi_ffi_[a-z_]+),", src)
+  defined = re.findall(r"XLA_FFI_DEFINE_HANDLER_SYMBOL\((lewi_ffi_[a-z0-9_]+),", src)
   assert sorted(defined) == sorted(jax_ops._TARGETS)
-  used = set(re.findall(r'ffi_call\(\s*"(lewi_ffi_[a-z_]+)"', open(jax_ops.__file__).read()))
+  used = set(re.findall(r'ffi_call\(\s*"(lewi_ffi_[a-z0-9_]+)"', open(jax_ops.__file__).read()))
   assert used == set(defined)
 
 
