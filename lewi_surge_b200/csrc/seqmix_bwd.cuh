@@ -145,18 +145,28 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_bwd_scan_kernel(const __nv_bf
       sEk[tid] = __expf(gl - gc);
     }
     __syncthreads();
-    for (int i = tid; i < C * K; i += kGdnThreads) {
-      const int r = i / K, c = i - r * K;
+    const int kv8 = K / 8;   // K is a multiple of 8: 16-byte pieces of the bf16 rows
+    for (int i = tid; i < C * kv8; i += kGdnThreads) {
+      const int r = i / kv8, c = (i - r * kv8) * 8;
       const long long t = tok0 + r;
-      float kv = 0.f, qv = 0.f;
+      uint4 kraw = make_uint4(0, 0, 0, 0), qraw = make_uint4(0, 0, 0, 0);
       if (t < D.S) {
         const long long off = (((long long)b * D.S + t) * D.H + h) * K + c;
-        kv = __bfloat162float(k[off]);
-        if (backward) qv = gdn_round_bf16(__bfloat162float(q[off]) * scale);
+        kraw = *reinterpret_cast<const uint4*>(k + off);
+        if (backward) qraw = *reinterpret_cast<const uint4*>(q + off);
       }
-      sQ[r * KP + c] = qv * sEq[r];
-      sK[r * KP + c] = kv * sEk[r];
-      sW[r * KP + c] = __bfloat162float(w_in[i]);
+      const uint4 wraw = *reinterpret_cast<const uint4*>(w_in + r * K + c);
+      float kf[8], qf[8], wf[8];
+      lewi::Elem<__nv_bfloat16>::unpack(kraw, kf);
+      lewi::Elem<__nv_bfloat16>::unpack(qraw, qf);
+      lewi::Elem<__nv_bfloat16>::unpack(wraw, wf);
+      const float eq = sEq[r], ek = sEk[r];
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        sQ[r * KP + c + x] = gdn_round_bf16(qf[x] * scale) * eq;
+        sK[r * KP + c + x] = kf[x] * ek;
+        sW[r * KP + c + x] = wf[x];
+      }
     }
     for (int i = tid; i < C * VB; i += kGdnThreads) {
       const int r = i / VB, c = i - r * VB;
@@ -256,45 +266,25 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_bwd_scan_kernel(const __nv_bf
     }
     __syncthreads();
     // what contracts over this CTA's columns leaves as a partial: dqE = do h_in^T, dkd = v_new dh^T, dw = -dv_new h_in^T
+    // (one product at a time: three sets of 32 accumulators at once did not fit the register file)
     for (int col0 = 0; col0 < K; col0 += 128) {
-      float aq[4][8], ak[4][8], aw[4][8];
-      gdn_tile_zero(aq);
-      gdn_tile_zero(ak);
-      gdn_tile_zero(aw);
-      for (int x = 0; x < VB; ++x) {
-        float a_do[4], a_vn[4], a_dv[4], b_hin[8], b_dh[8];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          a_do[i] = sDo[(tr * 4 + i) * VBP + x];
-          a_vn[i] = sVn[(tr * 4 + i) * VBP + x];
-          a_dv[i] = sDv[(tr * 4 + i) * VBP + x];
-        }
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int kk = col0 + tc + 16 * j;
-          b_hin[j] = kk < K ? sHin[kk * VBP + x] : 0.f;
-          b_dh[j] = kk < K ? sH[kk * VBP + x] : 0.f;
-        }
+      for (int which = 0; which < 3; ++which) {
+        const float* lhs = which == 0 ? sDo : (which == 1 ? sVn : sDv);
+        const float* rhs = which == 1 ? sH : sHin;
+        float* dst = which == 0 ? pq : (which == 1 ? pk : pw);
+        const float sign = which == 2 ? -1.f : 1.f;
+        float acc[4][8];
+        gdn_tile_zero(acc);
+        gdn_tile_mm<8>(acc, 0, VB, [&](int i, int x) { return lhs[(tr * 4 + i) * VBP + x]; },
+                       [&](int j, int x) { const int kk = col0 + tc + 16 * j; return kk < K ? rhs[kk * VBP + x] : 0.f; });
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
-            aq[i][j] = fmaf(a_do[i], b_hin[j], aq[i][j]);
-            ak[i][j] = fmaf(a_vn[i], b_dh[j], ak[i][j]);
-            aw[i][j] = fmaf(a_dv[i], b_hin[j], aw[i][j]);
+            const int r = tr * 4 + i, kk = col0 + tc + 16 * j;
+            if (kk < K) dst[(chunk * C + r) * K + kk] = sign * acc[i][j];
           }
       }
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int r = tr * 4 + i, kk = col0 + tc + 16 * j;
-          if (kk >= K) continue;
-          const long long at = (chunk * C + r) * K + kk;
-          pq[at] = aq[i][j];
-          pk[at] = ak[i][j];
-          pw[at] = -aw[i][j];
-        }
     }
     // dattn = lower(do v_new^T)
     {
@@ -364,7 +354,7 @@ inline size_t gdn_bwd_chunk_smem_bytes(int K, int V) {
   return (size_t)(2 * C * KP + 2 * C * WP + 4 * C * (C + 1) + 8 * C) * 4;
 }
 
-__global__ void __launch_bounds__(kGdnThreads) gdn_bwd_chunk_kernel(const __nv_bfloat16* __restrict__ q,
+__global__ void __launch_bounds__(kGdnThreads, 1) gdn_bwd_chunk_kernel(const __nv_bfloat16* __restrict__ q,
                                                                     const __nv_bfloat16* __restrict__ k,
                                                                     const __nv_bfloat16* __restrict__ v,
                                                                     const __nv_bfloat16* __restrict__ beta,
