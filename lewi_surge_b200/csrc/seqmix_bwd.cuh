@@ -43,6 +43,28 @@ __device__ __forceinline__ void gdn_tile_mm(float (&acc)[4][NJ], int x0, int x1,
   }
 }
 
+// The same tile when both operands are contiguous along the contraction: four steps per iteration through 16-byte
+// loads (fa4 / fb4 return elements x .. x+3, x a multiple of 4), added in ascending x.
+template <int NJ, class FA, class FB>
+__device__ __forceinline__ void gdn_tile_mm_x4(float (&acc)[4][NJ], int x0, int x1, FA fa4, FB fb4) {
+  for (int x = x0; x < x1; x += 4) {
+    float4 a[4], b[NJ];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) a[i] = fa4(i, x);
+#pragma unroll
+    for (int j = 0; j < NJ; ++j) b[j] = fb4(j, x);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+#pragma unroll
+      for (int j = 0; j < NJ; ++j) {
+        acc[i][j] = fmaf(a[i].x, b[j].x, acc[i][j]);
+        acc[i][j] = fmaf(a[i].y, b[j].y, acc[i][j]);
+        acc[i][j] = fmaf(a[i].z, b[j].z, acc[i][j]);
+        acc[i][j] = fmaf(a[i].w, b[j].w, acc[i][j]);
+      }
+  }
+}
+
 template <int NJ>
 __device__ __forceinline__ void gdn_tile_zero(float (&acc)[4][NJ]) {
 #pragma unroll
@@ -86,7 +108,7 @@ __host__ __device__ inline GdnBwdWs gdn_bwd_ws(const GdnDims& D) {
 }
 
 inline size_t gdn_bwd_scan_smem_bytes(int K) {
-  const int C = kGdnChunk, KP = K + 1, VBP = kGdnBwdVB + 1;
+  const int C = kGdnChunk, KP = K + 1, VBP = kGdnBwdVB + 4;
   return (size_t)(2 * K * VBP + 3 * C * KP + 3 * C * VBP + C * (C + 1) + 3 * C + 32) * 4;
 }
 
@@ -99,7 +121,9 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_bwd_scan_kernel(const __nv_bf
                                                                    uint8_t* __restrict__ bws, float* __restrict__ dh0,
                                                                    GdnDims D) {
   extern __shared__ float gdn_smem[];
-  constexpr int C = kGdnChunk, VB = kGdnBwdVB, VBP = VB + 1;
+  // rows of the [*, VB] arrays are 36 floats apart: 16-byte aligned for the 4-wide loads of the products that contract
+  // over the columns, and the 8 lanes of one 16-byte load phase (rows tc .. tc+7) fall on 8 different bank groups
+  constexpr int C = kGdnChunk, VB = kGdnBwdVB, VBP = VB + 4;
   const int K = D.K, V = D.V, KP = K + 1;
   float* sH = gdn_smem;               // [K][VBP]   forward state, later dh
   float* sHin = sH + K * VBP;         // [K][VBP]   state at the start of the current chunk
@@ -275,8 +299,12 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_bwd_scan_kernel(const __nv_bf
         const float sign = which == 2 ? -1.f : 1.f;
         float acc[4][8];
         gdn_tile_zero(acc);
-        gdn_tile_mm<8>(acc, 0, VB, [&](int i, int x) { return lhs[(tr * 4 + i) * VBP + x]; },
-                       [&](int j, int x) { const int kk = col0 + tc + 16 * j; return kk < K ? rhs[kk * VBP + x] : 0.f; });
+        gdn_tile_mm_x4<8>(acc, 0, VB,
+                          [&](int i, int x) { return *reinterpret_cast<const float4*>(&lhs[(tr * 4 + i) * VBP + x]); },
+                          [&](int j, int x) {
+                            const int kk = col0 + tc + 16 * j;
+                            return kk < K ? *reinterpret_cast<const float4*>(&rhs[kk * VBP + x]) : make_float4(0.f, 0.f, 0.f, 0.f);
+                          });
 #pragma unroll
         for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -290,8 +318,9 @@ __global__ void __launch_bounds__(kGdnThreads) gdn_bwd_scan_kernel(const __nv_bf
     {
       float acc[4][4];
       gdn_tile_zero(acc);
-      gdn_tile_mm<4>(acc, 0, VB, [&](int i, int x) { return sDo[(tr * 4 + i) * VBP + x]; },
-                     [&](int j, int x) { return sVn[(tc + 16 * j) * VBP + x]; });
+      gdn_tile_mm_x4<4>(acc, 0, VB,
+                        [&](int i, int x) { return *reinterpret_cast<const float4*>(&sDo[(tr * 4 + i) * VBP + x]); },
+                        [&](int j, int x) { return *reinterpret_cast<const float4*>(&sVn[(tc + 16 * j) * VBP + x]); });
 #pragma unroll
       for (int i = 0; i < 4; ++i)
 #pragma unroll
@@ -411,16 +440,37 @@ __global__ void __launch_bounds__(kGdnThreads, 1) gdn_bwd_chunk_kernel(const __n
     return s;
   };
 
-  // ---- loads
-  for (int i = tid; i < C * K; i += kGdnThreads) {
-    const int r = i / K, c = i - r * K;
-    float kv = 0.f, qv = 0.f;
-    if (live(r)) {
-      kv = __bfloat162float(k[tok_off(r) * K + c]);
-      qv = gdn_round_bf16(__bfloat162float(q[tok_off(r) * K + c]) * scale);
+  // the same sum for four adjacent elements (16-byte loads; every partial array starts on a 256-byte boundary and the
+  // extents are multiples of 8)
+  auto psum4 = [&](const float* p, long long stride, long long at) {
+    float4 s4 = *reinterpret_cast<const float4*>(p + at);
+    for (int sl = 1; sl < W.slices; ++sl) {
+      const float4 t4 = *reinterpret_cast<const float4*>(p + at + sl * stride);
+      s4.x += t4.x; s4.y += t4.y; s4.z += t4.z; s4.w += t4.w;
     }
-    sK[r * KP + c] = kv;
-    sQ[r * KP + c] = qv;
+    return s4;
+  };
+
+  // ---- loads (16-byte pieces: the loops below are short enough for their loads to be in flight together)
+  {
+    const int kv8 = K / 8;
+#pragma unroll 4
+    for (int i = tid; i < C * kv8; i += kGdnThreads) {
+      const int r = i / kv8, c = (i - r * kv8) * 8;
+      uint4 kraw = make_uint4(0, 0, 0, 0), qraw = make_uint4(0, 0, 0, 0);
+      if (live(r)) {
+        kraw = *reinterpret_cast<const uint4*>(k + tok_off(r) * K + c);
+        qraw = *reinterpret_cast<const uint4*>(q + tok_off(r) * K + c);
+      }
+      float kf[8], qf[8];
+      lewi::Elem<__nv_bfloat16>::unpack(kraw, kf);
+      lewi::Elem<__nv_bfloat16>::unpack(qraw, qf);
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        sK[r * KP + c + x] = kf[x];
+        sQ[r * KP + c + x] = gdn_round_bf16(qf[x] * scale);
+      }
+    }
   }
   if (tid < C) {
     const float gc = gcs_in[tid];
@@ -464,11 +514,30 @@ __global__ void __launch_bounds__(kGdnThreads, 1) gdn_bwd_chunk_kernel(const __n
     }
   }
   // ---- dattn (sum of the partials), G = dattn attn, then dattn D in place
-  for (int i = tid; i < C * C; i += kGdnThreads) {
-    const int r = i / C, c = i - r * C;
-    const float da = c <= r ? psum(pat, pstride_c, i) : 0.f;
-    sX[r * CP + c] = da * attn_in[i];
-    sT[r * CP + c] = c <= r ? da * __expf(sG[r] - sG[c]) : 0.f;
+#pragma unroll 2
+  for (int i4 = tid; i4 < C * C / 4; i4 += kGdnThreads) {
+    const int r = i4 / (C / 4), c0 = (i4 - r * (C / 4)) * 4;
+    const float4 da4 = psum4(pat, pstride_c, (long long)i4 * 4);
+    const float4 at4 = *reinterpret_cast<const float4*>(attn_in + i4 * 4);
+    const float da[4] = {da4.x, da4.y, da4.z, da4.w}, at[4] = {at4.x, at4.y, at4.z, at4.w};
+#pragma unroll
+    for (int x = 0; x < 4; ++x) {
+      const int c = c0 + x;
+      const float d = c <= r ? da[x] : 0.f;
+      sX[r * CP + c] = d * at[x];
+      sT[r * CP + c] = c <= r ? d * __expf(sG[r] - sG[c]) : 0.f;
+    }
+  }
+  // dqE and dkd (sums of the partials) wait in the two areas that vb and dv_new take over later
+  {
+    const int k4 = K / 4;
+#pragma unroll 2
+    for (int i4 = tid; i4 < C * k4; i4 += kGdnThreads) {
+      const int r = i4 / k4, c0 = (i4 - r * k4) * 4;
+      const float4 a4 = psum4(pq, pstride_k, (long long)i4 * 4), b4 = psum4(pk, pstride_k, (long long)i4 * 4);
+      sV[r * VP + c0] = a4.x; sV[r * VP + c0 + 1] = a4.y; sV[r * VP + c0 + 2] = a4.z; sV[r * VP + c0 + 3] = a4.w;
+      sU[r * VP + c0] = b4.x; sU[r * VP + c0 + 1] = b4.y; sU[r * VP + c0 + 2] = b4.z; sU[r * VP + c0 + 3] = b4.w;
+    }
   }
   __syncthreads();
   if (tid < C) {   // rowsum(G) - colsum(G)
@@ -500,8 +569,7 @@ __global__ void __launch_bounds__(kGdnThreads, 1) gdn_bwd_chunk_kernel(const __n
       for (int j = 0; j < 8; ++j) {
         const int c = tc + 16 * j;
         if (c >= K) continue;
-        const float dqe = psum(pq, pstride_k, (long long)r * K + c);
-        const float dkd = psum(pk, pstride_k, (long long)r * K + c);
+        const float dqe = sV[r * VP + c], dkd = sU[r * VP + c];
         acc[i][j] = fmaf(dqe, sE[r], acc[i][j]);
         rq = fmaf(dqe, sQ[r * KP + c] * sE[r], rq);
         dk_acc[i][j] = fmaf(dkd, sEk[r], dk_acc[i][j]);
@@ -523,15 +591,29 @@ __global__ void __launch_bounds__(kGdnThreads, 1) gdn_bwd_chunk_kernel(const __n
     sDgA[C - 1] += tot;
   }
   // ---- dw (partials) over q's place, vb and dv_new
-  for (int i = tid; i < C * K; i += kGdnThreads) {
-    const int r = i / K, c = i - r * K;
-    sQ[r * KP + c] = psum(pw, pstride_k, i);
-  }
-  for (int i = tid; i < C * V; i += kGdnThreads) {
-    const int r = i / V, c = i - r * V;
-    const float vv = live(r) ? __bfloat162float(v[tok_off(r) * V + c]) : 0.f;
-    sV[r * VP + c] = gdn_round_bf16(vv * sB[r]);
-    sU[r * VP + c] = du_in[i];
+  {
+    const int k4 = K / 4, v8 = V / 8;
+#pragma unroll 2
+    for (int i4 = tid; i4 < C * k4; i4 += kGdnThreads) {
+      const int r = i4 / k4, c0 = (i4 - r * k4) * 4;
+      const float4 w4 = psum4(pw, pstride_k, (long long)i4 * 4);
+      sQ[r * KP + c0] = w4.x; sQ[r * KP + c0 + 1] = w4.y; sQ[r * KP + c0 + 2] = w4.z; sQ[r * KP + c0 + 3] = w4.w;
+    }
+#pragma unroll 2
+    for (int i8 = tid; i8 < C * v8; i8 += kGdnThreads) {
+      const int r = i8 / v8, c0 = (i8 - r * v8) * 8;
+      const uint4 vraw = live(r) ? *reinterpret_cast<const uint4*>(v + tok_off(r) * V + c0) : make_uint4(0, 0, 0, 0);
+      const float4 u0 = *reinterpret_cast<const float4*>(du_in + (long long)r * V + c0);
+      const float4 u1 = *reinterpret_cast<const float4*>(du_in + (long long)r * V + c0 + 4);
+      float vf[8];
+      lewi::Elem<__nv_bfloat16>::unpack(vraw, vf);
+      const float uu[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+#pragma unroll
+      for (int x = 0; x < 8; ++x) {
+        sV[r * VP + c0 + x] = gdn_round_bf16(vf[x] * sB[r]);
+        sU[r * VP + c0 + x] = uu[x];
+      }
+    }
   }
   __syncthreads();
   // ---- dA = dv_new vb^T + dw kg^T  (over dattn D, which is no longer needed)
