@@ -229,7 +229,7 @@ def workload_config(args, c, world):
                       + (", Zipf(1.2) router logit bias" if c["bias"] else ""),
           "tokens_per_gpu": c["T"], "global_tokens": c["T"] * world,
           "parallelism": "single GPU" if world == 1 else
-                         f"expert-parallel x{world} ({'peer-memory push/return kernels' if args.ep_impl == 'p2p' else 'NCCL all-to-all'})",
+                         f"expert-parallel x{world} ({'peer memory: push kernels, rows returned from GEMM epilogues' if args.ep_impl == 'p2p' else 'NCCL all-to-all'})",
           "l2": "inputs larger than L2 (weights 0.4 GB + activations > 2 GB per step)"}
 
 
