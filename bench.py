@@ -262,6 +262,9 @@ def main():
   ap.add_argument("--ep-return-sms", default=None,
                   help="SMs given to the GEMMs whose epilogues send rows home; the next range's first GEMM runs beside "
                        "them on the rest (0: one GEMM at a time on all SMs); N or FWD,BWD")
+  ap.add_argument("--ep-router-tail", action="store_true",
+                  help="A/B switch: router backward on the exchange stream right after the last barrier, beside the "
+                       "weight-gradient GEMMs, instead of on the main stream after them")
   ap.add_argument("--ep-dw-per-range", action="store_true",
                   help="A/B switch: weight-gradient GEMMs range by range instead of once after the last range")
   ap.add_argument("--preload-s", type=float, default=2.0,
@@ -630,6 +633,8 @@ def ep_exchange_mode(args):
   if args.ep_return is not None:
     kw["fused_return"] = args.ep_return == "fused"
     kw["combined_return"] = args.ep_return == "combined"
+  if getattr(args, "ep_router_tail", False):
+    kw["router_tail"] = True
   if args.ep_return_sms is not None:
     kw["return_sms"] = tuple(int(v) for v in str(args.ep_return_sms).split(","))[:2]
   return kw

@@ -57,7 +57,8 @@ def _worker(rank, world, port, cfg, out_dir, impl="nccl"):
                                  range_weights=[1, 2, 1] if impl == "p2p-ranges" else None,
                                  dw_deferred=impl != "p2p-ranges", fused_return=impl != "p2p-ranges",
                                  unique_push=impl.startswith("p2p-unique"),
-                                 combined_return=impl == "p2p-unique", return_sms=48 if impl == "p2p-split" else 0)
+                                 combined_return=impl == "p2p-unique", return_sms=48 if impl == "p2p-split" else 0,
+                                 router_tail=impl == "p2p-nccl")   # (one variant keeps the router backward on the exchange stream)
     else:
       lay = ep.ExpertParallelLayer(w, k, e)
     sl = slice(rank * t, (rank + 1) * t)
