@@ -235,3 +235,15 @@ def test_gdn_backward_kernels_against_the_oracle(cuda, b, s, h, kd, vd, state):
     assert O.rel_err(to_np(got[name]), w) <= (2e-3 if name in ("g", "h0") else 1e-2), name
   again = run()
   assert all(torch.equal(got[n], again[n]) for n in got)
+
+
+def test_oracle_backward_without_a_state_matches_autograd():
+  """No initial state and no gradient into the final state: the case of a layer that starts every sequence from zero."""
+  i = _gdn_inputs(1, 100, 2, 16, 16, seed=11)
+  t = {n: torch.tensor(i[n], dtype=torch.float64, requires_grad=True) for n in ("q", "k", "v", "g", "beta")}
+  o, _ = _torch_chunked_delta_rule(t["q"], t["k"], t["v"], t["g"], t["beta"], torch.zeros(1, 2, 16, 16, dtype=torch.float64))
+  (o * torch.tensor(i["do"], dtype=torch.float64)).sum().backward()
+  got = O.chunk_gated_delta_rule_bwd(i["q"], i["k"], i["v"], i["g"], i["beta"], i["do"])
+  for name, a in zip(("q", "k", "v", "g", "beta"), got):
+    assert O.rel_err(a, t[name].grad.numpy()) <= 1e-3, name
+  assert np.all(np.isfinite(got[5]))
